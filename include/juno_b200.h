@@ -1,0 +1,196 @@
+/*
+ * juno_b200.h — C ABI of the B200 (sm_100a) decode engine for Juno.
+ *
+ * This is the surface a Java host binds with java.lang.foreign
+ * (Linker.nativeLinker().downcallHandle) in place of the cudart/cuBLAS symbol
+ * table of node/src/main/java/cab/ml/juno/node/CudaBindings.java:139-211.
+ * Conventions follow that file: every function returns an int status (0 = OK,
+ * CudaBindings.java:247-250 turns non-zero into IllegalStateException), handles
+ * are opaque pointers returned through out-parameters (CudaBindings.java:222-231),
+ * and all host buffers are plain native memory (Panama rejects heap segments,
+ * CudaMatVec.java:158-160).  No C++ types, callbacks or varargs cross the boundary.
+ *
+ * Threading: every entry point may be called from any thread; the library
+ * selects the device itself and serialises work per context (the reference
+ * holds one lock per device, GpuContext.java:99-101).
+ */
+#ifndef JUNO_B200_H
+#define JUNO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define JUNO_OK 0
+#define JUNO_ERR_INVALID_ARG (-1)
+#define JUNO_ERR_OOM (-2)      /* cudaMalloc failed (the reference string-matches "cudaMalloc",
+                                  LlamaTransformerHandler.java:350-352); there is no CPU fallback */
+#define JUNO_ERR_CUDA (-3)
+#define JUNO_ERR_NCCL (-4)
+#define JUNO_ERR_TIMEOUT (-5)
+#define JUNO_ERR_CLOSED (-6)   /* handle already freed (IllegalStateException in MatVec.java:46-54) */
+#define JUNO_ERR_UNSUPPORTED (-7)
+
+/* GGML tensor type ids accepted (GgufReader.java:54-63) */
+#define JUNO_TYPE_F32 0
+#define JUNO_TYPE_Q8_0 8
+#define JUNO_TYPE_Q4_K 12
+#define JUNO_TYPE_Q6_K 14
+
+typedef struct juno_ctx juno_ctx;
+typedef struct juno_qmat juno_qmat;
+typedef struct juno_model juno_model;
+typedef struct juno_seq juno_seq;
+typedef struct juno_kvpool juno_kvpool;
+
+/* Thread-local text of the last failure on the calling thread. */
+const char *juno_last_error(void);
+
+/* ── device discovery: replaces cudaGetDeviceCount / cudaGetDeviceProperties and
+ *    the fixed-offset pokes into cudaDeviceProp (CudaBindings.java:75-79,107-118).
+ *    Fails soft: with no driver or no device, count is 0 and the status is JUNO_OK. */
+int juno_device_count(int32_t *count);
+int juno_device_name(int32_t device, char *buf, int32_t buf_len);
+int juno_device_total_mem(int32_t device, int64_t *bytes);
+
+/* ── context: replaces GpuContext.shared/close (GpuContext.java:109-153,229-243). */
+int juno_ctx_create(int32_t device, juno_ctx **out);
+int juno_ctx_destroy(juno_ctx *ctx); /* idempotent on a closed handle: returns JUNO_ERR_CLOSED */
+int juno_ctx_device(juno_ctx *ctx, int32_t *device);
+int juno_ctx_synchronize(juno_ctx *ctx);
+
+/* ── MatVec operator (boundary A) ─────────────────────────────────────────────
+ * juno_qmat_upload replaces GpuMatVec.uploadHalf(float[],rows,cols)
+ * (GpuMatVec.java:38-70, DeviceHalfMatrix.java:66-91): it keeps the QUANTISED
+ * GGUF blocks resident (repacked into the kernels' tile order) instead of a
+ * dequantised FP16 copy.  `blocks` is the row-major raw tensor as
+ * GgufReader.tensorRaw returns it (GgufReader.java:329-360).  The caller keeps
+ * ownership of `blocks`. */
+int juno_qmat_upload(juno_ctx *ctx, const void *blocks, int32_t ggml_type, int64_t rows, int64_t cols,
+                     juno_qmat **out);
+int juno_qmat_free(juno_qmat *m);
+int juno_qmat_shape(juno_qmat *m, int64_t *rows, int64_t *cols, int32_t *ggml_type);
+
+/* y[b][rows] = A · x[b][cols], b < batch; host in, host out.  Semantics of
+ * MatVec.sgemv(DeviceHalfMatrix, float[]) (MatVec.java:86-90, CudaMatVec.java:276-333)
+ * on the quantised weights of LlamaTransformerHandler.matVec (:1200-1245):
+ * inputs are not modified, JUNO_ERR_INVALID_ARG on a dimension mismatch,
+ * JUNO_ERR_CLOSED on a freed matrix. */
+int juno_gemv(juno_ctx *ctx, juno_qmat *m, const float *x_host, int32_t batch, float *y_host);
+
+/* Same product with x and y already in device memory, enqueued on `stream`
+ * (a cudaStream_t, NULL = the context's stream) and not synchronised. */
+int juno_gemv_device(juno_ctx *ctx, juno_qmat *m, const float *x_dev, int32_t batch, float *y_dev,
+                     void *stream);
+
+/* Bit-exact dequantisation of rows [row_start, row_start+n_rows) to host FP32:
+ * LlamaTransformerHandler.dequantize (:873-885).  Used for parity checks and for
+ * embedding rows. */
+int juno_dequantize(juno_ctx *ctx, juno_qmat *m, int64_t row_start, int64_t n_rows, float *out_host);
+
+/* FP32 host-matrix product: MatVec.sgemv(float[] A, float[] x, rows, cols)
+ * (MatVec.java:66, CudaMatVec.java:141-196). */
+int juno_sgemv_f32(juno_ctx *ctx, const float *a_host, const float *x_host, int64_t rows, int64_t cols,
+                   float *y_host);
+
+/* ── paged KV cache + GQA decode attention operator ───────────────────────────
+ * Replaces the per-request float[L][pos*kvDim] heap cache and the scalar gqa()
+ * of LlamaTransformerHandler.java:670-733,1678-1730.  A pool holds `n_pages`
+ * pages of `page_tokens` (16) positions for every layer; kv_dtype 0 = FP16,
+ * 1 = FP32 (the reference's storage type). */
+int juno_kvpool_create(juno_ctx *ctx, int32_t n_layers, int32_t n_kv_heads, int32_t head_dim,
+                       int32_t n_pages, int32_t kv_dtype, juno_kvpool **out);
+int juno_kvpool_free(juno_kvpool *p);
+/* A sequence handle stands for one requestId (ForwardRequest.java:26-48);
+ * freeing it is evict(requestId) (LlamaTransformerHandler.java:498-505). */
+int juno_kvseq_create(juno_kvpool *p, int32_t max_tokens, juno_seq **out);
+int juno_seq_free(juno_seq *s);
+int juno_seq_length(juno_seq *s, int32_t *n_tokens);
+/* Append n_tokens positions of K and V ([n_tokens][n_kv_heads*head_dim] FP32, host)
+ * for one layer at positions [pos, pos+n_tokens); values are rounded to the pool dtype. */
+int juno_seq_append_kv(juno_seq *s, int32_t layer, int32_t pos, int32_t n_tokens, const float *k_host,
+                       const float *v_host);
+/* out[i][n_heads*head_dim] = gqa(q[i], K_i, V_i, len_i) for n sequences at one layer
+ * (len_i = current length of seqs[i]); host in, host out. */
+int juno_attn_decode(juno_ctx *ctx, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs,
+                     int32_t n_heads, const float *q_host, float *out_host);
+
+/* ── forward-pass operator (boundaries B and C) ───────────────────────────────
+ * juno_model_* replaces the device half of LlamaTransformerHandler
+ * (ForwardPassHandler.java:33-70); juno_forward with n sequences is
+ * InferencePipeline.forwardBatch (InferencePipeline.java:62-69). */
+typedef struct juno_model_cfg {
+    int32_t struct_size;   /* sizeof(juno_model_cfg), for forward compatibility */
+    int32_t hidden;        /* <arch>.embedding_length   (LlamaConfig.java:58-91) */
+    int32_t n_layers;      /* <arch>.block_count */
+    int32_t n_heads;       /* <arch>.attention.head_count */
+    int32_t n_kv_heads;    /* <arch>.attention.head_count_kv */
+    int32_t inter;         /* <arch>.feed_forward_length */
+    int32_t vocab;
+    float rms_eps;
+    float rope_theta;
+    int32_t max_batch;     /* most sequences per juno_forward call */
+    int32_t max_seqs;      /* most live sequences */
+    int32_t max_ctx;       /* most positions per sequence (the reference caps at 2048) */
+    int32_t kv_dtype;      /* 0 = FP16 pages, 1 = FP32 pages */
+    int32_t tp_rank;       /* TensorShardContext.tensorRank  (TensorShardContext.java:41-100) */
+    int32_t tp_world;      /* TensorShardContext.tensorWorldSize; 1 = single GPU */
+    uint8_t nccl_id[128];  /* ncclUniqueId bytes shared by all ranks when tp_world > 1 */
+} juno_model_cfg;
+
+/* tensor kinds, named after the GGUF tensors of LlamaTransformerHandler.java:238-275 */
+#define JUNO_T_TOKEN_EMBD 0
+#define JUNO_T_OUTPUT_NORM 1
+#define JUNO_T_OUTPUT 2
+#define JUNO_T_ATTN_NORM 3
+#define JUNO_T_FFN_NORM 4
+#define JUNO_T_ATTN_Q 5
+#define JUNO_T_ATTN_K 6
+#define JUNO_T_ATTN_V 7
+#define JUNO_T_ATTN_OUT 8
+#define JUNO_T_FFN_GATE 9
+#define JUNO_T_FFN_UP 10
+#define JUNO_T_FFN_DOWN 11
+
+int juno_model_create(juno_ctx *ctx, const juno_model_cfg *cfg, juno_model **out);
+/* Hands one FULL (unsharded) tensor to the model; with tp_world > 1 the library keeps only
+ * this rank's slice (column-parallel Q/K/V/gate/up by head and FFN rows, row-parallel
+ * O/down by whole super-blocks, vocab-parallel output).  layer is ignored for the three
+ * global tensors.  Omitting JUNO_T_OUTPUT ties the output projection to token_embd
+ * (LlamaTransformerHandler.java:463-470). */
+int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void *blocks,
+                          int32_t ggml_type, int64_t rows, int64_t cols);
+int juno_model_finalize(juno_model *m);
+int juno_model_free(juno_model *m); /* releaseGpuResources (LlamaTransformerHandler.java:424-448) */
+int juno_model_seq_create(juno_model *m, juno_seq **out);
+
+/* One decode step for n sequences: token_ids[i] is fed at positions[i] (only the last token
+ * of a request is used, LlamaTransformerHandler.java:653-655).  logits_host ([n][vocab]) and
+ * argmax_out ([n], first maximum = SampleStep.java:51-58) may each be NULL. */
+int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *token_ids,
+                 const int32_t *positions, float *logits_host, int32_t *argmax_out);
+/* `steps` greedy steps kept on the device: step 0 feeds first_tokens at positions, step s>0
+ * feeds the token picked at step s-1 at positions+s.  out_ids is [steps][n]. */
+int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *first_tokens,
+                       const int32_t *positions, int32_t steps, int32_t *out_ids);
+/* Residual stream after the last layer for the most recent juno_forward ([n][hidden]). */
+int juno_model_last_hidden(juno_model *m, int32_t n, float *hidden_host);
+
+/* ── counters: what a host needs to emit juno.MatVec / juno.ForwardPass events
+ *    (MatVecEvent.java:41-72, ForwardPassEvent.java:50-75). */
+typedef struct juno_counters {
+    int64_t kernel_launches; /* kernels of this library launched (graph replays count their nodes) */
+    int64_t gemv_calls;
+    int64_t forward_calls;
+    int64_t h2d_bytes;
+    int64_t d2h_bytes;
+} juno_counters;
+int juno_ctx_counters(juno_ctx *ctx, juno_counters *out, int32_t reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JUNO_B200_H */

@@ -1,0 +1,100 @@
+// Shared host-side plumbing of the engine: status codes, thread-local error text,
+// the context object and launch bookkeeping.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/juno_b200.h"
+
+namespace juno {
+
+void set_error(const char *fmt, ...);
+const char *get_error();
+
+#define JUNO_CUDA_TRY(expr)                                                                   \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess) {                                                              \
+            ::juno::set_error("%s failed: rc=%d (%s) at %s:%d", #expr, (int)_e,               \
+                              cudaGetErrorString(_e), __FILE__, __LINE__);                    \
+            return (_e == cudaErrorMemoryAllocation) ? JUNO_ERR_OOM : JUNO_ERR_CUDA;          \
+        }                                                                                     \
+    } while (0)
+
+#define JUNO_TRY(expr)          \
+    do {                        \
+        int _rc = (expr);       \
+        if (_rc != JUNO_OK)     \
+            return _rc;         \
+    } while (0)
+
+#define JUNO_REQUIRE(cond, ...)            \
+    do {                                   \
+        if (!(cond)) {                     \
+            ::juno::set_error(__VA_ARGS__); \
+            return JUNO_ERR_INVALID_ARG;   \
+        }                                  \
+    } while (0)
+
+constexpr uint32_t kMagicCtx = 0x4A435458;    // "JCTX"
+constexpr uint32_t kMagicQmat = 0x4A514D54;   // "JQMT"
+constexpr uint32_t kMagicModel = 0x4A4D444C;  // "JMDL"
+constexpr uint32_t kMagicSeq = 0x4A534551;    // "JSEQ"
+constexpr uint32_t kMagicPool = 0x4A4B5650;   // "JKVP"
+constexpr uint32_t kMagicDead = 0xDEADDEAD;
+
+// Scratch used by split-K reductions of the GEMV kernels (partials + arrival counters).
+struct GemvScratch {
+    float *partial = nullptr;
+    size_t partial_bytes = 0;
+    unsigned *counters = nullptr;
+    size_t n_counters = 0;
+};
+
+}  // namespace juno
+
+struct juno_ctx {
+    uint32_t magic;
+    int device;
+    int sm_count;
+    size_t smem_optin;
+    cudaStream_t stream;
+    std::recursive_mutex mu;
+    juno::GemvScratch gemv_scratch;
+    // staging buffers for the host-in/host-out entry points
+    float *stage_x = nullptr, *stage_y = nullptr;
+    size_t stage_x_bytes = 0, stage_y_bytes = 0;
+    void *pinned = nullptr;
+    size_t pinned_bytes = 0;
+    std::atomic<int64_t> kernel_launches{0}, gemv_calls{0}, forward_calls{0}, h2d_bytes{0}, d2h_bytes{0};
+};
+
+namespace juno {
+
+inline bool ctx_ok(juno_ctx *c) { return c && c->magic == kMagicCtx; }
+int ctx_check(juno_ctx *c);
+// Grows a device buffer (never shrinks). Returns JUNO_OK / JUNO_ERR_OOM.
+int ensure_device(void **ptr, size_t *cur, size_t want);
+int ensure_pinned(juno_ctx *c, size_t want);
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev)
+            cudaSetDevice(dev);
+        else
+            prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0)
+            cudaSetDevice(prev);
+    }
+};
+
+}  // namespace juno

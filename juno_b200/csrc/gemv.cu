@@ -1,0 +1,1099 @@
+// Fused dequant-GEMV for GGUF Q4_K / Q6_K / Q8_0 weights, batched over decode sequences.
+//
+// y[b][r] = sum_c w(r,c) * x[b][c] with w dequantised on the fly exactly as
+// LlamaTransformerHandler.matVecQ4Kraw/Q6Kraw/Q8_0raw do (LlamaTransformerHandler.java:1428-1508,
+// 1587-1638), but accumulated in a different order (FP32 throughout).
+//
+// Data flow per warp: 128-bit coalesced loads of one 16x256 tile straight from HBM into registers
+// (layout.cuh), 4/6/8-bit fields unpacked in registers into exact small-integer bf16 pairs, one
+// mma.sync.m16n8k16 per 16 columns against the activation held in shared memory as three bf16
+// limbs (x = hi+mid+lo exactly, so the products are exact FP32 terms), the per-sub-block scale
+// applied to the FP32 accumulator fragment, and the Q4_K "min" term handled the same way with an
+// m16n8k8 MMA of the 6-bit mins against per-sub-block sums of x.  Tensor cores are used here as an
+// exact integer-times-float dot-product unit; the kernel is bound by HBM, not by the tensor pipe.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "gemv.cuh"
+#include "layout.cuh"
+
+namespace juno {
+
+// ───────────────────────────── device helpers ─────────────────────────────────────────────
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
+
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t v, uint32_t c) {
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&v);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&c);
+    __nv_bfloat162 r = __hsub2(a, b);
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+
+__device__ __forceinline__ float f16bits_to_f32(uint32_t bits) {
+    return __half2float(__ushort_as_half((unsigned short)(bits & 0xFFFFu)));
+}
+
+constexpr uint32_t kBf128 = 0x43004300u;  // (128, 128)
+constexpr uint32_t kBf160 = 0x43204320u;  // (160, 160)
+constexpr uint32_t kBf384 = 0x43C043C0u;  // (384, 384)
+
+// Splits v into three bf16 limbs with hi + mid + lo == v.
+__device__ __forceinline__ void split3(float v, unsigned short &hi, unsigned short &mid, unsigned short &lo) {
+    __nv_bfloat16 h = __float2bfloat16_rn(v);
+    float r1 = v - __bfloat162float(h);
+    __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    float r2 = r1 - __bfloat162float(m);
+    __nv_bfloat16 l = __float2bfloat16_rn(r2);
+    hi = __bfloat16_as_ushort(h);
+    mid = __bfloat16_as_ushort(m);
+    lo = __bfloat16_as_ushort(l);
+}
+
+// SiLU as LlamaTransformerHandler.silu (:1733-1735): x / (1f + (float) Math.exp(-x)).
+__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.f, (float)exp((double)(-x)))); }
+
+// ───────────────────────────── kernel parameters ──────────────────────────────────────────
+struct GemvParams {
+    const uint8_t *w[3];
+    float *out[3];
+    int rows[3];
+    int rt_begin[4];  // cumulative row-tile starts, rt_begin[nseg] = total
+    int nseg;
+    int K, nb, batch, ncols;
+    int kw, tiles_per_task, ntasks;
+    int ld_out;
+    int pro;
+    const float *x;
+    int ldx;
+    const float *x_add, *normw, *up;
+    float *x_out;
+    float eps;
+    float *partial;       // [kw][batch][rows_pad_total]
+    unsigned *counters;   // [total row tiles]
+    int rows_pad_total;
+};
+
+template <int TYPE>
+struct TileRegs;
+template <>
+struct TileRegs<12> {
+    uint4 h0, h1, q[4];
+};
+template <>
+struct TileRegs<14> {
+    uint4 ql[4], qh[2];
+    uint32_t sc0, sc1;
+    uint32_t d01;
+};
+template <>
+struct TileRegs<8> {
+    uint4 q[8], d0, d1;
+};
+
+template <int TYPE>
+__device__ __forceinline__ void load_tile(TileRegs<TYPE> &r, const uint8_t *tile, int lane);
+
+template <>
+__device__ __forceinline__ void load_tile<12>(TileRegs<12> &r, const uint8_t *tile, int lane) {
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
+    int r8 = lane >> 2;
+    r.h0 = ld_stream(t4 + r8);
+    r.h1 = ld_stream(t4 + r8 + 8);
+#pragma unroll
+    for (int g = 0; g < 4; g++) r.q[g] = ld_stream(t4 + 16 + g * 32 + lane);
+}
+template <>
+__device__ __forceinline__ void load_tile<14>(TileRegs<14> &r, const uint8_t *tile, int lane) {
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
+    int r8 = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int m = 0; m < 4; m++) r.ql[m] = ld_stream(t4 + m * 32 + lane);
+#pragma unroll
+    for (int p = 0; p < 2; p++) r.qh[p] = ld_stream(t4 + 128 + p * 32 + lane);
+    const uint32_t *sc = reinterpret_cast<const uint32_t *>(tile + 3072);
+    r.sc0 = __ldcs(sc + r8 * 4 + c);
+    r.sc1 = __ldcs(sc + (r8 + 8) * 4 + c);
+    const unsigned short *d = reinterpret_cast<const unsigned short *>(tile + 3328);
+    r.d01 = (uint32_t)__ldcs(d + r8) | ((uint32_t)__ldcs(d + r8 + 8) << 16);
+}
+template <>
+__device__ __forceinline__ void load_tile<8>(TileRegs<8> &r, const uint8_t *tile, int lane) {
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
+    int r8 = lane >> 2;
+#pragma unroll
+    for (int j = 0; j < 8; j++) r.q[j] = ld_stream(t4 + j * 32 + lane);
+    r.d0 = ld_stream(t4 + 256 + r8);
+    r.d1 = ld_stream(t4 + 256 + r8 + 8);
+}
+
+// B-operand fetch for s16 sub-block `s16` and n-tile `nt`: 8 bytes = (x[4c],x[4c+2]) (x[4c+1],x[4c+3]).
+__device__ __forceinline__ uint2 ld_xb(const unsigned short *xb, int s16, int ncols, int col, int c) {
+    if (col < ncols) return *reinterpret_cast<const uint2 *>(xb + ((s16 * ncols + col) * 4 + c) * 4);
+    return make_uint2(0u, 0u);
+}
+
+// ── Q4_K tile ────────────────────────────────────────────────────────────────────────────
+__device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t &lo_a, uint32_t &lo_b, uint32_t &hi_a, uint32_t &hi_b) {
+    const uint32_t M = 0x000F000Fu;
+    lo_a = bf2_sub((w & M) | kBf128, kBf128);          // (byte0.lo, byte2.lo)
+    hi_a = bf2_sub(((w >> 4) & M) | kBf128, kBf128);   // (byte0.hi, byte2.hi)
+    lo_b = bf2_sub(((w >> 8) & M) | kBf128, kBf128);   // (byte1.lo, byte3.lo)
+    hi_b = bf2_sub(((w >> 12) & M) | kBf128, kBf128);  // (byte1.hi, byte3.hi)
+}
+
+// Decodes one row's 16-byte Q4_K header for the lane's two sub-blocks 2c, 2c+1.
+__device__ __forceinline__ void q4_header(const uint4 &h, int c, float &sc0, float &sc1, uint32_t &mins_bf2, float &dmin) {
+    float d = f16bits_to_f32(h.x);
+    dmin = f16bits_to_f32(h.x >> 16);
+    uint32_t sA = h.y & 0x3f3f3f3fu, mA = h.z & 0x3f3f3f3fu;
+    uint32_t sB = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
+    uint32_t mB = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
+    uint32_t S = (c < 2) ? sA : sB, Mn = (c < 2) ? mA : mB;
+    int sh = (c & 1) * 16;
+    sc0 = __fmul_rn(d, (float)((S >> sh) & 0xFFu));
+    sc1 = __fmul_rn(d, (float)((S >> (sh + 8)) & 0xFFu));
+    uint32_t mp = (Mn >> sh) & 0xFFFFu;                        // bytes (m0, m1)
+    mins_bf2 = bf2_sub(__byte_perm(mp, 0x43434343u, 0x4140), kBf128);  // bf16x2 (m0, m1)
+}
+
+template <int NT>
+__device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, const unsigned short *xb,
+                                             const uint32_t *xs32, int ncols, int lane, float (&acc)[NT][4],
+                                             float (&macc)[NT][4]) {
+    const int r8 = lane >> 2, c = lane & 3;
+    float s_r[2], s_q[2], dmin_r, dmin_q;
+    uint32_t mins_r, mins_q;
+    q4_header(R.h0, c, s_r[0], s_r[1], mins_r, dmin_r);
+    q4_header(R.h1, c, s_q[0], s_q[1], mins_q, dmin_q);
+    const int s16base = sb * 16;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        uint32_t la_x, lb_x, ha_x, hb_x, la_y, lb_y, ha_y, hb_y, la_z, lb_z, ha_z, hb_z, la_w, lb_w, ha_w, hb_w;
+        q4_unpack(R.q[g].x, la_x, lb_x, ha_x, hb_x);
+        q4_unpack(R.q[g].y, la_y, lb_y, ha_y, hb_y);
+        q4_unpack(R.q[g].z, la_z, lb_z, ha_z, hb_z);
+        q4_unpack(R.q[g].w, la_w, lb_w, ha_w, hb_w);
+        const int src = (lane & ~3) | g;  // quad lane g owns sub-blocks 2g and 2g+1
+        float sr0 = __shfl_sync(0xffffffffu, s_r[0], src), sr1 = __shfl_sync(0xffffffffu, s_r[1], src);
+        float sq0 = __shfl_sync(0xffffffffu, s_q[0], src), sq1 = __shfl_sync(0xffffffffu, s_q[1], src);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int col = nt * 8 + r8;
+            float ct[4] = {0.f, 0.f, 0.f, 0.f};
+            uint2 b = ld_xb(xb, s16base + 4 * g + 0, ncols, col, c);
+            mma16816(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
+            b = ld_xb(xb, s16base + 4 * g + 1, ncols, col, c);
+            mma16816(ct, la_y, la_w, lb_y, lb_w, b.x, b.y);
+            acc[nt][0] = fmaf(sr0, ct[0], acc[nt][0]);
+            acc[nt][1] = fmaf(sr0, ct[1], acc[nt][1]);
+            acc[nt][2] = fmaf(sq0, ct[2], acc[nt][2]);
+            acc[nt][3] = fmaf(sq0, ct[3], acc[nt][3]);
+            float ch[4] = {0.f, 0.f, 0.f, 0.f};
+            b = ld_xb(xb, s16base + 4 * g + 2, ncols, col, c);
+            mma16816(ch, ha_x, ha_z, hb_x, hb_z, b.x, b.y);
+            b = ld_xb(xb, s16base + 4 * g + 3, ncols, col, c);
+            mma16816(ch, ha_y, ha_w, hb_y, hb_w, b.x, b.y);
+            acc[nt][0] = fmaf(sr1, ch[0], acc[nt][0]);
+            acc[nt][1] = fmaf(sr1, ch[1], acc[nt][1]);
+            acc[nt][2] = fmaf(sq1, ch[2], acc[nt][2]);
+            acc[nt][3] = fmaf(sq1, ch[3], acc[nt][3]);
+        }
+    }
+    // min term: sum_j (dmin*m_j) * sum_{c in sub-block j} x[c]
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int col = nt * 8 + r8;
+        uint32_t bm = (col < ncols) ? xs32[(sb * ncols + col) * 4 + c] : 0u;
+        float cm[4] = {0.f, 0.f, 0.f, 0.f};
+        mma1688(cm, mins_r, mins_q, bm);
+        macc[nt][0] = fmaf(dmin_r, cm[0], macc[nt][0]);
+        macc[nt][1] = fmaf(dmin_r, cm[1], macc[nt][1]);
+        macc[nt][2] = fmaf(dmin_q, cm[2], macc[nt][2]);
+        macc[nt][3] = fmaf(dmin_q, cm[3], macc[nt][3]);
+    }
+}
+
+// ── Q6_K tile ────────────────────────────────────────────────────────────────────────────
+__device__ __forceinline__ float i8_to_f32(uint32_t w, int k) { return (float)(int)(signed char)((w >> (8 * k)) & 0xFFu); }
+
+template <int NT>
+__device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, const unsigned short *xb,
+                                             const uint32_t * /*xs32*/, int ncols, int lane, float (&acc)[NT][4],
+                                             float (& /*macc*/)[NT][4]) {
+    const int r8 = lane >> 2, c = lane & 3;
+    const float d_r = f16bits_to_f32(R.d01), d_q = f16bits_to_f32(R.d01 >> 16);
+    float s_r[4], s_q[4];  // scales of sub-blocks 4c..4c+3 for rows r8 and r8+8
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        s_r[k] = __fmul_rn(d_r, i8_to_f32(R.sc0, k));
+        s_q[k] = __fmul_rn(d_q, i8_to_f32(R.sc1, k));
+    }
+    const int s16base = sb * 16;
+    const uint32_t NIB = 0x0F0F0F0Fu, HI = 0x30303030u;
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        const uint32_t WA_r = R.ql[m].x, WB_r = R.ql[m].y, WA_q = R.ql[m].z, WB_q = R.ql[m].w;
+        const uint4 hq = R.qh[m >> 1];
+        const uint32_t H_r = (m & 1) ? hq.y : hq.x, H_q = (m & 1) ? hq.w : hq.z;
+        uint32_t V_r[4], V_q[4];  // four 6-bit values per word, for sub-blocks 4m+0..3
+        V_r[0] = (WA_r & NIB) | (H_r & HI);
+        V_r[1] = ((WA_r >> 4) & NIB) | ((H_r >> 2) & HI);
+        V_r[2] = (WB_r & NIB) | ((H_r << 2) & HI);
+        V_r[3] = ((WB_r >> 4) & NIB) | ((H_r << 4) & HI);
+        V_q[0] = (WA_q & NIB) | (H_q & HI);
+        V_q[1] = ((WA_q >> 4) & NIB) | ((H_q >> 2) & HI);
+        V_q[2] = (WB_q & NIB) | ((H_q << 2) & HI);
+        V_q[3] = ((WB_q >> 4) & NIB) | ((H_q << 4) & HI);
+        const int src = (lane & ~3) | m;  // quad lane m owns the scales of sub-blocks 4m..4m+3
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float sr = __shfl_sync(0xffffffffu, s_r[k], src), sq = __shfl_sync(0xffffffffu, s_q[k], src);
+            const uint32_t a0 = bf2_sub(__byte_perm(V_r[k], 0x43434343u, 0x4140), kBf160);
+            const uint32_t a2 = bf2_sub(__byte_perm(V_r[k], 0x43434343u, 0x4342), kBf160);
+            const uint32_t a1 = bf2_sub(__byte_perm(V_q[k], 0x43434343u, 0x4140), kBf160);
+            const uint32_t a3 = bf2_sub(__byte_perm(V_q[k], 0x43434343u, 0x4342), kBf160);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int col = nt * 8 + r8;
+                float ct[4] = {0.f, 0.f, 0.f, 0.f};
+                uint2 b = ld_xb(xb, s16base + 4 * m + k, ncols, col, c);
+                mma16816(ct, a0, a1, a2, a3, b.x, b.y);
+                acc[nt][0] = fmaf(sr, ct[0], acc[nt][0]);
+                acc[nt][1] = fmaf(sr, ct[1], acc[nt][1]);
+                acc[nt][2] = fmaf(sq, ct[2], acc[nt][2]);
+                acc[nt][3] = fmaf(sq, ct[3], acc[nt][3]);
+            }
+        }
+    }
+}
+
+// ── Q8_0 tile: int8 q = 16*h + l, both nibble planes exact in bf16 ────────────────────────
+__device__ __forceinline__ void q8_unpack(uint32_t w, uint32_t &l_a, uint32_t &l_b, uint32_t &h_a, uint32_t &h_b) {
+    const uint32_t M = 0x000F000Fu, MH = 0x00780078u;
+    l_a = bf2_sub((w & M) | kBf128, kBf128);              // (b0&15, b2&15)
+    l_b = bf2_sub(((w >> 8) & M) | kBf128, kBf128);       // (b1&15, b3&15)
+    h_a = bf2_sub(((w >> 1) & MH) ^ kBf384, kBf384);      // 16*(b0>>4), 16*(b2>>4)  (arithmetic >>)
+    h_b = bf2_sub(((w >> 9) & MH) ^ kBf384, kBf384);      // 16*(b1>>4), 16*(b3>>4)
+}
+
+template <int NT>
+__device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const unsigned short *xb,
+                                             const uint32_t * /*xs32*/, int ncols, int lane, float (&acc)[NT][4],
+                                             float (& /*macc*/)[NT][4]) {
+    const int r8 = lane >> 2, c = lane & 3;
+    const int s16base = sb * 16;
+    const uint32_t dr[4] = {R.d0.x, R.d0.y, R.d0.z, R.d0.w}, dq[4] = {R.d1.x, R.d1.y, R.d1.z, R.d1.w};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float d_r = f16bits_to_f32(dr[j >> 1] >> ((j & 1) * 16)), d_q = f16bits_to_f32(dq[j >> 1] >> ((j & 1) * 16));
+        uint32_t la_x, lb_x, ha_x, hb_x, la_y, lb_y, ha_y, hb_y, la_z, lb_z, ha_z, hb_z, la_w, lb_w, ha_w, hb_w;
+        q8_unpack(R.q[j].x, la_x, lb_x, ha_x, hb_x);
+        q8_unpack(R.q[j].y, la_y, lb_y, ha_y, hb_y);
+        q8_unpack(R.q[j].z, la_z, lb_z, ha_z, hb_z);
+        q8_unpack(R.q[j].w, la_w, lb_w, ha_w, hb_w);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int col = nt * 8 + r8;
+            float ct[4] = {0.f, 0.f, 0.f, 0.f};
+            uint2 b = ld_xb(xb, s16base + 2 * j, ncols, col, c);
+            mma16816(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
+            mma16816(ct, ha_x, ha_z, hb_x, hb_z, b.x, b.y);
+            b = ld_xb(xb, s16base + 2 * j + 1, ncols, col, c);
+            mma16816(ct, la_y, la_w, lb_y, lb_w, b.x, b.y);
+            mma16816(ct, ha_y, ha_w, hb_y, hb_w, b.x, b.y);
+            acc[nt][0] = fmaf(d_r, ct[0], acc[nt][0]);
+            acc[nt][1] = fmaf(d_r, ct[1], acc[nt][1]);
+            acc[nt][2] = fmaf(d_q, ct[2], acc[nt][2]);
+            acc[nt][3] = fmaf(d_q, ct[3], acc[nt][3]);
+        }
+    }
+}
+
+// ───────────────────────────── the kernel ─────────────────────────────────────────────────
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <int TYPE>
+__device__ __forceinline__ const uint8_t *tile_ptr(const GemvParams &p, int task, int tile_in_task, int &R, int &kj,
+                                                   int &sb) {
+    R = task / p.kw;
+    kj = task - R * p.kw;
+    sb = kj * p.tiles_per_task + tile_in_task;
+    int s = 0;
+    if (p.nseg > 1 && R >= p.rt_begin[1]) s = 1;
+    if (p.nseg > 2 && R >= p.rt_begin[2]) s = 2;
+    return p.w[s] + ((size_t)(R - p.rt_begin[s]) * p.nb + sb) * (size_t)tile_bytes(TYPE);
+}
+
+template <int TYPE, int NT>
+__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = p.K, ncols = p.ncols, batch = p.batch;
+    unsigned short *xb = reinterpret_cast<unsigned short *>(smem);                 // K*ncols bf16
+    unsigned short *xs = xb + (size_t)K * ncols;                                   // (K/32)*ncols bf16 (padded to 8 B)
+    size_t xs_elems = (((size_t)(K / 32) * ncols) + 7) & ~(size_t)7;
+    float *cs = reinterpret_cast<float *>(xs + xs_elems);                          // kWarps * 16 * 8NT
+    float *red = cs + kWarps * 16 * 8 * NT;                                        // batch * kWarps
+
+    // work assignment: task = (row tile, K chunk); warp gw takes tasks gw, gw+W, ...
+    const int W = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+    const int my_tasks = (gw < p.ntasks) ? (p.ntasks - gw + W - 1) / W : 0;
+    const int total_it = my_tasks * p.tiles_per_task;
+
+    // Issue the first tile's loads before touching x: the weights do not depend on the producer of x.
+    TileRegs<TYPE> cur;
+    int R = 0, kj = 0, sb = 0;
+    int task = gw, tin = 0;
+    if (total_it > 0) load_tile<TYPE>(cur, tile_ptr<TYPE>(p, task, 0, R, kj, sb), lane);
+
+    // ── stage x: prologue transform, three bf16 limbs in MMA feed order, sub-block sums ──
+    if (p.pro == PRO_RMSNORM) {
+        for (int b = 0; b < batch; b++) {
+            float part = 0.f;
+            for (int i = tid; i < K; i += kThreads) {
+                float r = p.x[(size_t)b * p.ldx + i];
+                if (p.x_add) r = __fadd_rn(r, p.x_add[(size_t)b * p.ldx + i]);
+                part = fmaf(r, r, part);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0) red[b * kWarps + warp] = part;
+        }
+        __syncthreads();
+    }
+    for (int b = 0; b < batch; b++) {
+        float scale = 1.f;
+        if (p.pro == PRO_RMSNORM) {
+            float ss = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < kWarps; w8++) ss += red[b * kWarps + w8];
+            // rmsNorm (:818-828): 1f / (float) Math.sqrt(ss / n + eps)
+            scale = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(ss, (float)K), p.eps)));
+        }
+        for (int i = tid; i < K; i += kThreads) {
+            float v;
+            const size_t gi = (size_t)b * p.ldx + i;
+            if (p.pro == PRO_RMSNORM) {
+                float r = p.x[gi];
+                if (p.x_add) r = __fadd_rn(r, p.x_add[gi]);
+                if (p.x_out && blockIdx.x == 0) p.x_out[gi] = r;
+                v = __fmul_rn(__fmul_rn(p.normw[i], r), scale);
+            } else if (p.pro == PRO_SILU) {
+                v = __fmul_rn(silu_ref(p.x[gi]), p.up[gi]);
+            } else {
+                v = p.x[gi];
+            }
+            unsigned short hi, mid, lo;
+            split3(v, hi, mid, lo);
+            const int s16 = i >> 4, c = (i >> 2) & 3, pos = feed_pos(i & 3);
+            unsigned short *dst = xb + ((size_t)(s16 * ncols + 3 * b) * 4 + c) * 4 + pos;
+            dst[0] = hi;
+            dst[16] = mid;  // next column: +4*4 elements
+            dst[32] = lo;
+            if (TYPE == 12) {
+                float s = v;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane < 3) {
+                    unsigned short l3[3];
+                    split3(s, l3[0], l3[1], l3[2]);
+                    xs[xs_index(i >> 5, ncols, 3 * b + lane)] = l3[lane];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const uint32_t *xs32 = reinterpret_cast<const uint32_t *>(xs);
+    float *mycs = cs + warp * 16 * 8 * NT;
+
+    float acc[NT][4], macc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[nt][i] = macc[nt][i] = 0.f;
+
+    for (int it = 0; it < total_it; it++) {
+        // prefetch the next tile of this warp's stream
+        TileRegs<TYPE> nxt;
+        int nR = R, nkj = kj, nsb = sb, ntask = task, ntin = tin + 1;
+        if (ntin == p.tiles_per_task) {
+            ntin = 0;
+            ntask = task + W;
+        }
+        if (it + 1 < total_it) load_tile<TYPE>(nxt, tile_ptr<TYPE>(p, ntask, ntin, nR, nkj, nsb), lane);
+
+        compute_tile<NT>(cur, sb, xb, xs32, ncols, lane, acc, macc);
+
+        if (tin == p.tiles_per_task - 1) {
+            // ── flush this task: fragment -> per-warp smem tile -> limb sums ──
+            const int r8 = lane >> 2, c = lane & 3;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float *row0 = mycs + r8 * (8 * NT) + nt * 8 + 2 * c;
+                float *row1 = mycs + (r8 + 8) * (8 * NT) + nt * 8 + 2 * c;
+                row0[0] = acc[nt][0] - macc[nt][0];
+                row0[1] = acc[nt][1] - macc[nt][1];
+                row1[0] = acc[nt][2] - macc[nt][2];
+                row1[1] = acc[nt][3] - macc[nt][3];
+                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+                macc[nt][0] = macc[nt][1] = macc[nt][2] = macc[nt][3] = 0.f;
+            }
+            __syncwarp();
+            int s = 0;
+            if (p.nseg > 1 && R >= p.rt_begin[1]) s = 1;
+            if (p.nseg > 2 && R >= p.rt_begin[2]) s = 2;
+            const int row_base = (R - p.rt_begin[s]) * 16;
+            if (p.kw == 1) {
+                for (int idx = lane; idx < 16 * batch; idx += 32) {
+                    const int row = idx & 15, b = idx >> 4;
+                    const float *cr = mycs + row * (8 * NT) + 3 * b;
+                    float v = (cr[2] + cr[1]) + cr[0];
+                    if (row_base + row < p.rows[s]) p.out[s][(size_t)b * p.ld_out + row_base + row] = v;
+                }
+            } else {
+                for (int idx = lane; idx < 16 * batch; idx += 32) {
+                    const int row = idx & 15, b = idx >> 4;
+                    const float *cr = mycs + row * (8 * NT) + 3 * b;
+                    float v = (cr[2] + cr[1]) + cr[0];
+                    __stcg(p.partial + ((size_t)kj * batch + b) * p.rows_pad_total + R * 16 + row, v);
+                }
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + R, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == (unsigned)(p.kw - 1)) {  // last K chunk to arrive reduces in fixed order
+                    __threadfence();
+                    for (int idx = lane; idx < 16 * batch; idx += 32) {
+                        const int row = idx & 15, b = idx >> 4;
+                        float v = 0.f;
+                        for (int k2 = 0; k2 < p.kw; k2++)
+                            v += __ldcg(p.partial + ((size_t)k2 * batch + b) * p.rows_pad_total + R * 16 + row);
+                        if (row_base + row < p.rows[s]) p.out[s][(size_t)b * p.ld_out + row_base + row] = v;
+                    }
+                    if (lane == 0) p.counters[R] = 0u;  // ready for the next launch
+                }
+            }
+            __syncwarp();
+        }
+        cur = nxt;
+        R = nR;
+        kj = nkj;
+        sb = nsb;
+        task = ntask;
+        tin = ntin;
+    }
+}
+
+// ───────────────────────────── host: launch ───────────────────────────────────────────────
+static int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+static size_t gemv_smem_bytes(int K, int ncols, int NT, int batch) {
+    size_t xb = (size_t)K * ncols * 2;
+    size_t xs = ((((size_t)(K / 32) * ncols) + 7) & ~(size_t)7) * 2;
+    size_t cs = (size_t)kWarps * 16 * 8 * NT * 4;
+    size_t red = (size_t)batch * kWarps * 4;
+    return xb + xs + cs + red;
+}
+
+template <int TYPE, int NT>
+static int launch_inst(juno_ctx *ctx, const GemvParams &p, int grid, size_t smem, cudaStream_t st) {
+    static std::mutex mu;
+    static size_t configured[16] = {0};  // per device
+    {
+        std::lock_guard<std::mutex> g(mu);
+        int dev = ctx->device & 15;
+        if (smem > 48 * 1024 && smem > configured[dev]) {
+            JUNO_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<TYPE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)ctx->smem_optin));
+            configured[dev] = ctx->smem_optin;
+        }
+    }
+    gemv_kernel<TYPE, NT><<<grid, kThreads, smem, st>>>(p);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+template <int TYPE>
+static int launch_type(juno_ctx *ctx, const GemvParams &p, int NT, int grid, size_t smem, cudaStream_t st) {
+    switch (NT) {
+    case 1: return launch_inst<TYPE, 1>(ctx, p, grid, smem, st);
+    case 2: return launch_inst<TYPE, 2>(ctx, p, grid, smem, st);
+    case 3: return launch_inst<TYPE, 3>(ctx, p, grid, smem, st);
+    case 4: return launch_inst<TYPE, 4>(ctx, p, grid, smem, st);
+    case 5: return launch_inst<TYPE, 5>(ctx, p, grid, smem, st);
+    case 6: return launch_inst<TYPE, 6>(ctx, p, grid, smem, st);
+    default: break;
+    }
+    set_error("gemv: unsupported column-tile count %d", NT);
+    return JUNO_ERR_UNSUPPORTED;
+}
+
+constexpr int kMaxBatchChunk = 16;  // 48 limb columns = 6 n-tiles
+
+int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
+    JUNO_REQUIRE(a.nseg >= 1 && a.nseg <= 3, "gemv: nseg %d", a.nseg);
+    JUNO_REQUIRE(a.type == 12 || a.type == 14 || a.type == 8, "gemv: type %d has no tiled kernel", a.type);
+    JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0, "gemv: K=%d must be a multiple of 256", a.K);
+    JUNO_REQUIRE(a.batch >= 1, "gemv: batch %d", a.batch);
+    const int nb = a.K / 256;
+    int total_rt = 0;
+    for (int s = 0; s < a.nseg; s++) total_rt += a.seg[s].row_tiles;
+
+    // batch chunk: limb columns must fit shared memory and 6 n-tiles
+    const size_t smem_cap = ctx->smem_optin;
+    int bc = std::min(a.batch, kMaxBatchChunk);
+    while (bc > 1 && gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) > smem_cap) bc--;
+    JUNO_REQUIRE(gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) <= smem_cap, "gemv: K=%d does not fit shared memory",
+                 a.K);
+
+    // K split: enough tasks to give every resident warp work, using divisors of nb only
+    const int ctas_per_sm = (gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) * 2 <= smem_cap) ? 2 : 1;
+    const int max_grid = ctx->sm_count * ctas_per_sm;
+    const int want_tasks = max_grid * kWarps * 2;
+    int kw = 1;
+    for (int d = 1; d <= nb; d++) {
+        if (nb % d) continue;
+        kw = d;
+        if ((long long)total_rt * d >= want_tasks) break;
+    }
+    kw = env_int("JUNO_GEMV_KW", kw);
+    if (kw < 1 || nb % kw) kw = 1;
+    const int ntasks = total_rt * kw;
+    // grid: best balance of tasks over warps, preferring more CTAs
+    int grid = std::min(max_grid, (ntasks + kWarps - 1) / kWarps);
+    {
+        double best = -1;
+        int best_g = grid;
+        for (int g = grid; g >= std::min(grid, ctx->sm_count); g--) {
+            long long wps = (long long)g * kWarps;
+            long long rounds = (ntasks + wps - 1) / wps;
+            double eff = (double)ntasks / (double)(rounds * wps);
+            if (eff > best + 1e-9) {
+                best = eff;
+                best_g = g;
+            }
+        }
+        grid = best_g;
+    }
+    grid = env_int("JUNO_GEMV_GRID", grid);
+    if (grid < 1) grid = 1;
+
+    int rows_pad_total = total_rt * 16;
+    if (kw > 1) {
+        size_t need = (size_t)kw * bc * rows_pad_total * sizeof(float);
+        void *pp = ctx->gemv_scratch.partial;
+        JUNO_TRY(ensure_device(&pp, &ctx->gemv_scratch.partial_bytes, need));
+        ctx->gemv_scratch.partial = (float *)pp;
+        if ((size_t)total_rt > ctx->gemv_scratch.n_counters) {
+            void *cp = ctx->gemv_scratch.counters;
+            size_t curb = ctx->gemv_scratch.n_counters * sizeof(unsigned);
+            size_t wantb = (size_t)std::max(total_rt, 16384) * sizeof(unsigned);
+            JUNO_TRY(ensure_device(&cp, &curb, wantb));
+            ctx->gemv_scratch.counters = (unsigned *)cp;
+            ctx->gemv_scratch.n_counters = curb / sizeof(unsigned);
+            JUNO_CUDA_TRY(cudaMemsetAsync(cp, 0, curb, st));
+        }
+    }
+
+    for (int b0 = 0; b0 < a.batch; b0 += bc) {
+        const int nbatch = std::min(bc, a.batch - b0);
+        GemvParams p;
+        memset(&p, 0, sizeof(p));
+        int rt = 0;
+        for (int s = 0; s < a.nseg; s++) {
+            p.w[s] = a.seg[s].w;
+            p.out[s] = a.seg[s].out + (size_t)b0 * a.ld_out;
+            p.rows[s] = a.seg[s].rows;
+            p.rt_begin[s] = rt;
+            rt += a.seg[s].row_tiles;
+        }
+        for (int s = a.nseg; s < 4; s++) p.rt_begin[s] = rt;
+        p.nseg = a.nseg;
+        p.K = a.K;
+        p.nb = nb;
+        p.batch = nbatch;
+        p.ncols = 3 * nbatch;
+        p.kw = kw;
+        p.tiles_per_task = nb / kw;
+        p.ntasks = ntasks;
+        p.ld_out = a.ld_out;
+        p.pro = a.pro;
+        p.x = a.x + (size_t)b0 * a.ldx;
+        p.ldx = a.ldx;
+        p.x_add = a.x_add ? a.x_add + (size_t)b0 * a.ldx : nullptr;
+        p.normw = a.normw;
+        p.up = a.up ? a.up + (size_t)b0 * a.ldx : nullptr;
+        p.x_out = a.x_out ? a.x_out + (size_t)b0 * a.ldx : nullptr;
+        p.eps = a.eps;
+        p.partial = ctx->gemv_scratch.partial;
+        p.counters = ctx->gemv_scratch.counters;
+        p.rows_pad_total = rows_pad_total;
+        const int NT = (p.ncols + 7) / 8;
+        const size_t smem = gemv_smem_bytes(a.K, p.ncols, NT, nbatch);
+        int rc;
+        if (a.type == 12)
+            rc = launch_type<12>(ctx, p, NT, grid, smem, st);
+        else if (a.type == 14)
+            rc = launch_type<14>(ctx, p, NT, grid, smem, st);
+        else
+            rc = launch_type<8>(ctx, p, NT, grid, smem, st);
+        JUNO_TRY(rc);
+    }
+    return JUNO_OK;
+}
+
+// ───────────────────────────── repack (raw GGUF blocks -> tiles) ───────────────────────────
+// raw: device copy of rows [0,nrows) of the source tensor, row stride raw_row_bytes; the tile matrix covers
+// super-blocks [sb0, sb0+nsb) of each row.  One thread per 32-bit output word.
+__global__ void repack_q4k_kernel(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb0, int nsb, uint8_t *out) {
+    const size_t words_per_tile = kQ4KTileBytes / 4;
+    size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t ntiles = (size_t)((nrows + 15) / 16) * nsb;
+    if (gidx >= ntiles * words_per_tile) return;
+    size_t tile = gidx / words_per_tile;
+    int w = (int)(gidx - tile * words_per_tile);
+    int R = (int)(tile / nsb), b = (int)(tile - (size_t)R * nsb);
+    int row16, off;
+    q4k_word_src(w, row16, off);
+    int row = R * 16 + row16;
+    uint32_t v = 0;
+    if (row < nrows) {
+        const uint8_t *src = raw + (size_t)row * raw_row_bytes + (size_t)(sb0 + b) * 144 + off;
+        v = (uint32_t)src[0] | ((uint32_t)src[1] << 8) | ((uint32_t)src[2] << 16) | ((uint32_t)src[3] << 24);
+    }
+    reinterpret_cast<uint32_t *>(out)[gidx] = v;
+}
+
+__host__ __device__ inline uint32_t q6k_tile_word(const uint8_t *blk_row /* raw block of (row, sb) or null */, int w,
+                                                  int lane_c, bool ql_section, int mp, int k4) {
+    // Builds one ql word W[j] or qh word H[i] for lane column group c from a raw block.
+    (void)w;
+    uint32_t v = 0;
+    if (!blk_row) return 0;
+    if (ql_section) {
+        int j = 2 * mp + (k4 & 1);
+        for (int odd = 0; odd < 2; odd++)
+            for (int t = 0; t < 4; t++) {
+                int e = 16 * (2 * j + odd) + 4 * lane_c + t;
+                int nu = 2 * feed_pos(t) + odd;
+                v |= (uint32_t)(q6k_raw_u6(blk_row, e) & 15) << (4 * nu);
+            }
+    } else {
+        int i = 2 * mp + (k4 & 1);
+        for (int isB = 0; isB < 2; isB++) {
+            int j = 2 * i + isB;
+            for (int odd = 0; odd < 2; odd++)
+                for (int t = 0; t < 4; t++) {
+                    int e = 16 * (2 * j + odd) + 4 * lane_c + t;
+                    int nu = 2 * feed_pos(t) + odd;
+                    v |= (uint32_t)(q6k_raw_u6(blk_row, e) >> 4) << q6k_field_bit(isB, nu);
+                }
+        }
+    }
+    return v;
+}
+
+__host__ __device__ inline uint32_t q6k_out_word(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb_abs, int R,
+                                                 int w) {
+    // w: 32-bit word index inside the 3360-byte tile (0..839)
+    if (w < 768) {  // ql (512 words) then qh (256 words)
+        bool ql = w < 512;
+        int v = ql ? w : w - 512;
+        int mp = v >> 7, lane = (v >> 2) & 31, k4 = v & 3;
+        int row = R * 16 + (lane >> 2) + 8 * (k4 >> 1);
+        const uint8_t *blk = (row < nrows) ? raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 210 : nullptr;
+        return q6k_tile_word(blk, w, lane & 3, ql, mp, k4);
+    } else if (w < 832) {  // sc: 16 rows x 16 bytes
+        int v = w - 768, row16 = v >> 2, q = v & 3;
+        int row = R * 16 + row16;
+        if (row >= nrows) return 0;
+        const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 210 + 192 + q * 4;
+        return (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    } else {  // d: 16 rows x f16, two per word
+        int v = w - 832;
+        uint32_t outv = 0;
+        for (int h = 0; h < 2; h++) {
+            int row = R * 16 + 2 * v + h;
+            if (row < nrows) {
+                const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 210 + 208;
+                outv |= ((uint32_t)s[0] | ((uint32_t)s[1] << 8)) << (16 * h);
+            }
+        }
+        return outv;
+    }
+}
+
+__global__ void repack_q6k_kernel(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb0, int nsb, uint8_t *out) {
+    const size_t words_per_tile = kQ6KTileBytes / 4;
+    size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t ntiles = (size_t)((nrows + 15) / 16) * nsb;
+    if (gidx >= ntiles * words_per_tile) return;
+    size_t tile = gidx / words_per_tile;
+    int w = (int)(gidx - tile * words_per_tile);
+    int R = (int)(tile / nsb), b = (int)(tile - (size_t)R * nsb);
+    reinterpret_cast<uint32_t *>(out)[gidx] = q6k_out_word(raw, raw_row_bytes, nrows, sb0 + b, R, w);
+}
+
+__host__ __device__ inline uint32_t q80_out_word(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb_abs, int R,
+                                                 int w) {
+    if (w < 1024) {
+        int j = w >> 7, lane = (w >> 2) & 31, k4 = w & 3;
+        int row = R * 16 + (lane >> 2) + 8 * (k4 >> 1);
+        if (row >= nrows) return 0;
+        const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)(sb_abs * 8 + j) * 34 + 2 + 16 * (k4 & 1) + 4 * (lane & 3);
+        return (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    } else {  // d[row16][8] f16: 4 words per row
+        int v = w - 1024, row16 = v >> 2, q = v & 3;
+        int row = R * 16 + row16;
+        if (row >= nrows) return 0;
+        uint32_t outv = 0;
+        for (int h = 0; h < 2; h++) {
+            const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)(sb_abs * 8 + 2 * q + h) * 34;
+            outv |= ((uint32_t)s[0] | ((uint32_t)s[1] << 8)) << (16 * h);
+        }
+        return outv;
+    }
+}
+
+__global__ void repack_q80_kernel(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb0, int nsb, uint8_t *out) {
+    const size_t words_per_tile = kQ80TileBytes / 4;
+    size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t ntiles = (size_t)((nrows + 15) / 16) * nsb;
+    if (gidx >= ntiles * words_per_tile) return;
+    size_t tile = gidx / words_per_tile;
+    int w = (int)(gidx - tile * words_per_tile);
+    int R = (int)(tile / nsb), b = (int)(tile - (size_t)R * nsb);
+    reinterpret_cast<uint32_t *>(out)[gidx] = q80_out_word(raw, raw_row_bytes, nrows, sb0 + b, R, w);
+}
+
+// Host mirror of the repack, for layout tests that run without a GPU.
+extern "C" int juno_dbg_repack_host(int type, const uint8_t *raw, int64_t rows, int64_t cols, uint8_t *out) {
+    if (cols % 256 || rows < 1) return JUNO_ERR_INVALID_ARG;
+    int nsb = (int)(cols / 256), RT = (int)((rows + 15) / 16);
+    size_t rrb = (size_t)nsb * (type == 12 ? 144 : type == 14 ? 210 : 8 * 34);
+    int wpt = tile_bytes(type) / 4;
+    if (!wpt) return JUNO_ERR_UNSUPPORTED;
+    uint32_t *o = reinterpret_cast<uint32_t *>(out);
+    for (int R = 0; R < RT; R++)
+        for (int b = 0; b < nsb; b++)
+            for (int w = 0; w < wpt; w++) {
+                uint32_t v = 0;
+                if (type == 12) {
+                    int row16, off;
+                    q4k_word_src(w, row16, off);
+                    int row = R * 16 + row16;
+                    if (row < rows) {
+                        const uint8_t *s = raw + (size_t)row * rrb + (size_t)b * 144 + off;
+                        v = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+                    }
+                } else if (type == 14) {
+                    v = q6k_out_word(raw, rrb, (int)rows, b, R, w);
+                } else {
+                    v = q80_out_word(raw, rrb, (int)rows, b, R, w);
+                }
+                o[((size_t)R * nsb + b) * wpt + w] = v;
+            }
+    return JUNO_OK;
+}
+extern "C" int64_t juno_dbg_tiled_bytes(int type, int64_t rows, int64_t cols) {
+    if (cols % 256 || !tile_bytes(type)) return -1;
+    return ((rows + 15) / 16) * (cols / 256) * (int64_t)tile_bytes(type);
+}
+
+// ───────────────────────────── bit-exact dequantisation from tiles ─────────────────────────
+// Formulas and rounding order of LlamaTransformerHandler.dequantizeQ4K/Q6K/Q8_0 (:1017-1050,
+// :1095-1135, :895-913): every product and difference is rounded separately.
+__host__ __device__ inline float dq_f16(const uint8_t *p) {
+    uint32_t bits = (uint32_t)p[0] | ((uint32_t)p[1] << 8);
+#if defined(__CUDA_ARCH__)
+    return __half2float(__ushort_as_half((unsigned short)bits));
+#else
+    // host mirror of GgufReader.f16ToF32 (:1248-1271)
+    int s = (bits >> 15) & 1, e = (bits >> 10) & 0x1F, m = bits & 0x3FF;
+    uint32_t f;
+    if (e == 0) {
+        if (m == 0)
+            f = (uint32_t)s << 31;
+        else {
+            int ex = -14;
+            while ((m & 0x400) == 0) {
+                m <<= 1;
+                ex--;
+            }
+            m &= 0x3FF;
+            f = ((uint32_t)s << 31) | ((uint32_t)(ex + 127) << 23) | ((uint32_t)m << 13);
+        }
+    } else if (e == 31)
+        f = ((uint32_t)s << 31) | 0x7F800000u | ((uint32_t)m << 13);
+    else
+        f = ((uint32_t)s << 31) | ((uint32_t)(e - 15 + 127) << 23) | ((uint32_t)m << 13);
+    float o;
+    memcpy(&o, &f, 4);
+    return o;
+#endif
+}
+
+#if defined(__CUDA_ARCH__)
+#define JMUL(a, b) __fmul_rn((a), (b))
+#define JSUB(a, b) __fsub_rn((a), (b))
+#else
+#define JMUL(a, b) ((a) * (b))
+#define JSUB(a, b) ((a) - (b))
+#endif
+
+__host__ __device__ inline float tile_elem_value(int type, const uint8_t *tile, int row16, int e) {
+    if (type == 12) {
+        const uint8_t *hdr = tile + row16 * 16;
+        float d = dq_f16(hdr), dmin = dq_f16(hdr + 2);
+        int s = e >> 5;
+        float scale = JMUL(d, (float)q4k_scale6(hdr + 4, s));
+        float mn = JMUL(dmin, (float)q4k_min6(hdr + 4, s));
+        int off, hi;
+        q4k_elem_loc(row16, e, off, hi);
+        int q = hi ? (tile[off] >> 4) : (tile[off] & 15);
+        return JSUB(JMUL(scale, (float)q), mn);
+    } else if (type == 14) {
+        Q6Loc L = q6k_elem_loc(row16, e);
+        uint32_t W = (uint32_t)tile[L.w_off] | ((uint32_t)tile[L.w_off + 1] << 8) | ((uint32_t)tile[L.w_off + 2] << 16) |
+                     ((uint32_t)tile[L.w_off + 3] << 24);
+        uint32_t H = (uint32_t)tile[L.h_off] | ((uint32_t)tile[L.h_off + 1] << 8) | ((uint32_t)tile[L.h_off + 2] << 16) |
+                     ((uint32_t)tile[L.h_off + 3] << 24);
+        int u6 = (int)((W >> (4 * L.nu)) & 15u) | (int)(((H >> L.h_bit) & 3u) << 4);
+        float d = dq_f16(tile + L.d_off);
+        float ds = JMUL(d, (float)(int)(signed char)tile[L.sc_off]);
+        return JMUL(ds, (float)(u6 - 32));
+    } else {
+        int off, doff;
+        q80_elem_loc(row16, e, off, doff);
+        return JMUL(dq_f16(tile + doff), (float)(int)(signed char)tile[off]);
+    }
+}
+
+__global__ void dequant_tiled_kernel(int type, const uint8_t *tiles, int64_t nb, int64_t cols, int64_t row_start,
+                                     int64_t n_rows, float *out) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * cols) return;
+    int64_t r = idx / cols, col = idx - r * cols;
+    int64_t row = row_start + r;
+    const uint8_t *tile = tiles + ((row >> 4) * nb + (col >> 8)) * (int64_t)tile_bytes(type);
+    out[idx] = tile_elem_value(type, tile, (int)(row & 15), (int)(col & 255));
+}
+
+extern "C" int juno_dbg_dequant_tiled_host(int type, const uint8_t *tiles, int64_t rows, int64_t cols, float *out) {
+    if (cols % 256 || !tile_bytes(type)) return JUNO_ERR_INVALID_ARG;
+    int64_t nb = cols / 256;
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t c = 0; c < cols; c++) {
+            const uint8_t *tile = tiles + ((r >> 4) * nb + (c >> 8)) * (int64_t)tile_bytes(type);
+            out[r * cols + c] = tile_elem_value(type, tile, (int)(r & 15), (int)(c & 255));
+        }
+    return JUNO_OK;
+}
+
+// ───────────────────────────── raw-layout kernels (odd shapes, FP32) ───────────────────────
+__device__ inline float raw_elem_value(int type, const uint8_t *rowp, int64_t c) {
+    if (type == 0) return reinterpret_cast<const float *>(rowp)[c];
+    if (type == 8) {
+        const uint8_t *b = rowp + (c >> 5) * 34;
+        return __fmul_rn(dq_f16(b), (float)(int)(signed char)b[2 + (c & 31)]);
+    }
+    if (type == 12) {
+        const uint8_t *b = rowp + (c >> 8) * 144;
+        int e = (int)(c & 255), s = e >> 5;
+        float scale = __fmul_rn(dq_f16(b), (float)q4k_scale6(b + 4, s));
+        float mn = __fmul_rn(dq_f16(b + 2), (float)q4k_min6(b + 4, s));
+        int byte = b[16 + (e >> 6) * 32 + (e & 31)];
+        int q = ((e >> 5) & 1) ? (byte >> 4) : (byte & 15);
+        return __fsub_rn(__fmul_rn(scale, (float)q), mn);
+    }
+    const uint8_t *b = rowp + (c >> 8) * 210;
+    int e = (int)(c & 255);
+    float ds = __fmul_rn(dq_f16(b + 208), (float)(int)(signed char)b[192 + (e >> 4)]);
+    return __fmul_rn(ds, (float)(q6k_raw_u6(b, e) - 32));
+}
+
+__global__ void gemv_raw_kernel(int type, const uint8_t *raw, int64_t row_bytes, int64_t rows, int64_t cols,
+                                const float *x, int batch, float *y) {
+    int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (gw >= rows * batch) return;
+    int64_t r = gw % rows;
+    int b = (int)(gw / rows);
+    const uint8_t *rowp = raw + r * row_bytes;
+    const float *xv = x + (int64_t)b * cols;
+    float acc = 0.f;
+    for (int64_t c = lane; c < cols; c += 32) acc = fmaf(raw_elem_value(type, rowp, c), xv[c], acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[(int64_t)b * rows + r] = acc;
+}
+
+__global__ void dequant_raw_kernel(int type, const uint8_t *raw, int64_t row_bytes, int64_t cols, int64_t row_start,
+                                   int64_t n_rows, float *out) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * cols) return;
+    int64_t r = idx / cols, c = idx - r * cols;
+    out[idx] = raw_elem_value(type, raw + (row_start + r) * row_bytes, c);
+}
+
+static int64_t raw_row_bytes(int type, int64_t cols) {
+    return cols / raw_block_elems(type) * raw_block_bytes(type);
+}
+
+int launch_gemv_raw(juno_ctx *ctx, const juno_qmat *m, const float *x, int batch, float *y, cudaStream_t st) {
+    int64_t warps = m->rows * batch;
+    int threads = 256;
+    int64_t blocks = (warps * 32 + threads - 1) / threads;
+    gemv_raw_kernel<<<(unsigned)blocks, threads, 0, st>>>(m->type, m->dev, raw_row_bytes(m->type, m->cols), m->rows,
+                                                         m->cols, x, batch, y);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+int launch_dequant(juno_ctx *ctx, const juno_qmat *m, int64_t row_start, int64_t n_rows, float *out, cudaStream_t st) {
+    int64_t n = n_rows * m->cols;
+    int threads = 256;
+    int64_t blocks = (n + threads - 1) / threads;
+    if (blocks == 0) return JUNO_OK;
+    if (m->tiled)
+        dequant_tiled_kernel<<<(unsigned)blocks, threads, 0, st>>>(m->type, m->dev, m->nb, m->cols, row_start, n_rows, out);
+    else
+        dequant_raw_kernel<<<(unsigned)blocks, threads, 0, st>>>(m->type, m->dev, raw_row_bytes(m->type, m->cols),
+                                                                m->cols, row_start, n_rows, out);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+// ───────────────────────────── resident matrix ─────────────────────────────────────────────
+int qmat_create(juno_ctx *ctx, const void *blocks, int type, int64_t rows_total, int64_t cols_total, int64_t row0,
+                int64_t nrows, int64_t sb0, int64_t nsb, juno_qmat **out) {
+    JUNO_REQUIRE(type == 0 || type == 8 || type == 12 || type == 14, "unsupported GGML type %d", type);
+    JUNO_REQUIRE(rows_total > 0 && cols_total > 0 && nrows > 0 && row0 >= 0 && row0 + nrows <= rows_total,
+                 "bad matrix shape rows=%lld cols=%lld", (long long)rows_total, (long long)cols_total);
+    JUNO_REQUIRE(cols_total % raw_block_elems(type) == 0, "cols=%lld is not a multiple of the block size %d",
+                 (long long)cols_total, raw_block_elems(type));
+    const bool tiled = (type != 0) && (cols_total % 256 == 0);
+    const int64_t rrb = raw_row_bytes(type, cols_total);
+    int64_t cols = cols_total;
+    if (tiled) {
+        if (nsb <= 0) {
+            sb0 = 0;
+            nsb = cols_total / 256;
+        }
+        JUNO_REQUIRE(sb0 >= 0 && (sb0 + nsb) * 256 <= cols_total, "bad super-block slice");
+        cols = nsb * 256;
+    } else {
+        JUNO_REQUIRE(nsb <= 0, "column slicing needs a 256-multiple column count");
+    }
+    JUNO_REQUIRE(nrows < (1ll << 31) && cols < (1ll << 31), "matrix too large");
+
+    juno_qmat *m = new juno_qmat();
+    m->magic = kMagicQmat;
+    m->ctx = ctx;
+    m->type = type;
+    m->tiled = tiled ? 1 : 0;
+    m->rows = nrows;
+    m->cols = cols;
+    m->row_tiles = (nrows + 15) / 16;
+    m->nb = cols / 256;
+    m->dev = nullptr;
+    const uint8_t *src = static_cast<const uint8_t *>(blocks) + row0 * rrb;
+    const size_t raw_bytes = (size_t)nrows * rrb;
+    int rc = JUNO_OK;
+    cudaStream_t st = ctx->stream;
+    auto fail = [&](int code) {
+        if (m->dev) cudaFree(m->dev);
+        m->magic = kMagicDead;
+        delete m;
+        return code;
+    };
+    if (!tiled) {
+        m->bytes = raw_bytes;
+        if (cudaMalloc((void **)&m->dev, m->bytes) != cudaSuccess) {
+            cudaGetLastError();
+            set_error("cudaMalloc of %zu bytes failed", m->bytes);
+            return fail(JUNO_ERR_OOM);
+        }
+        if (cudaMemcpyAsync(m->dev, src, raw_bytes, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess) {
+            set_error("upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+            return fail(JUNO_ERR_CUDA);
+        }
+    } else {
+        m->bytes = (size_t)m->row_tiles * m->nb * tile_bytes(type);
+        uint8_t *tmp = nullptr;
+        if (cudaMalloc((void **)&m->dev, m->bytes) != cudaSuccess || cudaMalloc((void **)&tmp, raw_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            set_error("cudaMalloc of %zu + %zu bytes failed", m->bytes, raw_bytes);
+            return fail(JUNO_ERR_OOM);
+        }
+        cudaError_t e = cudaMemcpyAsync(tmp, src, raw_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) {
+            size_t words = m->bytes / 4;
+            int threads = 256;
+            unsigned blocks_n = (unsigned)((words + threads - 1) / threads);
+            if (type == 12)
+                repack_q4k_kernel<<<blocks_n, threads, 0, st>>>(tmp, (size_t)rrb, (int)nrows, (int)sb0, (int)nsb, m->dev);
+            else if (type == 14)
+                repack_q6k_kernel<<<blocks_n, threads, 0, st>>>(tmp, (size_t)rrb, (int)nrows, (int)sb0, (int)nsb, m->dev);
+            else
+                repack_q80_kernel<<<blocks_n, threads, 0, st>>>(tmp, (size_t)rrb, (int)nrows, (int)sb0, (int)nsb, m->dev);
+            e = cudaGetLastError();
+            ctx->kernel_launches++;
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        cudaFree(tmp);
+        if (e != cudaSuccess) {
+            set_error("repack failed: %s", cudaGetErrorString(e));
+            rc = JUNO_ERR_CUDA;
+            return fail(rc);
+        }
+    }
+    ctx->h2d_bytes += (int64_t)raw_bytes;
+    *out = m;
+    return JUNO_OK;
+}
+
+int qmat_destroy(juno_qmat *m) {
+    if (!m) return JUNO_ERR_INVALID_ARG;
+    if (m->magic != kMagicQmat) {
+        set_error("matrix handle is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    {
+        DeviceGuard g(m->ctx->device);
+        if (m->dev) cudaFree(m->dev);
+    }
+    m->dev = nullptr;
+    m->magic = kMagicDead;  // the small host record is kept so a second free reports CLOSED instead of crashing
+    return JUNO_OK;
+}
+
+}  // namespace juno

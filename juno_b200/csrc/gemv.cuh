@@ -1,0 +1,60 @@
+// Device-level interface of the fused dequant-GEMV: used by the MatVec entry points
+// and by the forward pass.
+#pragma once
+#include "common.cuh"
+
+struct juno_qmat {
+    uint32_t magic;
+    juno_ctx *ctx;
+    int type;          // GGML type id
+    int tiled;         // 1: 16x256 tile layout (layout.cuh); 0: raw row-major blocks
+    int64_t rows, cols;
+    int64_t row_tiles; // ceil(rows/16) when tiled
+    int64_t nb;        // cols/256 when tiled
+    uint8_t *dev;
+    size_t bytes;
+};
+
+namespace juno {
+
+enum GemvPrologue {
+    PRO_PLAIN = 0,   // v = x[i]
+    PRO_RMSNORM = 1, // r = x[i] (+ x_add[i]); optional store of r to x_out by block 0; v = (normw[i]*r)*rsqrt-scale
+    PRO_SILU = 2,    // v = silu(x[i]) * up[i]
+};
+
+struct GemvSeg {
+    const uint8_t *w; // tiled weights
+    float *out;       // [batch][ld_out]
+    int rows;         // valid rows
+    int row_tiles;
+};
+
+struct GemvArgs {
+    GemvSeg seg[3];
+    int nseg = 1;
+    int type = 0;
+    int K = 0;
+    int batch = 1;
+    int ld_out = 0;   // stride between batch rows of every seg.out
+    int pro = PRO_PLAIN;
+    const float *x = nullptr;  // [batch][ldx]
+    int ldx = 0;
+    const float *x_add = nullptr, *normw = nullptr, *up = nullptr;
+    float *x_out = nullptr;
+    float eps = 0.f;
+};
+
+// Enqueues the product on `stream`.  All pointers are device pointers.
+int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
+// Raw-layout / FP32 fallback (one warp per output), used for shapes the tile layout does not cover.
+int launch_gemv_raw(juno_ctx *ctx, const juno_qmat *m, const float *x, int batch, float *y, cudaStream_t stream);
+int launch_dequant(juno_ctx *ctx, const juno_qmat *m, int64_t row_start, int64_t n_rows, float *out,
+                   cudaStream_t stream);
+// Allocates and fills a resident matrix from raw host blocks (row range [row0,row0+nrows), super-block
+// column range [sb0, sb0+nsb) of the host tensor — the slicing used by tensor parallelism).
+int qmat_create(juno_ctx *ctx, const void *blocks, int type, int64_t rows_total, int64_t cols_total, int64_t row0,
+                int64_t nrows, int64_t sb0, int64_t nsb, juno_qmat **out);
+int qmat_destroy(juno_qmat *m);
+
+}  // namespace juno
