@@ -155,6 +155,9 @@ typedef struct juno_model_cfg {
 #define JUNO_T_FFN_UP 10
 #define JUNO_T_FFN_DOWN 11
 
+/* Fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and ships the bytes to the other ranks). */
+int juno_nccl_unique_id(uint8_t *out128);
+
 int juno_model_create(juno_ctx *ctx, const juno_model_cfg *cfg, juno_model **out);
 /* Hands one FULL (unsharded) tensor to the model; with tp_world > 1 the library keeps only
  * this rank's slice (column-parallel Q/K/V/gate/up by head and FFN rows, row-parallel

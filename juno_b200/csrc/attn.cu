@@ -1,0 +1,641 @@
+// Paged KV cache, RoPE + KV append, and GQA flash-decode attention with split-K over context.
+//
+// Replaces the per-request FP32 heap arrays and the scalar gqa()/softmax()/rope() loops of
+// LlamaTransformerHandler.java:670-733,1657-1730.  One CTA handles one (sequence, kv head, context
+// split): K and V pages are streamed once and shared by the G query heads of the group; each split
+// keeps an online-softmax state (m, l, o) and a second small kernel merges the splits.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "attn.cuh"
+
+namespace juno {
+
+// ───────────────────────────── kernels ────────────────────────────────────────────────────
+struct AttnParams {
+    const void *k, *v;
+    const int32_t *table;
+    int max_pages_per_seq, n_pages, n_kv_heads, n_heads, layer, n_splits;
+    const float *q;
+    int ldq;
+    const int32_t *slots, *seq_lens;
+    float *part_o, *part_ml, *out;
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T, int EPL>
+__device__ __forceinline__ void load_vec(const T *p, float (&o)[EPL]);
+template <>
+__device__ __forceinline__ void load_vec<__half, 4>(const __half *p, float (&o)[4]) {
+    uint2 u = *reinterpret_cast<const uint2 *>(p);
+    float2 a = __half22float2(*reinterpret_cast<__half2 *>(&u.x)), b = __half22float2(*reinterpret_cast<__half2 *>(&u.y));
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load_vec<__half, 2>(const __half *p, float (&o)[2]) {
+    uint32_t u = *reinterpret_cast<const uint32_t *>(p);
+    float2 a = __half22float2(*reinterpret_cast<__half2 *>(&u));
+    o[0] = a.x; o[1] = a.y;
+}
+template <>
+__device__ __forceinline__ void load_vec<float, 4>(const float *p, float (&o)[4]) {
+    float4 u = *reinterpret_cast<const float4 *>(p);
+    o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<float, 2>(const float *p, float (&o)[2]) {
+    float2 u = *reinterpret_cast<const float2 *>(p);
+    o[0] = u.x; o[1] = u.y;
+}
+
+constexpr int kAttnWarps = 4;
+
+template <typename T, int HD, int G>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnParams p) {
+    constexpr int EPL = HD / 32;
+    const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int len = p.seq_lens[seq];
+    const int chunk = (((len + p.n_splits - 1) / p.n_splits) + 15) & ~15;
+    const int t0 = split * chunk, t1 = min(len, t0 + chunk);
+    const int h0 = kvh * G;
+    float *po = p.part_o + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * HD;   // head stride n_splits*HD
+    float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
+    if (t0 >= t1) {  // empty split
+        if (tid < G) {
+            pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
+            pml[(size_t)tid * p.n_splits * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const float scale = (float)(1.0 / sqrt((double)HD));
+    float qr[G][EPL], o[G][EPL], m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const float *qp = p.q + (size_t)seq * p.ldq + (size_t)(h0 + g) * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) {
+            qr[g][e] = qp[e];
+            o[g][e] = 0.f;
+        }
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+    }
+    const int32_t *table = p.table + (size_t)p.slots[seq] * p.max_pages_per_seq;
+    const T *kbase = static_cast<const T *>(p.k), *vbase = static_cast<const T *>(p.v);
+    for (int t = t0 + warp; t < t1; t += kAttnWarps) {
+        const int page = table[t >> 4];
+        const size_t off = ((((size_t)p.layer * p.n_pages + page) * p.n_kv_heads + kvh) * kPageTokens + (t & 15)) * HD +
+                           lane * EPL;
+        float kv[EPL], vv[EPL];
+        load_vec<T, EPL>(kbase + off, kv);
+        load_vec<T, EPL>(vbase + off, vv);
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float d = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; e++) d = fmaf(qr[g][e], kv[e], d);
+            s[g] = d;
+        }
+#pragma unroll
+        for (int ofs = 16; ofs > 0; ofs >>= 1)
+#pragma unroll
+            for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], ofs);
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float sc = s[g] * scale;
+            const float mn = fmaxf(m[g], sc);
+            const float corr = expf(m[g] - mn), pe = expf(sc - mn);
+            l[g] = fmaf(l[g], corr, pe);
+#pragma unroll
+            for (int e = 0; e < EPL; e++) o[g][e] = fmaf(o[g][e], corr, pe * vv[e]);
+            m[g] = mn;
+        }
+    }
+    // merge the warps of this CTA
+    __shared__ float sm_m[kAttnWarps][G], sm_l[kAttnWarps][G];
+    __shared__ float sm_o[kAttnWarps][G][HD];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        if (lane == 0) {
+            sm_m[warp][g] = m[g];
+            sm_l[warp][g] = l[g];
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; e++) sm_o[warp][g][lane * EPL + e] = o[g][e];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; w++) M = fmaxf(M, sm_m[w][g]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; w++) {
+            if (sm_l[w][g] > 0.f) {
+                const float f = expf(sm_m[w][g] - M);
+                L = fmaf(sm_l[w][g], f, L);
+                acc = fmaf(sm_o[w][g][d], f, acc);
+            }
+        }
+        po[(size_t)g * p.n_splits * HD + d] = acc;
+        if (d == 0) {
+            pml[(size_t)g * p.n_splits * 2 + 0] = M;
+            pml[(size_t)g * p.n_splits * 2 + 1] = L;
+        }
+    }
+}
+
+template <int HD>
+__global__ void attn_combine_kernel(const AttnParams p) {
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
+    const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h) * p.n_splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < p.n_splits; s++) M = fmaxf(M, pml[2 * s]);
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < p.n_splits; s++) {
+        const float ls = pml[2 * s + 1];
+        if (ls > 0.f) {
+            const float f = expf(pml[2 * s] - M);
+            L = fmaf(ls, f, L);
+            acc = fmaf(po[(size_t)s * HD + d], f, acc);
+        }
+    }
+    p.out[(size_t)(seq * p.n_heads + h) * HD + d] = (L > 0.f) ? acc / L : 0.f;
+}
+
+// cos/sin of pos * theta^(-2i/hd) in binary64, cast to float, as LlamaTransformerHandler.rope (:1662-1666).
+__global__ void rope_table_kernel(const int32_t *positions, int n, int hd, float theta, float2 *table) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    int half = hd / 2;
+    if (idx >= n * half) return;
+    int seq = idx / half, i = idx - seq * half;
+    double freq = 1.0 / pow((double)theta, (2.0 * i) / hd);
+    double angle = positions[seq] * freq;
+    table[idx] = make_float2((float)cos(angle), (float)sin(angle));
+}
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+struct RopeParams {
+    void *k, *v;
+    const int32_t *table;
+    int max_pages_per_seq, n_pages, n_kv_heads, n_heads, layer, hd;
+    float *q;
+    int ldq;
+    const float *kin, *vin;
+    int ldkv;
+    const int32_t *slots, *positions;
+    const float2 *cs;
+};
+
+template <typename T>
+__global__ void rope_append_kernel(const RopeParams p) {
+    const int seq = blockIdx.x, head = blockIdx.y, i = threadIdx.x;  // i: pair index
+    const float2 cs = p.cs[seq * (p.hd / 2) + i];
+    if (head < p.n_heads) {
+        float *x = p.q + (size_t)seq * p.ldq + head * p.hd + 2 * i;
+        const float x0 = x[0], x1 = x[1];
+        x[0] = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+        x[1] = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+    } else {
+        const int kvh = head - p.n_heads;
+        const int pos = p.positions[seq];
+        const int page = p.table[(size_t)p.slots[seq] * p.max_pages_per_seq + (pos >> 4)];
+        const size_t off =
+            ((((size_t)p.layer * p.n_pages + page) * p.n_kv_heads + kvh) * kPageTokens + (pos & 15)) * p.hd + 2 * i;
+        const float *kx = p.kin + (size_t)seq * p.ldkv + kvh * p.hd + 2 * i;
+        const float *vx = p.vin + (size_t)seq * p.ldkv + kvh * p.hd + 2 * i;
+        const float x0 = kx[0], x1 = kx[1];
+        T *kd = static_cast<T *>(p.k) + off, *vd = static_cast<T *>(p.v) + off;
+        kd[0] = from_f32<T>(__fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y)));
+        kd[1] = from_f32<T>(__fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x)));
+        vd[0] = from_f32<T>(vx[0]);
+        vd[1] = from_f32<T>(vx[1]);
+    }
+}
+
+// Scatter of host-provided K/V rows (already on the device as FP32) into pages, for the operator API.
+template <typename T>
+__global__ void kv_scatter_kernel(void *kpool, void *vpool, const int32_t *table_row, int n_pages, int n_kv_heads, int hd,
+                                  int layer, int pos0, int n_tokens, const float *kin, const float *vin) {
+    const int kvdim = n_kv_heads * hd;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tokens * kvdim) return;
+    const int j = (int)(idx / kvdim), e = (int)(idx - (size_t)j * kvdim), kvh = e / hd, d = e - kvh * hd;
+    const int pos = pos0 + j, page = table_row[pos >> 4];
+    const size_t off = ((((size_t)layer * n_pages + page) * n_kv_heads + kvh) * kPageTokens + (pos & 15)) * hd + d;
+    static_cast<T *>(kpool)[off] = from_f32<T>(kin[idx]);
+    static_cast<T *>(vpool)[off] = from_f32<T>(vin[idx]);
+}
+
+// ───────────────────────────── host: launches ─────────────────────────────────────────────
+size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits) {
+    return (size_t)n * n_heads * n_splits * (hd + 2);
+}
+
+int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
+    const int target = ctx->sm_count * 4;  // CTAs of 128 threads wanted in flight
+    int by_occupancy = (target + n * n_kv_heads - 1) / std::max(1, n * n_kv_heads);
+    int by_length = std::max(1, (max_len + 63) / 64);  // at least 64 positions per split
+    int s = std::max(1, std::min(by_occupancy, by_length));
+    return std::min(s, 64);
+}
+
+template <typename T, int HD, int G>
+static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
+    dim3 grid(p.n_kv_heads, p.n_splits, n);
+    attn_split_kernel<T, HD, G><<<grid, kAttnWarps * 32, 0, st>>>(p);
+}
+
+template <typename T, int HD>
+static int attn_launch_g(const AttnParams &p, int n, int G, cudaStream_t st) {
+    switch (G) {
+    case 1: attn_launch_inst<T, HD, 1>(p, n, st); return JUNO_OK;
+    case 2: attn_launch_inst<T, HD, 2>(p, n, st); return JUNO_OK;
+    case 4: attn_launch_inst<T, HD, 4>(p, n, st); return JUNO_OK;
+    case 8: attn_launch_inst<T, HD, 8>(p, n, st); return JUNO_OK;
+    default: break;
+    }
+    set_error("attention: query/kv head ratio %d is not supported (1, 2, 4, 8)", G);
+    return JUNO_ERR_UNSUPPORTED;
+}
+
+int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
+    const juno_kvpool *pool = a.pool;
+    JUNO_REQUIRE(a.n_heads % pool->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", a.n_heads,
+                 pool->n_kv_heads);
+    const int G = a.n_heads / pool->n_kv_heads, hd = pool->head_dim;
+    JUNO_REQUIRE(hd == 64 || hd == 128, "attention: head_dim %d is not supported (64, 128)", hd);
+    AttnParams p;
+    p.k = pool->k;
+    p.v = pool->v;
+    p.table = pool->d_table;
+    p.max_pages_per_seq = pool->max_pages_per_seq;
+    p.n_pages = pool->n_pages;
+    p.n_kv_heads = pool->n_kv_heads;
+    p.n_heads = a.n_heads;
+    p.layer = a.layer;
+    p.n_splits = a.n_splits;
+    p.q = a.q;
+    p.ldq = a.ldq > 0 ? a.ldq : a.n_heads * hd;
+    p.slots = a.slots;
+    p.seq_lens = a.seq_lens;
+    p.part_o = a.part_o;
+    p.part_ml = a.part_ml;
+    p.out = a.out;
+    int rc;
+    if (pool->dtype == 0)
+        rc = hd == 128 ? attn_launch_g<__half, 128>(p, a.n, G, st) : attn_launch_g<__half, 64>(p, a.n, G, st);
+    else
+        rc = hd == 128 ? attn_launch_g<float, 128>(p, a.n, G, st) : attn_launch_g<float, 64>(p, a.n, G, st);
+    JUNO_TRY(rc);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    dim3 cgrid(a.n_heads, a.n);
+    if (hd == 128)
+        attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(p);
+    else
+        attn_combine_kernel<64><<<cgrid, 64, 0, st>>>(p);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches += 2;
+    return JUNO_OK;
+}
+
+int launch_rope_table(juno_ctx *ctx, const int32_t *positions, int n, int hd, float theta, float2 *table,
+                      cudaStream_t st) {
+    int total = n * hd / 2;
+    rope_table_kernel<<<(total + 127) / 128, 128, 0, st>>>(positions, n, hd, theta, table);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+int launch_rope_append(juno_ctx *ctx, const juno_kvpool *pool, int layer, int n, int n_heads, float *q, int ldq,
+                       const float *k, const float *v, int ldkv, const int32_t *slots, const int32_t *positions,
+                       const float2 *cs_table, cudaStream_t st) {
+    RopeParams p;
+    p.k = pool->k;
+    p.v = pool->v;
+    p.table = pool->d_table;
+    p.max_pages_per_seq = pool->max_pages_per_seq;
+    p.n_pages = pool->n_pages;
+    p.n_kv_heads = pool->n_kv_heads;
+    p.n_heads = n_heads;
+    p.layer = layer;
+    p.hd = pool->head_dim;
+    p.q = q;
+    p.ldq = ldq;
+    p.kin = k;
+    p.vin = v;
+    p.ldkv = ldkv;
+    p.slots = slots;
+    p.positions = positions;
+    p.cs = cs_table;
+    dim3 grid(n, n_heads + pool->n_kv_heads);
+    if (pool->dtype == 0)
+        rope_append_kernel<__half><<<grid, pool->head_dim / 2, 0, st>>>(p);
+    else
+        rope_append_kernel<float><<<grid, pool->head_dim / 2, 0, st>>>(p);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+// ───────────────────────────── pool and sequences ─────────────────────────────────────────
+int kvpool_create(juno_ctx *ctx, int n_layers, int n_kv_heads, int head_dim, int n_pages, int dtype, int max_slots,
+                  int max_pages_per_seq, juno_kvpool **out) {
+    JUNO_REQUIRE(n_layers > 0 && n_kv_heads > 0 && n_pages > 0 && max_slots > 0 && max_pages_per_seq > 0,
+                 "bad KV pool geometry");
+    JUNO_REQUIRE(head_dim == 64 || head_dim == 128, "head_dim %d is not supported (64, 128)", head_dim);
+    JUNO_REQUIRE(dtype == 0 || dtype == 1, "kv_dtype %d (0 = f16, 1 = f32)", dtype);
+    juno_kvpool *p = new juno_kvpool();
+    p->magic = kMagicPool;
+    p->ctx = ctx;
+    p->n_layers = n_layers;
+    p->n_kv_heads = n_kv_heads;
+    p->head_dim = head_dim;
+    p->n_pages = n_pages;
+    p->dtype = dtype;
+    p->page_tokens = kPageTokens;
+    p->elem_bytes = dtype == 0 ? 2 : 4;
+    p->max_slots = max_slots;
+    p->max_pages_per_seq = max_pages_per_seq;
+    p->k = p->v = nullptr;
+    p->d_table = p->h_table = nullptr;
+    p->owned_by_model = 0;
+    const size_t bytes = (size_t)n_layers * n_pages * n_kv_heads * kPageTokens * head_dim * p->elem_bytes;
+    const size_t tbytes = (size_t)max_slots * max_pages_per_seq * sizeof(int32_t);
+    cudaError_t e = cudaMalloc(&p->k, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->v, bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&p->d_table, tbytes);
+    if (e == cudaSuccess) e = cudaMallocHost((void **)&p->h_table, tbytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0, tbytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p->k, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p->v, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaMalloc of the KV pool (2 x %zu bytes) failed: %s", bytes, cudaGetErrorString(e));
+        if (p->k) cudaFree(p->k);
+        if (p->v) cudaFree(p->v);
+        if (p->d_table) cudaFree(p->d_table);
+        if (p->h_table) cudaFreeHost(p->h_table);
+        delete p;
+        return e == cudaErrorMemoryAllocation ? JUNO_ERR_OOM : JUNO_ERR_CUDA;
+    }
+    memset(p->h_table, 0, tbytes);
+    p->free_pages.reserve(n_pages);
+    for (int i = n_pages - 1; i >= 0; i--) p->free_pages.push_back(i);
+    for (int i = max_slots - 1; i >= 0; i--) p->free_slots.push_back(i);
+    *out = p;
+    return JUNO_OK;
+}
+
+int kvpool_destroy(juno_kvpool *p) {
+    if (!p) return JUNO_ERR_INVALID_ARG;
+    if (p->magic != kMagicPool) {
+        set_error("KV pool is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    DeviceGuard g(p->ctx->device);
+    cudaStreamSynchronize(p->ctx->stream);
+    cudaFree(p->k);
+    cudaFree(p->v);
+    cudaFree(p->d_table);
+    cudaFreeHost(p->h_table);
+    p->k = p->v = nullptr;
+    p->magic = kMagicDead;
+    return JUNO_OK;
+}
+
+int seq_create(juno_kvpool *p, int max_tokens, juno_seq **out) {
+    JUNO_REQUIRE(max_tokens > 0, "max_tokens %d", max_tokens);
+    const int need_pages = (max_tokens + kPageTokens - 1) / kPageTokens;
+    JUNO_REQUIRE(need_pages <= p->max_pages_per_seq, "max_tokens %d exceeds the pool's per-sequence limit %d", max_tokens,
+                 p->max_pages_per_seq * kPageTokens);
+    if (p->free_slots.empty()) {
+        set_error("no free sequence slot (max %d live sequences)", p->max_slots);
+        return JUNO_ERR_OOM;
+    }
+    juno_seq *s = new juno_seq();
+    s->magic = kMagicSeq;
+    s->pool = p;
+    s->max_tokens = max_tokens;
+    s->len = 0;
+    s->slot = p->free_slots.back();
+    p->free_slots.pop_back();
+    *out = s;
+    return JUNO_OK;
+}
+
+int seq_reserve(juno_seq *s, int upto, cudaStream_t st) {
+    juno_kvpool *p = s->pool;
+    JUNO_REQUIRE(upto <= s->max_tokens, "position %d is beyond this sequence's limit of %d", upto - 1, s->max_tokens);
+    const int need = (upto + kPageTokens - 1) / kPageTokens;
+    const int have = (int)s->pages.size();
+    if (need <= have) return JUNO_OK;
+    if ((int)p->free_pages.size() < need - have) {
+        set_error("KV pool exhausted: %d pages free, %d needed", (int)p->free_pages.size(), need - have);
+        return JUNO_ERR_OOM;
+    }
+    int32_t *row = p->h_table + (size_t)s->slot * p->max_pages_per_seq;
+    for (int i = have; i < need; i++) {
+        int pg = p->free_pages.back();
+        p->free_pages.pop_back();
+        s->pages.push_back(pg);
+        row[i] = pg;
+    }
+    JUNO_CUDA_TRY(cudaMemcpyAsync(p->d_table + (size_t)s->slot * p->max_pages_per_seq + have, row + have,
+                                  (size_t)(need - have) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    return JUNO_OK;
+}
+
+static int seq_check(juno_seq *s) {
+    if (!s) {
+        set_error("sequence is null");
+        return JUNO_ERR_INVALID_ARG;
+    }
+    if (s->magic != kMagicSeq || !s->pool || s->pool->magic != kMagicPool) {
+        set_error("sequence handle is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    return JUNO_OK;
+}
+
+}  // namespace juno
+
+using namespace juno;
+
+extern "C" {
+
+int juno_kvpool_create(juno_ctx *c, int32_t n_layers, int32_t n_kv_heads, int32_t head_dim, int32_t n_pages,
+                       int32_t kv_dtype, juno_kvpool **out) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(out, "out is null");
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    return kvpool_create(c, n_layers, n_kv_heads, head_dim, n_pages, kv_dtype, 256, std::min(n_pages, 8192), out);
+}
+
+int juno_kvpool_free(juno_kvpool *p) {
+    if (!p) {
+        set_error("pool is null");
+        return JUNO_ERR_INVALID_ARG;
+    }
+    if (p->magic != kMagicPool) {
+        set_error("KV pool is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    JUNO_REQUIRE(!p->owned_by_model, "this pool belongs to a model; free the model instead");
+    std::lock_guard<std::recursive_mutex> lk(p->ctx->mu);
+    return kvpool_destroy(p);
+}
+
+int juno_kvseq_create(juno_kvpool *p, int32_t max_tokens, juno_seq **out) {
+    JUNO_REQUIRE(p && out, "null argument");
+    if (p->magic != kMagicPool) {
+        set_error("KV pool is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    std::lock_guard<std::recursive_mutex> lk(p->ctx->mu);
+    return seq_create(p, max_tokens, out);
+}
+
+int juno_seq_free(juno_seq *s) {
+    JUNO_TRY(seq_check(s));
+    juno_kvpool *p = s->pool;
+    std::lock_guard<std::recursive_mutex> lk(p->ctx->mu);
+    {
+        DeviceGuard g(p->ctx->device);
+        cudaStreamSynchronize(p->ctx->stream);  // no kernel may still read these pages
+    }
+    for (int pg : s->pages) p->free_pages.push_back(pg);
+    p->free_slots.push_back(s->slot);
+    s->pages.clear();
+    s->magic = kMagicDead;
+    return JUNO_OK;
+}
+
+int juno_seq_length(juno_seq *s, int32_t *n_tokens) {
+    JUNO_TRY(seq_check(s));
+    JUNO_REQUIRE(n_tokens, "n_tokens is null");
+    *n_tokens = s->len;
+    return JUNO_OK;
+}
+
+int juno_seq_append_kv(juno_seq *s, int32_t layer, int32_t pos, int32_t n_tokens, const float *k_host,
+                       const float *v_host) {
+    JUNO_TRY(seq_check(s));
+    juno_kvpool *p = s->pool;
+    juno_ctx *c = p->ctx;
+    JUNO_REQUIRE(k_host && v_host, "null K/V");
+    JUNO_REQUIRE(layer >= 0 && layer < p->n_layers, "layer %d out of range", layer);
+    JUNO_REQUIRE(pos >= 0 && n_tokens >= 0, "bad position range");
+    if (n_tokens == 0) return JUNO_OK;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_TRY(seq_reserve(s, pos + n_tokens, c->stream));
+    const int kvdim = p->n_kv_heads * p->head_dim;
+    const size_t bytes = (size_t)n_tokens * kvdim * sizeof(float);
+    void *px = c->stage_x, *py = c->stage_y;
+    JUNO_TRY(ensure_device(&px, &c->stage_x_bytes, bytes));
+    c->stage_x = (float *)px;
+    JUNO_TRY(ensure_device(&py, &c->stage_y_bytes, bytes));
+    c->stage_y = (float *)py;
+    JUNO_CUDA_TRY(cudaMemcpyAsync(c->stage_x, k_host, bytes, cudaMemcpyHostToDevice, c->stream));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(c->stage_y, v_host, bytes, cudaMemcpyHostToDevice, c->stream));
+    const size_t total = (size_t)n_tokens * kvdim;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    const int32_t *row = p->d_table + (size_t)s->slot * p->max_pages_per_seq;
+    if (p->dtype == 0)
+        kv_scatter_kernel<__half><<<blocks, 256, 0, c->stream>>>(p->k, p->v, row, p->n_pages, p->n_kv_heads, p->head_dim,
+                                                                  layer, pos, n_tokens, c->stage_x, c->stage_y);
+    else
+        kv_scatter_kernel<float><<<blocks, 256, 0, c->stream>>>(p->k, p->v, row, p->n_pages, p->n_kv_heads, p->head_dim,
+                                                                 layer, pos, n_tokens, c->stage_x, c->stage_y);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    c->kernel_launches++;
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->h2d_bytes += (int64_t)(2 * bytes);
+    s->len = std::max(s->len, pos + n_tokens);
+    return JUNO_OK;
+}
+
+int juno_attn_decode(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs, int32_t n_heads,
+                     const float *q_host, float *out_host) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(p && seqs && q_host && out_host, "null argument");
+    if (p->magic != kMagicPool) {
+        set_error("KV pool is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    JUNO_REQUIRE(p->ctx == c, "pool belongs to another context");
+    JUNO_REQUIRE(n >= 1 && n <= 4096, "n=%d out of range", n);
+    JUNO_REQUIRE(layer >= 0 && layer < p->n_layers, "layer %d out of range", layer);
+    JUNO_REQUIRE(n_heads > 0 && n_heads % p->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", n_heads,
+                 p->n_kv_heads);
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    int max_len = 0;
+    std::vector<int32_t> meta(2 * (size_t)n);
+    for (int i = 0; i < n; i++) {
+        JUNO_TRY(seq_check(seqs[i]));
+        JUNO_REQUIRE(seqs[i]->pool == p, "sequence %d belongs to another pool", i);
+        JUNO_REQUIRE(seqs[i]->len > 0, "sequence %d is empty", i);
+        meta[i] = seqs[i]->slot;
+        meta[n + i] = seqs[i]->len;
+        max_len = std::max(max_len, seqs[i]->len);
+    }
+    const int hd = p->head_dim, qdim = n_heads * hd;
+    const int n_splits = attn_pick_splits(c, n, p->n_kv_heads, max_len);
+    const size_t qbytes = (size_t)n * qdim * sizeof(float);
+    const size_t scratch = attn_scratch_floats(n, n_heads, hd, n_splits) * sizeof(float);
+    const size_t meta_bytes = meta.size() * sizeof(int32_t);
+    // stage_x: q | meta ; stage_y: out | scratch
+    const size_t qoff = (qbytes + 255) & ~(size_t)255;
+    void *px = c->stage_x, *py = c->stage_y;
+    JUNO_TRY(ensure_device(&px, &c->stage_x_bytes, qoff + meta_bytes));
+    c->stage_x = (float *)px;
+    JUNO_TRY(ensure_device(&py, &c->stage_y_bytes, qoff + scratch));
+    c->stage_y = (float *)py;
+    int32_t *d_meta = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(c->stage_x) + qoff);
+    JUNO_CUDA_TRY(cudaMemcpyAsync(c->stage_x, q_host, qbytes, cudaMemcpyHostToDevice, c->stream));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(d_meta, meta.data(), meta_bytes, cudaMemcpyHostToDevice, c->stream));
+    AttnArgs a;
+    a.pool = p;
+    a.layer = layer;
+    a.n = n;
+    a.n_heads = n_heads;
+    a.q = c->stage_x;
+    a.out = c->stage_y;
+    a.slots = d_meta;
+    a.seq_lens = d_meta + n;
+    a.n_splits = n_splits;
+    float *sc = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(c->stage_y) + qoff);
+    a.part_o = sc;
+    a.part_ml = sc + (size_t)n * n_heads * n_splits * hd;
+    JUNO_TRY(launch_attn(c, a, c->stream));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(out_host, c->stage_y, qbytes, cudaMemcpyDeviceToHost, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));  // meta (pageable host memory) is consumed by now
+    c->h2d_bytes += (int64_t)(qbytes + meta_bytes);
+    c->d2h_bytes += (int64_t)qbytes;
+    return JUNO_OK;
+}
+
+}  // extern "C"

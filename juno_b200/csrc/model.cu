@@ -1,0 +1,816 @@
+// Forward-pass operator: the device half of LlamaTransformerHandler.forward
+// (LlamaTransformerHandler.java:602-628,651-810) for n sequences per step, with real tensor
+// parallelism (column-parallel Q/K/V/gate/up, row-parallel O/down, vocab-parallel logits) in place of
+// the coordinator-side logits sum of TensorParallelPipelineClient.allReduceSum (:244-272).
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <vector>
+
+#include "attn.cuh"
+#include "common.cuh"
+#include "dequant.cuh"
+#include "gemv.cuh"
+
+namespace juno {
+
+// ───────────────────────────── NCCL, resolved at run time ─────────────────────────────────
+// Single-GPU hosts never load it.  In a process that already holds an NCCL (e.g. one rank per GPU under
+// torch.distributed) the soname resolves to that copy.
+struct NcclId {
+    char internal[128];
+};
+typedef struct ncclComm *NcclComm;
+struct NcclApi {
+    void *h = nullptr;
+    int (*GetUniqueId)(NcclId *) = nullptr;
+    int (*CommInitRank)(NcclComm *, int, NcclId, int) = nullptr;
+    int (*CommDestroy)(NcclComm) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+};
+static NcclApi g_nccl;
+static std::mutex g_nccl_mu;
+constexpr int kNcclFloat = 7, kNcclSum = 0;
+
+static int nccl_load() {
+    std::lock_guard<std::mutex> g(g_nccl_mu);
+    if (g_nccl.h) return JUNO_OK;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+        set_error("tensor parallelism needs libnccl.so.2: %s", dlerror());
+        return JUNO_ERR_NCCL;
+    }
+    g_nccl.GetUniqueId = (int (*)(NcclId *))dlsym(h, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (int (*)(NcclComm *, int, NcclId, int))dlsym(h, "ncclCommInitRank");
+    g_nccl.CommDestroy = (int (*)(NcclComm))dlsym(h, "ncclCommDestroy");
+    g_nccl.AllReduce =
+        (int (*)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t))dlsym(h, "ncclAllReduce");
+    g_nccl.AllGather = (int (*)(const void *, void *, size_t, int, NcclComm, cudaStream_t))dlsym(h, "ncclAllGather");
+    g_nccl.GetErrorString = (const char *(*)(int))dlsym(h, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.CommDestroy || !g_nccl.AllReduce || !g_nccl.AllGather) {
+        set_error("libnccl.so.2 lacks a required symbol");
+        return JUNO_ERR_NCCL;
+    }
+    g_nccl.h = h;
+    return JUNO_OK;
+}
+
+#define JUNO_NCCL_TRY(expr)                                                                         \
+    do {                                                                                            \
+        int _r = (expr);                                                                            \
+        if (_r != 0) {                                                                              \
+            set_error("%s failed: rc=%d (%s)", #expr, _r,                                           \
+                      g_nccl.GetErrorString ? g_nccl.GetErrorString(_r) : "?");                     \
+            return JUNO_ERR_NCCL;                                                                   \
+        }                                                                                           \
+    } while (0)
+
+// ───────────────────────────── small kernels ──────────────────────────────────────────────
+// Embedding row of the dequantised token_embd (getInitialActivation :651-660): token id clamped to
+// [0, vocab-1], values bit-exact with dequantizeQ4K & co.
+__global__ void embed_kernel(int type, int tiled, const uint8_t *w, int64_t nb, int64_t row_bytes, int hidden, int vocab,
+                             const int32_t *tokens, float *x) {
+    const int seq = blockIdx.y, col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= hidden) return;
+    int tok = tokens[seq];
+    tok = max(0, min(tok, vocab - 1));
+    float v;
+    if (tiled) {
+        const uint8_t *tile = w + (((int64_t)tok >> 4) * nb + (col >> 8)) * (int64_t)tile_bytes(type);
+        v = tile_elem_value(type, tile, tok & 15, col & 255);
+    } else {
+        v = raw_elem_value(type, w + (int64_t)tok * row_bytes, col);
+    }
+    x[(size_t)seq * hidden + col] = v;
+}
+
+// Element (seq, v) of the logits: plain [n][V], or, after an all-gather of vocab slices, [world][n][V/world].
+struct LogitsView {
+    const float *base;
+    int n, vocab, vloc;  // vloc == vocab: plain layout
+    __device__ __forceinline__ float at(int seq, int v) const {
+        if (vloc == vocab) return base[(size_t)seq * vocab + v];
+        const int r = v / vloc, j = v - r * vloc;
+        return base[((size_t)r * n + seq) * vloc + j];
+    }
+};
+
+constexpr int kArgmaxBlocks = 32;
+// First maximum (lowest index among equal values), as SampleStep.greedy (sampler/.../SampleStep.java:51-58)
+// picks after a monotone softmax.
+__global__ void argmax_partial_kernel(LogitsView lv, float *pval, int32_t *pidx) {
+    const int seq = blockIdx.y, blk = blockIdx.x;
+    const int per = (lv.vocab + kArgmaxBlocks - 1) / kArgmaxBlocks;
+    const int v0 = blk * per, v1 = min(lv.vocab, v0 + per);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+        const float x = lv.at(seq, v);
+        if (x > best || (x == best && v < bi)) {
+            best = x;
+            bi = v;
+        }
+    }
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    sv[threadIdx.x] = best;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s];
+            const int oi = si[threadIdx.x + s];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+                sv[threadIdx.x] = ov;
+                si[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        pval[seq * kArgmaxBlocks + blk] = sv[0];
+        pidx[seq * kArgmaxBlocks + blk] = si[0];
+    }
+}
+__global__ void argmax_final_kernel(const float *pval, const int32_t *pidx, int n, int32_t *out) {
+    const int seq = blockIdx.x * blockDim.x + threadIdx.x;
+    if (seq >= n) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int b = 0; b < kArgmaxBlocks; b++) {
+        const float v = pval[seq * kArgmaxBlocks + b];
+        const int i = pidx[seq * kArgmaxBlocks + b];
+        if (i != 0x7fffffff && (v > best || (v == best && i < bi))) {
+            best = v;
+            bi = i;
+        }
+    }
+    out[seq] = (bi == 0x7fffffff) ? 0 : bi;  // all-NaN logits: index 0, as a loop that never finds a larger value
+}
+
+// Greedy loop kept on the device: the picked token becomes the next input, one position further.
+__global__ void advance_kernel(int n, const int32_t *picked, int32_t *tokens, int32_t *positions, int32_t *seq_lens,
+                               int32_t *out_ids, int32_t *step_counter) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int step = *step_counter;
+    if (i < n) {
+        tokens[i] = picked[i];
+        positions[i] += 1;
+        seq_lens[i] += 1;
+        out_ids[(size_t)step * n + i] = picked[i];
+    }
+    __syncthreads();
+    if (i == 0) *step_counter = step + 1;
+}
+
+// [world][n][vloc] -> [n][vocab]
+__global__ void ungather_logits_kernel(LogitsView lv, float *out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)lv.n * lv.vocab) return;
+    const int seq = (int)(idx / lv.vocab), v = (int)(idx - (size_t)seq * lv.vocab);
+    out[idx] = lv.at(seq, v);
+}
+
+}  // namespace juno
+
+// ───────────────────────────── model object ───────────────────────────────────────────────
+struct JunoLayer {
+    juno_qmat *w[12] = {nullptr};  // indexed by tensor kind (ATTN_Q .. FFN_DOWN)
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+};
+
+struct JunoGraph {
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+    int seen = 0;
+};
+
+struct juno_model {
+    uint32_t magic;
+    juno_ctx *ctx;
+    juno_model_cfg cfg;
+    int hd, world, rank;
+    int heads_loc, kv_loc, inter_loc, vocab_loc;  // this rank's share
+    int qkv_ld;
+    bool finalized = false;
+    bool vocab_sharded = false;
+    std::vector<JunoLayer> layers;
+    juno_qmat *tok_embd = nullptr, *output = nullptr;
+    bool output_is_embd = false, output_slice_of_embd = false;
+    float *output_norm = nullptr;
+    juno_kvpool *pool = nullptr;
+    juno::NcclComm comm = nullptr;
+    // activations
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *gu = nullptr;
+    float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
+    float *attn_scratch = nullptr;
+    size_t attn_scratch_floats = 0;
+    float2 *rope_cs = nullptr;
+    int32_t *d_step = nullptr;  // tokens | positions | slots | seq_lens, max_batch each
+    int32_t *d_argmax = nullptr, *d_pidx = nullptr, *d_out_ids = nullptr, *d_step_counter = nullptr;
+    float *d_pval = nullptr;
+    int out_ids_cap = 0;
+    int32_t *h_step = nullptr;  // pinned mirror of d_step
+    int last_n = 0, last_x = 0;
+    std::map<uint64_t, JunoGraph> graphs;
+    bool use_graphs = true;
+};
+
+namespace juno {
+
+static int model_check(juno_model *m) {
+    if (!m) {
+        set_error("model is null");
+        return JUNO_ERR_INVALID_ARG;
+    }
+    if (m->magic != kMagicModel) {
+        set_error("model handle is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    return JUNO_OK;
+}
+
+static int dev_alloc(void **p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 4);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        return JUNO_ERR_OOM;
+    }
+    return JUNO_OK;
+}
+
+static int upload_f32_vector(juno_ctx *c, const void *blocks, int type, int64_t rows, int64_t cols, int want, float **dst) {
+    JUNO_REQUIRE(type == JUNO_TYPE_F32, "norm weights must be F32 (got GGML type %d)", type);
+    JUNO_REQUIRE(rows * cols == want, "norm weight has %lld elements, expected %d", (long long)(rows * cols), want);
+    if (*dst) cudaFree(*dst);
+    *dst = nullptr;
+    JUNO_TRY(dev_alloc((void **)dst, (size_t)want * 4));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(*dst, blocks, (size_t)want * 4, cudaMemcpyHostToDevice, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->h2d_bytes += want * 4;
+    return JUNO_OK;
+}
+
+static void free_qmat(juno_qmat *&q) {
+    if (q) {
+        qmat_destroy(q);
+        delete q;
+        q = nullptr;
+    }
+}
+
+static void model_release(juno_model *m) {
+    juno_ctx *c = m->ctx;
+    DeviceGuard g(c->device);
+    cudaStreamSynchronize(c->stream);
+    for (auto &kv : m->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    m->graphs.clear();
+    if (m->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(m->comm);
+    m->comm = nullptr;
+    for (auto &L : m->layers) {
+        for (int k = 0; k < 12; k++) free_qmat(L.w[k]);
+        if (L.attn_norm) cudaFree(L.attn_norm);
+        if (L.ffn_norm) cudaFree(L.ffn_norm);
+    }
+    m->layers.clear();
+    if (m->output_is_embd) m->output = nullptr;
+    free_qmat(m->output);
+    free_qmat(m->tok_embd);
+    if (m->pool) {
+        m->pool->owned_by_model = 0;
+        kvpool_destroy(m->pool);
+    }
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->gu, m->logits_loc, m->logits_gather, m->logits_full,
+                    m->attn_scratch, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
+                    m->d_pval, m->output_norm};
+    for (void *b : bufs)
+        if (b) cudaFree(b);
+    if (m->h_step) cudaFreeHost(m->h_step);
+    m->magic = kMagicDead;
+}
+
+}  // namespace juno
+
+using namespace juno;
+
+extern "C" {
+
+int juno_nccl_unique_id(uint8_t *out128) {
+    JUNO_REQUIRE(out128, "out is null");
+    JUNO_TRY(nccl_load());
+    NcclId id;
+    JUNO_NCCL_TRY(g_nccl.GetUniqueId(&id));
+    memcpy(out128, id.internal, 128);
+    return JUNO_OK;
+}
+
+int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(cfg && out, "null argument");
+    JUNO_REQUIRE(cfg->struct_size == (int32_t)sizeof(juno_model_cfg), "juno_model_cfg.struct_size is %d, expected %d",
+                 cfg->struct_size, (int)sizeof(juno_model_cfg));
+    JUNO_REQUIRE(cfg->hidden > 0 && cfg->n_layers > 0 && cfg->n_heads > 0 && cfg->n_kv_heads > 0 && cfg->inter > 0 &&
+                     cfg->vocab > 0,
+                 "model dimensions must be positive");
+    JUNO_REQUIRE(cfg->hidden % cfg->n_heads == 0, "hidden %d is not a multiple of n_heads %d", cfg->hidden, cfg->n_heads);
+    JUNO_REQUIRE(cfg->n_heads % cfg->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", cfg->n_heads,
+                 cfg->n_kv_heads);
+    JUNO_REQUIRE(cfg->max_batch >= 1 && cfg->max_batch <= 1024 && cfg->max_seqs >= 1 && cfg->max_ctx >= 1,
+                 "max_batch/max_seqs/max_ctx out of range");
+    JUNO_REQUIRE(cfg->tp_world >= 1 && cfg->tp_rank >= 0 && cfg->tp_rank < cfg->tp_world,
+                 "tensorRank (%d) must be < tensorWorldSize (%d)", cfg->tp_rank, cfg->tp_world);
+    const int hd = cfg->hidden / cfg->n_heads, w = cfg->tp_world;
+    JUNO_REQUIRE(hd == 64 || hd == 128, "head_dim %d is not supported (64, 128)", hd);
+    JUNO_REQUIRE(cfg->hidden % 256 == 0 && cfg->inter % 256 == 0, "hidden and feed_forward_length must be multiples of 256");
+    if (w > 1) {
+        // geometry of TensorShardContext (:74-100): headsPerNode = numHeads / world, sliceDim = hidden / world
+        JUNO_REQUIRE(cfg->n_heads % 2 == 0, "numHeads (%d) must be divisible by 2 for tensor-parallel mode", cfg->n_heads);
+        JUNO_REQUIRE(cfg->n_heads % w == 0 && cfg->n_kv_heads % w == 0,
+                     "heads (%d query, %d kv) do not divide over %d ranks", cfg->n_heads, cfg->n_kv_heads, w);
+        JUNO_REQUIRE((cfg->hidden / w) % 256 == 0 && (cfg->inter / w) % 256 == 0 && cfg->inter % w == 0,
+                     "hidden/world and feed_forward_length/world must be multiples of 256 (whole super-blocks)");
+    }
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    juno_model *m = new juno_model();
+    m->magic = kMagicModel;
+    m->ctx = c;
+    m->cfg = *cfg;
+    m->hd = hd;
+    m->world = w;
+    m->rank = cfg->tp_rank;
+    m->heads_loc = cfg->n_heads / w;
+    m->kv_loc = cfg->n_kv_heads / w;
+    m->inter_loc = cfg->inter / w;
+    m->vocab_sharded = (w > 1) && (cfg->vocab % w == 0);
+    m->vocab_loc = m->vocab_sharded ? cfg->vocab / w : cfg->vocab;
+    m->qkv_ld = (m->heads_loc + 2 * m->kv_loc) * hd;
+    m->layers.resize(cfg->n_layers);
+    const char *ng = getenv("JUNO_NO_GRAPH");
+    m->use_graphs = !(ng && *ng == '1');
+    if (w > 1) {
+        int rc = nccl_load();
+        if (rc == JUNO_OK) {
+            NcclId id;
+            memcpy(id.internal, cfg->nccl_id, 128);
+            int r = g_nccl.CommInitRank(&m->comm, w, id, cfg->tp_rank);
+            if (r != 0) {
+                set_error("ncclCommInitRank failed: rc=%d (%s)", r, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "?");
+                rc = JUNO_ERR_NCCL;
+            }
+        }
+        if (rc != JUNO_OK) {
+            m->magic = kMagicDead;
+            delete m;
+            return rc;
+        }
+    }
+    *out = m;
+    return JUNO_OK;
+}
+
+int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void *blocks, int32_t type, int64_t rows,
+                          int64_t cols) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(blocks, "blocks is null");
+    JUNO_REQUIRE(!m->finalized, "model is already finalized");
+    JUNO_REQUIRE(kind >= 0 && kind <= JUNO_T_FFN_DOWN, "unknown tensor kind %d", kind);
+    juno_ctx *c = m->ctx;
+    const juno_model_cfg &f = m->cfg;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    const int H = f.hidden, I = f.inter, V = f.vocab, hd = m->hd, r = m->rank;
+    if (kind == JUNO_T_OUTPUT_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->output_norm);
+    if (kind > JUNO_T_OUTPUT) JUNO_REQUIRE(layer >= 0 && layer < f.n_layers, "layer %d out of range", layer);
+    if (kind == JUNO_T_ATTN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].attn_norm);
+    if (kind == JUNO_T_FFN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].ffn_norm);
+
+    int64_t want_rows = 0, want_cols = 0, row0 = 0, nrows = 0, sb0 = 0, nsb = 0;
+    switch (kind) {
+    case JUNO_T_TOKEN_EMBD: want_rows = V; want_cols = H; row0 = 0; nrows = V; break;
+    case JUNO_T_OUTPUT: want_rows = V; want_cols = H; row0 = m->vocab_sharded ? (int64_t)r * m->vocab_loc : 0; nrows = m->vocab_loc; break;
+    case JUNO_T_ATTN_Q: want_rows = H; want_cols = H; row0 = (int64_t)r * m->heads_loc * hd; nrows = m->heads_loc * hd; break;
+    case JUNO_T_ATTN_K:
+    case JUNO_T_ATTN_V: want_rows = f.n_kv_heads * hd; want_cols = H; row0 = (int64_t)r * m->kv_loc * hd; nrows = m->kv_loc * hd; break;
+    case JUNO_T_ATTN_OUT: want_rows = H; want_cols = H; nrows = H; sb0 = (int64_t)r * m->heads_loc * hd / 256; nsb = m->heads_loc * hd / 256; break;
+    case JUNO_T_FFN_GATE:
+    case JUNO_T_FFN_UP: want_rows = I; want_cols = H; row0 = (int64_t)r * m->inter_loc; nrows = m->inter_loc; break;
+    case JUNO_T_FFN_DOWN: want_rows = H; want_cols = I; nrows = H; sb0 = (int64_t)r * m->inter_loc / 256; nsb = m->inter_loc / 256; break;
+    default: break;
+    }
+    JUNO_REQUIRE(rows == want_rows && cols == want_cols, "tensor kind %d has shape %lldx%lld, expected %lldx%lld", kind,
+                 (long long)rows, (long long)cols, (long long)want_rows, (long long)want_cols);
+    if (kind != JUNO_T_TOKEN_EMBD)
+        JUNO_REQUIRE(type == JUNO_TYPE_Q4_K || type == JUNO_TYPE_Q6_K || type == JUNO_TYPE_Q8_0,
+                     "projection weights must be Q4_K, Q6_K or Q8_0 (got GGML type %d)", type);
+    if (m->world == 1) sb0 = nsb = 0;
+    juno_qmat **slot = kind == JUNO_T_TOKEN_EMBD ? &m->tok_embd : kind == JUNO_T_OUTPUT ? &m->output : &m->layers[layer].w[kind];
+    free_qmat(*slot);
+    JUNO_TRY(qmat_create(c, blocks, type, rows, cols, row0, nrows, sb0, nsb, slot));
+    if (kind == JUNO_T_OUTPUT) m->output_slice_of_embd = false;
+    if (kind == JUNO_T_TOKEN_EMBD && m->vocab_sharded && (!m->output || m->output_slice_of_embd)) {
+        // tied embeddings under vocab sharding: this rank's output projection is a row slice of token_embd
+        if (type == JUNO_TYPE_Q4_K || type == JUNO_TYPE_Q6_K || type == JUNO_TYPE_Q8_0) {
+            free_qmat(m->output);
+            JUNO_TRY(qmat_create(c, blocks, type, rows, cols, (int64_t)r * m->vocab_loc, m->vocab_loc, 0, 0, &m->output));
+            m->output_slice_of_embd = true;
+        }
+    }
+    return JUNO_OK;
+}
+
+}  // extern "C"
+
+// ───────────────────────────── finalize ───────────────────────────────────────────────────
+extern "C" int juno_model_finalize(juno_model *m) {
+    JUNO_TRY(model_check(m));
+    if (m->finalized) return JUNO_OK;
+    juno_ctx *c = m->ctx;
+    const juno_model_cfg &f = m->cfg;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_REQUIRE(m->tok_embd && m->output_norm, "token_embd.weight and output_norm.weight are required");
+    if (!m->output) {  // tied embeddings (LlamaTransformerHandler.java:463-470)
+        JUNO_REQUIRE(m->tok_embd->tiled, "a tied output projection needs a Q4_K/Q6_K/Q8_0 token_embd");
+        m->output = m->tok_embd;
+        m->output_is_embd = true;
+    }
+    for (int l = 0; l < f.n_layers; l++) {
+        JunoLayer &L = m->layers[l];
+        JUNO_REQUIRE(L.attn_norm && L.ffn_norm, "layer %d: norm weights missing", l);
+        for (int k = JUNO_T_ATTN_Q; k <= JUNO_T_FFN_DOWN; k++) JUNO_REQUIRE(L.w[k], "layer %d: tensor kind %d missing", l, k);
+    }
+    const int B = f.max_batch, H = f.hidden, hd = m->hd;
+    const int max_pages_per_seq = (f.max_ctx + kPageTokens - 1) / kPageTokens;
+    const long long want_pages = (long long)f.max_seqs * max_pages_per_seq;
+    JUNO_REQUIRE(want_pages < (1ll << 31), "KV pool too large");
+    JUNO_TRY(kvpool_create(c, f.n_layers, m->kv_loc, hd, (int)want_pages, f.kv_dtype, f.max_seqs, max_pages_per_seq,
+                           &m->pool));
+    m->pool->owned_by_model = 1;
+    JUNO_TRY(dev_alloc((void **)&m->x[0], (size_t)B * H * 4));
+    JUNO_TRY(dev_alloc((void **)&m->x[1], (size_t)B * H * 4));
+    JUNO_TRY(dev_alloc((void **)&m->qkv, (size_t)B * m->qkv_ld * 4));
+    JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
+    JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
+    JUNO_TRY(dev_alloc((void **)&m->gu, (size_t)B * 2 * m->inter_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->logits_loc, (size_t)B * m->vocab_loc * 4));
+    if (m->vocab_sharded) {
+        JUNO_TRY(dev_alloc((void **)&m->logits_gather, (size_t)B * f.vocab * 4));
+        JUNO_TRY(dev_alloc((void **)&m->logits_full, (size_t)B * f.vocab * 4));
+    }
+    m->attn_scratch_floats = (size_t)(c->sm_count * 4 + B * m->kv_loc) * (m->heads_loc / m->kv_loc) * (hd + 2) + 64;
+    JUNO_TRY(dev_alloc((void **)&m->attn_scratch, m->attn_scratch_floats * 4));
+    JUNO_TRY(dev_alloc((void **)&m->rope_cs, (size_t)B * (hd / 2) * sizeof(float2)));
+    JUNO_TRY(dev_alloc((void **)&m->d_step, (size_t)4 * B * 4));
+    JUNO_TRY(dev_alloc((void **)&m->d_argmax, (size_t)B * 4));
+    JUNO_TRY(dev_alloc((void **)&m->d_pidx, (size_t)B * kArgmaxBlocks * 4));
+    JUNO_TRY(dev_alloc((void **)&m->d_pval, (size_t)B * kArgmaxBlocks * 4));
+    JUNO_TRY(dev_alloc((void **)&m->d_step_counter, 4));
+    JUNO_CUDA_TRY(cudaMallocHost((void **)&m->h_step, (size_t)4 * B * 4));
+    m->finalized = true;
+    return JUNO_OK;
+}
+
+namespace juno {
+
+// ───────────────────────────── one decode step, enqueued on the context stream ────────────
+static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, int ld_out, int batch,
+                      const GemvArgs &proto, cudaStream_t st) {
+    // consecutive matrices of one block format share a launch (they share the staged activation)
+    int i = 0;
+    while (i < count) {
+        int j = i + 1;
+        while (j < count && j - i < 3 && mats[j]->type == mats[i]->type) j++;
+        GemvArgs a = proto;
+        a.nseg = j - i;
+        for (int s = 0; s < a.nseg; s++) {
+            a.seg[s].w = mats[i + s]->dev;
+            a.seg[s].out = outs[i + s];
+            a.seg[s].rows = (int)mats[i + s]->rows;
+            a.seg[s].row_tiles = (int)mats[i + s]->row_tiles;
+        }
+        a.type = mats[i]->type;
+        a.K = (int)mats[i]->cols;
+        a.batch = batch;
+        a.ld_out = ld_out;
+        if (i > 0) a.x_out = nullptr;  // the residual stream is written once
+        JUNO_TRY(launch_gemv(m->ctx, a, st));
+        i = j;
+    }
+    return JUNO_OK;
+}
+
+static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
+    juno_ctx *c = m->ctx;
+    const juno_model_cfg &f = m->cfg;
+    const int H = f.hidden, hd = m->hd, B = f.max_batch;
+    const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
+    const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
+
+    // embedding lookup -> x[0]
+    {
+        juno_qmat *e = m->tok_embd;
+        dim3 grid((H + 255) / 256, n);
+        int64_t rb = e->tiled ? 0 : e->cols / raw_block_elems(e->type) * raw_block_bytes(e->type);
+        embed_kernel<<<grid, 256, 0, st>>>(e->type, e->tiled, e->dev, e->nb, rb, H, f.vocab, d_tok, m->x[0]);
+        JUNO_CUDA_TRY(cudaGetLastError());
+        c->kernel_launches++;
+    }
+    JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
+
+    int cur = 0;                   // x[cur] holds the residual stream entering the layer
+    const float *pending = nullptr; // projection still to be added to it (fused into the next RMSNorm prologue)
+    for (int l = 0; l < f.n_layers; l++) {
+        JunoLayer &L = m->layers[l];
+        // xn = rmsNorm(x (+ pending)); q,k,v = W·xn
+        GemvArgs a;
+        a.pro = PRO_RMSNORM;
+        a.x = m->x[cur];
+        a.ldx = H;
+        a.x_add = pending;
+        a.x_out = pending ? m->x[cur ^ 1] : nullptr;
+        a.normw = L.attn_norm;
+        a.eps = f.rms_eps;
+        juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
+        float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
+        JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, m->qkv_ld, n, a, st));
+        if (pending) cur ^= 1;
+        JUNO_TRY(launch_rope_append(c, m->pool, l, n, m->heads_loc, m->qkv, m->qkv_ld, m->qkv + Hl, m->qkv + Hl + KVl,
+                                    m->qkv_ld, d_slot, d_pos, m->rope_cs, st));
+        AttnArgs at;
+        at.pool = m->pool;
+        at.layer = l;
+        at.n = n;
+        at.n_heads = m->heads_loc;
+        at.q = m->qkv;
+        at.ldq = m->qkv_ld;
+        at.out = m->att;
+        at.slots = d_slot;
+        at.seq_lens = d_len;
+        at.n_splits = n_splits;
+        at.part_o = m->attn_scratch;
+        at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
+        JUNO_TRY(launch_attn(c, at, st));
+        // proj = Wo·att  (row-parallel under TP: partial sums, all-reduced)
+        GemvArgs o;
+        o.pro = PRO_PLAIN;
+        o.x = m->att;
+        o.ldx = Hl;
+        juno_qmat *o_m[1] = {L.w[JUNO_T_ATTN_OUT]};
+        float *o_o[1] = {m->proj};
+        JUNO_TRY(gemv_group(m, o_m, o_o, 1, H, n, o, st));
+        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        // x2 = x + proj ; xn2 = rmsNorm(x2) ; gate, up = W·xn2
+        GemvArgs gu;
+        gu.pro = PRO_RMSNORM;
+        gu.x = m->x[cur];
+        gu.ldx = H;
+        gu.x_add = m->proj;
+        gu.x_out = m->x[cur ^ 1];
+        gu.normw = L.ffn_norm;
+        gu.eps = f.rms_eps;
+        juno_qmat *gu_m[2] = {L.w[JUNO_T_FFN_GATE], L.w[JUNO_T_FFN_UP]};
+        float *gu_o[2] = {m->gu, m->gu + Il};
+        JUNO_TRY(gemv_group(m, gu_m, gu_o, 2, 2 * Il, n, gu, st));
+        cur ^= 1;
+        // proj = Wdown·(silu(gate)*up)
+        GemvArgs d;
+        d.pro = PRO_SILU;
+        d.x = m->gu;
+        d.up = m->gu + Il;
+        d.ldx = 2 * Il;
+        juno_qmat *d_m[1] = {L.w[JUNO_T_FFN_DOWN]};
+        float *d_o[1] = {m->proj};
+        JUNO_TRY(gemv_group(m, d_m, d_o, 1, H, n, d, st));
+        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        pending = m->proj;
+    }
+    // logits = Wout · rmsNorm(x + pending, output_norm)
+    GemvArgs lo;
+    lo.pro = PRO_RMSNORM;
+    lo.x = m->x[cur];
+    lo.ldx = H;
+    lo.x_add = pending;
+    lo.x_out = m->x[cur ^ 1];
+    lo.normw = m->output_norm;
+    lo.eps = f.rms_eps;
+    juno_qmat *l_m[1] = {m->output};
+    float *l_o[1] = {m->logits_loc};
+    JUNO_TRY(gemv_group(m, l_m, l_o, 1, m->vocab_loc, n, lo, st));
+    m->last_x = cur ^ 1;
+    LogitsView lv;
+    lv.n = n;
+    lv.vocab = f.vocab;
+    if (m->vocab_sharded) {
+        JUNO_NCCL_TRY(g_nccl.AllGather(m->logits_loc, m->logits_gather, (size_t)n * m->vocab_loc, kNcclFloat, m->comm, st));
+        lv.base = m->logits_gather;
+        lv.vloc = m->vocab_loc;
+    } else {
+        lv.base = m->logits_loc;
+        lv.vloc = f.vocab;
+    }
+    argmax_partial_kernel<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(lv, m->d_pval, m->d_pidx);
+    argmax_final_kernel<<<(n + 63) / 64, 64, 0, st>>>(m->d_pval, m->d_pidx, n, m->d_argmax);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    c->kernel_launches += 2;
+    if (greedy_advance) {
+        advance_kernel<<<1, std::max(32, (n + 31) / 32 * 32), 0, st>>>(n, m->d_argmax, m->d_step, m->d_step + B,
+                                                                      m->d_step + 3 * B, m->d_out_ids, m->d_step_counter);
+        JUNO_CUDA_TRY(cudaGetLastError());
+        c->kernel_launches++;
+    }
+    return JUNO_OK;
+}
+
+// Runs one step: the first call for a (n, splits, mode) key runs eagerly (it also sizes every scratch
+// buffer); the second captures the same launches into a CUDA graph, later ones replay it.
+static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
+    juno_ctx *c = m->ctx;
+    cudaStream_t st = c->stream;
+    if (!m->use_graphs) return enqueue_step(m, n, n_splits, greedy_advance, st);
+    const uint64_t key = ((uint64_t)n << 32) | ((uint64_t)n_splits << 1) | (greedy_advance ? 1u : 0u);
+    JunoGraph &g = m->graphs[key];
+    if (g.exec) {
+        JUNO_CUDA_TRY(cudaGraphLaunch(g.exec, st));
+        c->kernel_launches += g.launches;
+        return JUNO_OK;
+    }
+    if (!g.seen) {
+        g.seen = 1;
+        return enqueue_step(m, n, n_splits, greedy_advance, st);
+    }
+    const int64_t before = c->kernel_launches.load();
+    JUNO_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_step(m, n, n_splits, greedy_advance, st);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(st, &graph);
+    const int launches = (int)(c->kernel_launches.load() - before);
+    c->kernel_launches = before;
+    if (rc != JUNO_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (e != cudaSuccess || !graph) {
+        set_error("graph capture failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return JUNO_ERR_CUDA;
+    }
+    e = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        g.exec = nullptr;
+        set_error("cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+        return JUNO_ERR_CUDA;
+    }
+    g.launches = launches;
+    JUNO_CUDA_TRY(cudaGraphLaunch(g.exec, st));
+    c->kernel_launches += launches;
+    return JUNO_OK;
+}
+
+static int bucket_len(int len) {
+    int b = 64;
+    while (b < len) b <<= 1;
+    return b;
+}
+
+// Validates the step, reserves pages and ships (tokens, positions, slots, lengths) to the device.
+static int prepare_step(juno_model *m, int n, juno_seq *const *seqs, const int32_t *tokens, const int32_t *positions,
+                        int extra_positions, int *n_splits) {
+    juno_ctx *c = m->ctx;
+    const int B = m->cfg.max_batch;
+    JUNO_REQUIRE(m->finalized, "model is not finalized");
+    JUNO_REQUIRE(n >= 1 && n <= B, "n=%d outside [1, max_batch=%d]", n, B);
+    JUNO_REQUIRE(seqs && tokens && positions, "null argument");
+    int max_len = 0;
+    for (int i = 0; i < n; i++) {
+        juno_seq *s = seqs[i];
+        JUNO_REQUIRE(s && s->magic == kMagicSeq && s->pool == m->pool, "sequence %d is closed or belongs to another model", i);
+        for (int j = 0; j < i; j++) JUNO_REQUIRE(seqs[j] != s, "sequence listed twice in one step");
+        JUNO_REQUIRE(positions[i] >= 0 && positions[i] + extra_positions < m->cfg.max_ctx,
+                     "position %d is beyond max_ctx %d", positions[i] + extra_positions, m->cfg.max_ctx);
+        JUNO_TRY(seq_reserve(s, positions[i] + 1 + extra_positions, c->stream));
+        m->h_step[i] = tokens[i];
+        m->h_step[B + i] = positions[i];
+        m->h_step[2 * B + i] = s->slot;
+        m->h_step[3 * B + i] = positions[i] + 1;
+        max_len = std::max(max_len, positions[i] + 1 + extra_positions);
+    }
+    *n_splits = attn_pick_splits(c, n, m->kv_loc, bucket_len(max_len));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(m->d_step, m->h_step, (size_t)4 * B * 4, cudaMemcpyHostToDevice, c->stream));
+    c->h2d_bytes += 4 * n * 4;
+    return JUNO_OK;
+}
+
+}  // namespace juno
+
+extern "C" {
+
+int juno_model_seq_create(juno_model *m, juno_seq **out) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(out, "out is null");
+    JUNO_REQUIRE(m->finalized, "model is not finalized");
+    std::lock_guard<std::recursive_mutex> lk(m->ctx->mu);
+    return seq_create(m->pool, m->cfg.max_ctx, out);
+}
+
+int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *token_ids, const int32_t *positions,
+                 float *logits_host, int32_t *argmax_out) {
+    JUNO_TRY(model_check(m));
+    juno_ctx *c = m->ctx;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    // the pinned step buffer is reused: the previous step must have consumed it
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    int n_splits = 1;
+    JUNO_TRY(prepare_step(m, n, seqs, token_ids, positions, 0, &n_splits));
+    JUNO_TRY(run_step(m, n, n_splits, false));
+    c->forward_calls++;
+    const int V = m->cfg.vocab;
+    if (logits_host) {
+        const float *src = m->logits_loc;
+        if (m->vocab_sharded) {
+            LogitsView lv{m->logits_gather, n, V, m->vocab_loc};
+            size_t tot = (size_t)n * V;
+            ungather_logits_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(lv, m->logits_full);
+            JUNO_CUDA_TRY(cudaGetLastError());
+            c->kernel_launches++;
+            src = m->logits_full;
+        }
+        JUNO_CUDA_TRY(cudaMemcpyAsync(logits_host, src, (size_t)n * V * 4, cudaMemcpyDeviceToHost, c->stream));
+        c->d2h_bytes += (int64_t)n * V * 4;
+    }
+    if (argmax_out) {
+        JUNO_CUDA_TRY(cudaMemcpyAsync(argmax_out, m->d_argmax, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
+        c->d2h_bytes += n * 4;
+    }
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + 1);
+    m->last_n = n;
+    return JUNO_OK;
+}
+
+int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *first_tokens,
+                       const int32_t *positions, int32_t steps, int32_t *out_ids) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(steps >= 1 && steps <= 65536 && out_ids, "bad steps/out_ids");
+    juno_ctx *c = m->ctx;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    int n_splits = 1;
+    JUNO_TRY(prepare_step(m, n, seqs, first_tokens, positions, steps - 1, &n_splits));
+    const int need = steps * m->cfg.max_batch;
+    if (need > m->out_ids_cap) {
+        if (m->d_out_ids) cudaFree(m->d_out_ids);
+        m->d_out_ids = nullptr;
+        m->out_ids_cap = 0;
+        JUNO_TRY(dev_alloc((void **)&m->d_out_ids, (size_t)need * 4));
+        m->out_ids_cap = need;
+        // the buffer address is baked into captured graphs of the greedy mode
+        for (auto it = m->graphs.begin(); it != m->graphs.end();) {
+            if (it->first & 1u) {
+                if (it->second.exec) cudaGraphExecDestroy(it->second.exec);
+                it = m->graphs.erase(it);
+            } else
+                ++it;
+        }
+    }
+    JUNO_CUDA_TRY(cudaMemsetAsync(m->d_step_counter, 0, 4, c->stream));
+    for (int s = 0; s < steps; s++) JUNO_TRY(run_step(m, n, n_splits, true));
+    c->forward_calls += steps;
+    JUNO_CUDA_TRY(cudaMemcpyAsync(out_ids, m->d_out_ids, (size_t)steps * n * 4, cudaMemcpyDeviceToHost, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->d2h_bytes += (int64_t)steps * n * 4;
+    for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + steps);
+    m->last_n = n;
+    return JUNO_OK;
+}
+
+int juno_model_last_hidden(juno_model *m, int32_t n, float *hidden_host) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(hidden_host && n >= 1 && n <= m->last_n, "no forward result for %d sequences", n);
+    juno_ctx *c = m->ctx;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_CUDA_TRY(cudaMemcpyAsync(hidden_host, m->x[m->last_x], (size_t)n * m->cfg.hidden * 4, cudaMemcpyDeviceToHost,
+                                  c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return JUNO_OK;
+}
+
+int juno_model_free(juno_model *m) {
+    JUNO_TRY(model_check(m));
+    std::lock_guard<std::recursive_mutex> lk(m->ctx->mu);
+    model_release(m);
+    return JUNO_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,84 @@
+"""CPU checks of the product library: it loads, exports every symbol the header declares, and its
+tile layout round-trips bit-exactly (host mirrors of the device repack / dequantise index maps)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from juno_b200 import _lib, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.load()
+    hdr = open(os.path.join(ROOT, "include", "juno_b200.h")).read()
+    declared = set(re.findall(r"\b(juno_[a-z0-9_]+)\s*\(", hdr))
+    assert len(declared) >= 30
+    for name in declared:
+        assert hasattr(L, name), name
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_cfg_struct_matches_header():
+    assert C.sizeof(_lib.ModelCfg) == 4 * 15 + 128
+    assert C.sizeof(_lib.Counters) == 40
+
+
+def test_device_probe_fails_soft():
+    n = C.c_int32(-1)
+    assert _lib.load().juno_device_count(C.byref(n)) == _lib.OK and n.value >= 0
+    if n.value == 0:  # no GPU: the context refuses loudly, there is no CPU fallback
+        h = C.c_void_p()
+        assert _lib.load().juno_ctx_create(0, C.byref(h)) == _lib.ERR_CUDA
+        assert "no CPU fallback" in _lib.last_error()
+
+
+def test_null_and_closed_handles_return_codes():
+    L = _lib.load()
+    assert L.juno_qmat_free(None) == _lib.ERR_INVALID_ARG
+    assert L.juno_ctx_destroy(None) == _lib.ERR_INVALID_ARG
+    assert L.juno_model_free(None) == _lib.ERR_INVALID_ARG
+    assert L.juno_seq_free(None) == _lib.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("t", [synth.Q4_K, synth.Q6_K, synth.Q8_0])
+@pytest.mark.parametrize("rows,cols", [(16, 256), (37, 512), (5, 1024)])
+def test_tile_layout_round_trip_bit_exact(oracle, t, rows, cols):
+    L = C.CDLL(_lib.LIB_PATH)
+    L.juno_dbg_tiled_bytes.restype = C.c_int64
+    L.juno_dbg_tiled_bytes.argtypes = [C.c_int, C.c_int64, C.c_int64]
+    L.juno_dbg_repack_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    L.juno_dbg_dequant_tiled_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    raw = synth.random_blocks(np.random.default_rng(t), t, rows, cols)
+    n = L.juno_dbg_tiled_bytes(t, rows, cols)
+    assert n == ((rows + 15) // 16) * (cols // 256) * {12: 2304, 14: 3360, 8: 4352}[t]
+    tiles = np.zeros(n, dtype=np.uint8)
+    assert L.juno_dbg_repack_host(t, raw.ctypes.data, rows, cols, tiles.ctypes.data) == 0
+    out = np.empty((rows, cols), dtype=np.float32)
+    assert L.juno_dbg_dequant_tiled_host(t, tiles.ctypes.data, rows, cols, out.ctypes.data) == 0
+    ref = oracle.dequantize(t, raw, rows, cols)
+    assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+
+
+def test_synthetic_block_distributions(oracle):
+    rng = np.random.default_rng(0)
+    raw = synth.random_blocks(rng, synth.Q4_K, 64, 1024).reshape(-1, 144)
+    d = raw[:, 0:2].copy().view(np.float16).astype(np.float32)
+    assert 1e-3 * 0.99 <= d.min() and d.max() <= 2e-2 * 1.01
+    sc = np.array([[oracle.lib().jo_q4k_scale(np.ascontiguousarray(b[4:16]).ctypes.data, j) for j in range(8)] for b in raw[:50]])
+    assert sc.min() >= 0 and sc.max() <= 63 and sc.max() > 40
+    q8 = synth.random_blocks(rng, synth.Q8_0, 8, 256).reshape(-1, 34)[:, 2:].view(np.int8)
+    assert q8.min() >= -127 and q8.max() <= 127
+
+
+def test_tensor_shard_context_geometry():
+    from juno_b200.handler import TensorShardContext
+    c = TensorShardContext(num_heads=32, hidden_dim=4096, tensor_rank=3, tensor_world_size=8)
+    assert (c.heads_per_node(), c.head_start(), c.head_end(), c.head_dim(), c.slice_dim()) == (4, 12, 16, 128, 512)
+    with pytest.raises(ValueError):
+        TensorShardContext(32, 4096, 8, 8)
+    with pytest.raises(ValueError):
+        TensorShardContext(31, 4096, 0, 1)

@@ -1,0 +1,129 @@
+"""Forward-pass operator vs the oracle: logits within 1e-3 relative, greedy ids identical."""
+import numpy as np
+import pytest
+
+from conftest import rel_err
+from juno_b200 import synth
+from juno_b200.handler import B200InferencePipeline, ForwardRequest, generate_greedy
+from modelutil import SMALL128, TINY, build_pair
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+@pytest.mark.parametrize("arch", [TINY, SMALL128], ids=["hd64", "hd128"])
+@pytest.mark.parametrize("kv_dtype", ["f32", "f16"])
+def test_stepwise_logits_match_oracle(ctx, oracle, arch, kv_dtype):
+    om, h = build_pair(oracle, arch, seed=11, kv_dtype=kv_dtype, max_ctx=64, ctx=ctx)
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, arch.vocab, 40).tolist()
+    seq = om.new_seq()
+    worst = 0.0
+    for p, t in enumerate(toks):
+        ref, hid_ref = om.forward(seq, t, p, want_hidden=True)
+        res = h.forward(ForwardRequest("r0", toks[: p + 1], p))
+        worst = max(worst, rel_err(res.logits, ref))
+        assert rel_err(h.last_hidden(1)[0], hid_ref) < TOL
+        assert int(np.argmax(res.logits)) == oracle.greedy(ref)
+    assert worst < TOL, worst
+    h.release_gpu_resources()
+    h.release_gpu_resources()  # idempotent
+
+
+def test_token_id_clamped_like_reference(ctx, oracle):
+    om, h = build_pair(oracle, TINY, seed=12, kv_dtype="f32", max_ctx=32, ctx=ctx)
+    for tok in (-5, TINY.vocab + 7):
+        ref = om.forward(om.new_seq(), tok, 0)
+        got = h.forward(ForwardRequest(f"c{tok}", [tok], 0)).logits
+        assert rel_err(got, ref) < TOL
+    h.release_gpu_resources()
+
+
+@pytest.mark.parametrize("kv_dtype", ["f32", "f16"])
+def test_greedy_ids_identical(ctx, oracle, kv_dtype):
+    om, h = build_pair(oracle, SMALL128, seed=13, kv_dtype=kv_dtype, max_ctx=128, ctx=ctx)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, SMALL128.vocab, 24).tolist()
+    ref_ids, margins = om.generate_greedy(om.new_seq(), prompt, 48)
+    got = generate_greedy(B200InferencePipeline(h), "g0", prompt, 48)
+    assert got == ref_ids.tolist(), (got, ref_ids.tolist(), margins.min())
+    h.release_gpu_resources()
+
+
+def test_forward_batch_ragged_positions_and_evict(ctx, oracle):
+    """Continuous batching: three requests at different positions in one step; one is evicted and restarted."""
+    arch = TINY
+    om, h = build_pair(oracle, arch, seed=14, kv_dtype="f16", max_ctx=64, max_batch=4, max_seqs=4, ctx=ctx)
+    rng = np.random.default_rng(2)
+    streams = {r: rng.integers(0, arch.vocab, n).tolist() for r, n in (("a", 20), ("b", 9), ("c", 14))}
+    oseq = {r: om.new_seq() for r in streams}
+    pos = {r: 0 for r in streams}
+    # stagger: "a" runs alone for 6 steps, then all that still have tokens run together
+    for _ in range(6):
+        ref = om.forward(oseq["a"], streams["a"][pos["a"]], pos["a"])
+        got = h.forward_batch(["a"], [[streams["a"][pos["a"]]]], [pos["a"]])[0]
+        assert rel_err(got, ref) < TOL
+        pos["a"] += 1
+    while any(pos[r] < len(streams[r]) for r in streams):
+        live = [r for r in streams if pos[r] < len(streams[r])]
+        logits, ids = h.forward_batch(live, [[streams[r][pos[r]]] for r in live], [pos[r] for r in live],
+                                      want_logits=True, want_argmax=True)
+        for i, r in enumerate(live):
+            ref = om.forward(oseq[r], streams[r][pos[r]], pos[r])
+            assert rel_err(logits[i], ref) < TOL
+            assert ids[i] == oracle.greedy(ref)
+            pos[r] += 1
+    h.evict("b")
+    h.evict("b")  # unknown id: ignored
+    fresh = om.new_seq()
+    ref = om.forward(fresh, 5, 0)
+    assert rel_err(h.forward_batch(["b"], [[5]], [0])[0], ref) < TOL
+    with pytest.raises(ValueError):
+        h.forward_batch(["a", "a"], [[1], [2]], [0, 0])
+    with pytest.raises(ValueError):
+        h.forward_batch(["a"], [[1]], [64])  # beyond max_ctx
+    h.release_gpu_resources()
+
+
+def test_decode_greedy_batch_matches_stepwise(ctx, oracle):
+    arch = TINY
+    om, h = build_pair(oracle, arch, seed=15, kv_dtype="f32", max_ctx=96, max_batch=3, max_seqs=3, ctx=ctx)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, arch.vocab, n).tolist() for n in (5, 17, 11)]
+    refs = [om.generate_greedy(om.new_seq(), p, 20)[0].tolist() for p in prompts]
+    names = ["x", "y", "z"]
+    for r, p in zip(names, prompts):
+        for i in range(len(p) - 1):
+            h.forward_batch([r], [[p[i]]], [i], want_logits=False, want_argmax=True)
+    out = h.decode_greedy(names, [p[-1] for p in prompts], [len(p) - 1 for p in prompts], 20)
+    for i in range(3):
+        assert out[:, i].tolist() == refs[i]
+    h.release_gpu_resources()
+
+
+def test_all_q4k_and_q8_models(ctx, oracle):
+    """Other type maps on the same kernels: every matrix Q4_K (one fused QKV launch) and every matrix Q8_0."""
+    for tm in (lambda k: synth.Q4_K, lambda k: synth.Q8_0):
+        om, h = build_pair(oracle, TINY, seed=16, kv_dtype="f32", max_ctx=32, ctx=ctx, type_map=tm)
+        seq = om.new_seq()
+        for p, t in enumerate([3, 900, 17, 512]):
+            ref = om.forward(seq, t, p)
+            assert rel_err(h.forward_batch(["q"], [[t]], [p])[0], ref) < TOL
+        h.release_gpu_resources()
+
+
+def test_tinyllama_config0_greedy_64(ctx, oracle):
+    """TinyLlama-1.1B architecture, random-init Q4_K_M from seed 0, 128 random prompt ids, 64 greedy steps:
+    token ids identical to the CPU path (FP32 KV as the reference stores it, and the FP16-page engine against
+    the oracle run with FP16 KV)."""
+    arch = synth.TINYLLAMA
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, arch.vocab, 128).tolist()
+    for kv in ("f32", "f16"):
+        om, h = build_pair(oracle, arch, seed=0, kv_dtype=kv, max_ctx=256, ctx=ctx)
+        ref_ids, margins = om.generate_greedy(om.new_seq(), prompt, 64)
+        got = generate_greedy(B200InferencePipeline(h), "t0", prompt, 64)
+        h.release_gpu_resources()
+        om.close()
+        first_bad = next((i for i, (a, b) in enumerate(zip(got, ref_ids.tolist())) if a != b), None)
+        assert first_bad is None, (kv, first_bad, float(margins.min()))
