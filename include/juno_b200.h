@@ -61,6 +61,9 @@ int juno_ctx_create(int32_t device, juno_ctx **out);
 int juno_ctx_destroy(juno_ctx *ctx); /* idempotent on a closed handle: returns JUNO_ERR_CLOSED */
 int juno_ctx_device(juno_ctx *ctx, int32_t *device);
 int juno_ctx_synchronize(juno_ctx *ctx);
+/* The cudaStream_t all work of this context is enqueued on (replaces the per-thread stream of
+ * CudaMatVec.java:73-82); a host may record its own events on it. */
+int juno_ctx_stream(juno_ctx *ctx, void **stream);
 
 /* ── MatVec operator (boundary A) ─────────────────────────────────────────────
  * juno_qmat_upload replaces GpuMatVec.uploadHalf(float[],rows,cols)
@@ -192,6 +195,20 @@ typedef struct juno_counters {
     int64_t d2h_bytes;
 } juno_counters;
 int juno_ctx_counters(juno_ctx *ctx, juno_counters *out, int32_t reset);
+
+/* Per-kernel timing, the device-side counterpart of juno.MatVec durations (MatVecEvent.java:46-72).
+ * While enabled every launch is bracketed by CUDA events on the context stream and forward passes run
+ * without CUDA graphs; juno_ctx_profile_read synchronises and returns, per category, launches, summed
+ * milliseconds and the algorithmic bytes the launches had to move.  Categories: 0 Q4_K GEMV, 1 Q6_K GEMV,
+ * 2 Q8_0 GEMV, 3 attention (split + merge), 4 RoPE + KV append, 5 other. */
+#define JUNO_PROF_COUNT 6
+typedef struct juno_profile_entry {
+    int64_t launches;
+    double ms;
+    double algo_bytes;
+} juno_profile_entry;
+int juno_ctx_profile(juno_ctx *ctx, int32_t enable);
+int juno_ctx_profile_read(juno_ctx *ctx, juno_profile_entry *out, int32_t n_entries, int32_t reset);
 
 #ifdef __cplusplus
 }

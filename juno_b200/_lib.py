@@ -29,6 +29,12 @@ class Counters(C.Structure):
                 ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64)]
 
 
+class ProfileEntry(C.Structure):
+    _fields_ = [("launches", C.c_int64), ("ms", C.c_double), ("algo_bytes", C.c_double)]
+
+
+PROF_NAMES = ["gemv_q4k", "gemv_q6k", "gemv_q8_0", "attention", "rope_append", "other"]
+
 P = C.c_void_p
 PP = C.POINTER(C.c_void_p)
 I32, I64 = C.c_int32, C.c_int64
@@ -44,6 +50,9 @@ SIGNATURES = {
     "juno_ctx_device": (C.c_int, [P, C.POINTER(I32)]),
     "juno_ctx_synchronize": (C.c_int, [P]),
     "juno_ctx_counters": (C.c_int, [P, C.POINTER(Counters), I32]),
+    "juno_ctx_stream": (C.c_int, [P, PP]),
+    "juno_ctx_profile": (C.c_int, [P, I32]),
+    "juno_ctx_profile_read": (C.c_int, [P, P, I32, I32]),
     "juno_qmat_upload": (C.c_int, [P, P, I32, I64, I64, PP]),
     "juno_qmat_free": (C.c_int, [P]),
     "juno_qmat_shape": (C.c_int, [P, C.POINTER(I64), C.POINTER(I64), C.POINTER(I32)]),

@@ -300,6 +300,7 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     p.part_o = a.part_o;
     p.part_ml = a.part_ml;
     p.out = a.out;
+    ProfScope prof(ctx, st, PROF_ATTN, a.algo_bytes);
     int rc;
     if (pool->dtype == 0)
         rc = hd == 128 ? attn_launch_g<__half, 128>(p, a.n, G, st) : attn_launch_g<__half, 64>(p, a.n, G, st);
@@ -347,6 +348,7 @@ int launch_rope_append(juno_ctx *ctx, const juno_kvpool *pool, int layer, int n,
     p.slots = slots;
     p.positions = positions;
     p.cs = cs_table;
+    ProfScope prof(ctx, st, PROF_ROPE_APPEND, 0);
     dim3 grid(n, n_heads + pool->n_kv_heads);
     if (pool->dtype == 0)
         rope_append_kernel<__half><<<grid, pool->head_dim / 2, 0, st>>>(p);
@@ -627,6 +629,7 @@ int juno_attn_decode(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno
     a.slots = d_meta;
     a.seq_lens = d_meta + n;
     a.n_splits = n_splits;
+    for (int i = 0; i < n; i++) a.algo_bytes += (double)seqs[i]->len * p->n_kv_heads * hd * 2 * p->elem_bytes;
     float *sc = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(c->stage_y) + qoff);
     a.part_o = sc;
     a.part_ml = sc + (size_t)n * n_heads * n_splits * hd;

@@ -46,6 +46,7 @@ struct AttnArgs {
     int n_splits;
     float *part_o;       // [n][n_heads][n_splits][hd]
     float *part_ml;      // [n][n_heads][n_splits][2]
+    double algo_bytes = 0;  // K+V bytes the call has to read (for the profiler)
 };
 size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits);
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len);

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 #include "../../include/juno_b200.h"
 
@@ -58,6 +59,15 @@ struct GemvScratch {
 
 }  // namespace juno
 
+namespace juno {
+enum ProfCat { PROF_GEMV_Q4K = 0, PROF_GEMV_Q6K, PROF_GEMV_Q80, PROF_ATTN, PROF_ROPE_APPEND, PROF_OTHER, PROF_COUNT };
+struct ProfSpan {
+    int cat;
+    double bytes;
+    cudaEvent_t e0, e1;
+};
+}  // namespace juno
+
 struct juno_ctx {
     uint32_t magic;
     int device;
@@ -71,6 +81,11 @@ struct juno_ctx {
     size_t stage_x_bytes = 0, stage_y_bytes = 0;
     void *pinned = nullptr;
     size_t pinned_bytes = 0;
+    // per-kernel timing (off by default): event pairs around launches, summed at read time
+    bool profiling = false;
+    std::vector<juno::ProfSpan> prof_spans;
+    double prof_ms[juno::PROF_COUNT] = {0}, prof_bytes[juno::PROF_COUNT] = {0};
+    int64_t prof_launches[juno::PROF_COUNT] = {0};
     std::atomic<int64_t> kernel_launches{0}, gemv_calls{0}, forward_calls{0}, h2d_bytes{0}, d2h_bytes{0};
 };
 
@@ -81,6 +96,27 @@ int ctx_check(juno_ctx *c);
 // Grows a device buffer (never shrinks). Returns JUNO_OK / JUNO_ERR_OOM.
 int ensure_device(void **ptr, size_t *cur, size_t want);
 int ensure_pinned(juno_ctx *c, size_t want);
+
+// Brackets one launch (or a short group) with events when the context is profiling.
+struct ProfScope {
+    juno_ctx *c;
+    cudaStream_t st;
+    bool on;
+    ProfSpan sp;
+    ProfScope(juno_ctx *ctx, cudaStream_t stream, int cat, double bytes) : c(ctx), st(stream), on(ctx->profiling) {
+        if (!on) return;
+        sp.cat = cat;
+        sp.bytes = bytes;
+        cudaEventCreate(&sp.e0);
+        cudaEventCreate(&sp.e1);
+        cudaEventRecord(sp.e0, st);
+    }
+    ~ProfScope() {
+        if (!on) return;
+        cudaEventRecord(sp.e1, st);
+        c->prof_spans.push_back(sp);
+    }
+};
 
 struct DeviceGuard {
     int prev = -1;

@@ -158,6 +158,51 @@ int juno_ctx_synchronize(juno_ctx *c) {
     return JUNO_OK;
 }
 
+int juno_ctx_stream(juno_ctx *c, void **stream) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(stream, "stream is null");
+    *stream = (void *)c->stream;
+    return JUNO_OK;
+}
+
+int juno_ctx_profile(juno_ctx *c, int32_t enable) {
+    JUNO_TRY(ctx_check(c));
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    c->profiling = enable != 0;
+    return JUNO_OK;
+}
+
+int juno_ctx_profile_read(juno_ctx *c, juno_profile_entry *out, int32_t n_entries, int32_t reset) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(out && n_entries >= 1, "bad output array");
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    for (auto &sp : c->prof_spans) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, sp.e0, sp.e1) == cudaSuccess) {
+            c->prof_ms[sp.cat] += ms;
+            c->prof_bytes[sp.cat] += sp.bytes;
+            c->prof_launches[sp.cat]++;
+        }
+        cudaEventDestroy(sp.e0);
+        cudaEventDestroy(sp.e1);
+    }
+    cudaGetLastError();
+    c->prof_spans.clear();
+    for (int i = 0; i < n_entries && i < PROF_COUNT; i++) {
+        out[i].launches = c->prof_launches[i];
+        out[i].ms = c->prof_ms[i];
+        out[i].algo_bytes = c->prof_bytes[i];
+    }
+    if (reset)
+        for (int i = 0; i < PROF_COUNT; i++) {
+            c->prof_launches[i] = 0;
+            c->prof_ms[i] = c->prof_bytes[i] = 0;
+        }
+    return JUNO_OK;
+}
+
 int juno_ctx_counters(juno_ctx *c, juno_counters *out, int32_t reset) {
     JUNO_TRY(ctx_check(c));
     if (out) {

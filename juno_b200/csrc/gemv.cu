@@ -621,6 +621,12 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
         }
     }
 
+    double algo_bytes = (double)a.batch * a.K * 4;
+    {
+        const double bpw = a.type == 12 ? 144.0 / 256 : a.type == 14 ? 210.0 / 256 : 34.0 / 32;
+        for (int s = 0; s < a.nseg; s++) algo_bytes += (double)a.seg[s].rows * a.K * bpw + (double)a.batch * a.seg[s].rows * 4;
+    }
+    ProfScope prof(ctx, st, a.type == 12 ? PROF_GEMV_Q4K : a.type == 14 ? PROF_GEMV_Q6K : PROF_GEMV_Q80, algo_bytes);
     for (int b0 = 0; b0 < a.batch; b0 += bc) {
         const int nbatch = std::min(bc, a.batch - b0);
         GemvParams p;

@@ -217,6 +217,7 @@ struct juno_model {
     int out_ids_cap = 0;
     int32_t *h_step = nullptr;  // pinned mirror of d_step
     int last_n = 0, last_x = 0;
+    double step_kv_bytes = 0;  // K+V bytes one layer's attention reads in the current step
     std::map<uint64_t, JunoGraph> graphs;
     bool use_graphs = true;
 };
@@ -557,6 +558,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         at.n_splits = n_splits;
         at.part_o = m->attn_scratch;
         at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
+        at.algo_bytes = m->step_kv_bytes;
         JUNO_TRY(launch_attn(c, at, st));
         // proj = Wo·att  (row-parallel under TP: partial sums, all-reduced)
         GemvArgs o;
@@ -634,7 +636,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
 static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
     juno_ctx *c = m->ctx;
     cudaStream_t st = c->stream;
-    if (!m->use_graphs) return enqueue_step(m, n, n_splits, greedy_advance, st);
+    if (!m->use_graphs || c->profiling) return enqueue_step(m, n, n_splits, greedy_advance, st);
     const uint64_t key = ((uint64_t)n << 32) | ((uint64_t)n_splits << 1) | (greedy_advance ? 1u : 0u);
     JunoGraph &g = m->graphs[key];
     if (g.exec) {
@@ -703,6 +705,9 @@ static int prepare_step(juno_model *m, int n, juno_seq *const *seqs, const int32
         m->h_step[3 * B + i] = positions[i] + 1;
         max_len = std::max(max_len, positions[i] + 1 + extra_positions);
     }
+    m->step_kv_bytes = 0;
+    for (int i = 0; i < n; i++)
+        m->step_kv_bytes += (double)(positions[i] + 1) * m->kv_loc * m->hd * 2 * m->pool->elem_bytes;
     *n_splits = attn_pick_splits(c, n, m->kv_loc, bucket_len(max_len));
     JUNO_CUDA_TRY(cudaMemcpyAsync(m->d_step, m->h_step, (size_t)4 * B * 4, cudaMemcpyHostToDevice, c->stream));
     c->h2d_bytes += 4 * n * 4;

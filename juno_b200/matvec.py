@@ -60,6 +60,20 @@ class GpuContext:
         check(self._L.juno_ctx_counters(self.handle, C.byref(c), 1 if reset else 0), "juno_ctx_counters")
         return {k: getattr(c, k) for k, _ in c._fields_}
 
+    def stream(self) -> int:
+        """cudaStream_t (as an integer) all work of this context runs on."""
+        h = C.c_void_p()
+        check(self._L.juno_ctx_stream(self.handle, C.byref(h)), "juno_ctx_stream")
+        return h.value or 0
+
+    def profile(self, enable: bool) -> None:
+        check(self._L.juno_ctx_profile(self.handle, 1 if enable else 0), "juno_ctx_profile")
+
+    def profile_read(self, reset: bool = True) -> dict:
+        arr = (_lib.ProfileEntry * len(_lib.PROF_NAMES))()
+        check(self._L.juno_ctx_profile_read(self.handle, arr, len(arr), 1 if reset else 0), "juno_ctx_profile_read")
+        return {n: {"launches": e.launches, "ms": e.ms, "algo_bytes": e.algo_bytes} for n, e in zip(_lib.PROF_NAMES, arr)}
+
     def close(self) -> None:
         """No-op on the shared instance, like GpuContext.close (GpuContext.java:229-243)."""
         if self._is_shared or self.handle is None:
