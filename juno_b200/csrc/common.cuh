@@ -49,12 +49,14 @@ constexpr uint32_t kMagicSeq = 0x4A534551;    // "JSEQ"
 constexpr uint32_t kMagicPool = 0x4A4B5650;   // "JKVP"
 constexpr uint32_t kMagicDead = 0xDEADDEAD;
 
-// Scratch used by split-K reductions of the GEMV kernels (partials + arrival counters).
+// Device-side work counters of the GEMV kernels (dynamic task distribution): a ring of {next, done} pairs so
+// that consecutive launches never share a pair; each kernel leaves its pair at zero.
+constexpr int kGemvCounterSlots = 256;
 struct GemvScratch {
-    float *partial = nullptr;
-    size_t partial_bytes = 0;
-    unsigned *counters = nullptr;
-    size_t n_counters = 0;
+    unsigned *counters = nullptr;  // [kGemvCounterSlots][2]
+    unsigned next_slot = 0;
+    uint8_t *ximg = nullptr;       // staged activation for the host-level entry points
+    size_t ximg_bytes = 0;
 };
 
 }  // namespace juno

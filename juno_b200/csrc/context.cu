@@ -125,6 +125,13 @@ int juno_ctx_create(int32_t device, juno_ctx **out) {
         delete c;
         return JUNO_ERR_CUDA;
     }
+    if (e == cudaSuccess) e = cudaMalloc((void **)&c->gemv_scratch.counters, kGemvCounterSlots * 2 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(c->gemv_scratch.counters, 0, kGemvCounterSlots * 2 * sizeof(unsigned));
+    if (e != cudaSuccess) {
+        set_error("context set-up failed: rc=%d (%s)", (int)e, cudaGetErrorString(e));
+        delete c;
+        return e == cudaErrorMemoryAllocation ? JUNO_ERR_OOM : JUNO_ERR_CUDA;
+    }
     *out = c;
     return JUNO_OK;
 }
@@ -134,7 +141,7 @@ int juno_ctx_destroy(juno_ctx *c) {
     std::lock_guard<std::recursive_mutex> lk(c->mu);
     DeviceGuard g(c->device);
     cudaStreamSynchronize(c->stream);
-    if (c->gemv_scratch.partial) cudaFree(c->gemv_scratch.partial);
+    if (c->gemv_scratch.ximg) cudaFree(c->gemv_scratch.ximg);
     if (c->gemv_scratch.counters) cudaFree(c->gemv_scratch.counters);
     if (c->stage_x) cudaFree(c->stage_x);
     if (c->stage_y) cudaFree(c->stage_y);
@@ -266,6 +273,18 @@ int juno_qmat_shape(juno_qmat *m, int64_t *rows, int64_t *cols, int32_t *type) {
 
 static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, float *y, cudaStream_t st) {
     if (!m->tiled) return launch_gemv_raw(c, m, x, batch, y, st);
+    const size_t need = stage_image_bytes(c, (int)m->cols, batch);
+    void *pi = c->gemv_scratch.ximg;
+    JUNO_TRY(ensure_device(&pi, &c->gemv_scratch.ximg_bytes, need));
+    c->gemv_scratch.ximg = (uint8_t *)pi;
+    StageArgs sa;
+    sa.mode = STAGE_PLAIN;
+    sa.x = x;
+    sa.ldx = (int)m->cols;
+    sa.K = (int)m->cols;
+    sa.batch = batch;
+    sa.img = c->gemv_scratch.ximg;
+    JUNO_TRY(launch_stage(c, sa, st));
     GemvArgs a;
     a.nseg = 1;
     a.seg[0].w = m->dev;
@@ -276,9 +295,7 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
     a.K = (int)m->cols;
     a.batch = batch;
     a.ld_out = (int)m->rows;
-    a.pro = PRO_PLAIN;
-    a.x = x;
-    a.ldx = (int)m->cols;
+    a.ximg = c->gemv_scratch.ximg;
     return launch_gemv(c, a, st);
 }
 

@@ -49,11 +49,12 @@ __host__ __device__ inline float dq_f16(const uint8_t *p) {
 
 __host__ __device__ inline float tile_elem_value(int type, const uint8_t *tile, int row16, int e) {
     if (type == 12) {
-        const uint8_t *hdr = tile + row16 * 16;
-        float d = dq_f16(hdr), dmin = dq_f16(hdr + 2);
+        const uint8_t *dm = tile + row16 * 4;
+        float d = dq_f16(dm), dmin = dq_f16(dm + 2);
         int s = e >> 5;
-        float scale = JMUL(d, (float)q4k_scale6(hdr + 4, s));
-        float mn = JMUL(dmin, (float)q4k_min6(hdr + 4, s));
+        const uint8_t *sm = tile + 64 + (row16 * 4 + (s >> 1)) * 4;
+        float scale = JMUL(d, (float)sm[s & 1]);
+        float mn = JMUL(dmin, (float)sm[2 + (s & 1)]);
         int off, hi;
         q4k_elem_loc(row16, e, off, hi);
         int q = hi ? (tile[off] >> 4) : (tile[off] & 15);

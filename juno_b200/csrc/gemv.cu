@@ -72,32 +72,12 @@ __device__ __forceinline__ void split3(float v, unsigned short &hi, unsigned sho
 // SiLU as LlamaTransformerHandler.silu (:1733-1735): x / (1f + (float) Math.exp(-x)).
 __device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.f, (float)exp((double)(-x)))); }
 
-// ───────────────────────────── kernel parameters ──────────────────────────────────────────
-struct GemvParams {
-    const uint8_t *w[3];
-    float *out[3];
-    int rows[3];
-    int rt_begin[4];  // cumulative row-tile starts, rt_begin[nseg] = total
-    int nseg;
-    int K, nb, batch, ncols;
-    int kw, tiles_per_task, ntasks;
-    int ld_out;
-    int pro;
-    const float *x;
-    int ldx;
-    const float *x_add, *normw, *up;
-    float *x_out;
-    float eps;
-    float *partial;       // [kw][batch][rows_pad_total]
-    unsigned *counters;   // [total row tiles]
-    int rows_pad_total;
-};
-
 template <int TYPE>
 struct TileRegs;
 template <>
 struct TileRegs<12> {
-    uint4 h0, h1, q[4];
+    uint32_t dm0, dm1, sm0, sm1;  // d|dmin and the lane's scale/min bytes for rows r8, r8+8
+    uint4 q[4];
 };
 template <>
 struct TileRegs<14> {
@@ -115,12 +95,15 @@ __device__ __forceinline__ void load_tile(TileRegs<TYPE> &r, const uint8_t *tile
 
 template <>
 __device__ __forceinline__ void load_tile<12>(TileRegs<12> &r, const uint8_t *tile, int lane) {
-    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
-    int r8 = lane >> 2;
-    r.h0 = ld_stream(t4 + r8);
-    r.h1 = ld_stream(t4 + r8 + 8);
+    const uint32_t *t1 = reinterpret_cast<const uint32_t *>(tile);
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile + kQ4KQsOff);
+    const int r8 = lane >> 2, c = lane & 3;
+    r.dm0 = __ldcs(t1 + r8);
+    r.dm1 = __ldcs(t1 + r8 + 8);
+    r.sm0 = __ldcs(t1 + 16 + r8 * 4 + c);
+    r.sm1 = __ldcs(t1 + 16 + (r8 + 8) * 4 + c);
 #pragma unroll
-    for (int g = 0; g < 4; g++) r.q[g] = ld_stream(t4 + 16 + g * 32 + lane);
+    for (int g = 0; g < 4; g++) r.q[g] = ld_stream(t4 + g * 32 + lane);
 }
 template <>
 __device__ __forceinline__ void load_tile<14>(TileRegs<14> &r, const uint8_t *tile, int lane) {
@@ -146,11 +129,34 @@ __device__ __forceinline__ void load_tile<8>(TileRegs<8> &r, const uint8_t *tile
     r.d1 = ld_stream(t4 + 256 + r8 + 8);
 }
 
-// B-operand fetch for s16 sub-block `s16` and n-tile `nt`: 8 bytes = (x[4c],x[4c+2]) (x[4c+1],x[4c+3]).
-__device__ __forceinline__ uint2 ld_xb(const unsigned short *xb, int s16, int ncols, int col, int c) {
-    if (col < ncols) return *reinterpret_cast<const uint2 *>(xb + ((s16 * ncols + col) * 4 + c) * 4);
-    return make_uint2(0u, 0u);
+
+// MMA whose accumulator input is zero (the register file's zero register), so no clears are issued.
+__device__ __forceinline__ void mma16816_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
+__device__ __forceinline__ void mma1688_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.f));
+}
+
+// Shared-memory view of the staged activation for one lane.  NC = 3*NB limb columns are compile-time, so every
+// fetch below is a load with an immediate offset.  A lane whose fragment column does not exist (col >= NC) reads
+// column NC-1 instead: it only feeds accumulator columns that are never read back.
+template <int NC>
+struct XView {
+    const unsigned short *xb_lane[(NC + 7) / 8];  // xb + (colc*4 + c)*4 for each n-tile
+    const uint32_t *xs_lane[(NC + 7) / 8];        // xs32 + colc*4 + c
+    __device__ __forceinline__ uint2 b(int nt, int s16) const {
+        return *reinterpret_cast<const uint2 *>(xb_lane[nt] + s16 * (NC * 16));
+    }
+    __device__ __forceinline__ uint32_t sums(int nt, int sb) const { return xs_lane[nt][sb * (NC * 4)]; }
+};
 
 // ── Q4_K tile ────────────────────────────────────────────────────────────────────────────
 __device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t &lo_a, uint32_t &lo_b, uint32_t &hi_a, uint32_t &hi_b) {
@@ -161,30 +167,23 @@ __device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t &lo_a, uint32_t &
     hi_b = bf2_sub(((w >> 12) & M) | kBf128, kBf128);  // (byte1.hi, byte3.hi)
 }
 
-// Decodes one row's 16-byte Q4_K header for the lane's two sub-blocks 2c, 2c+1.
-__device__ __forceinline__ void q4_header(const uint4 &h, int c, float &sc0, float &sc1, uint32_t &mins_bf2, float &dmin) {
-    float d = f16bits_to_f32(h.x);
-    dmin = f16bits_to_f32(h.x >> 16);
-    uint32_t sA = h.y & 0x3f3f3f3fu, mA = h.z & 0x3f3f3f3fu;
-    uint32_t sB = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
-    uint32_t mB = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
-    uint32_t S = (c < 2) ? sA : sB, Mn = (c < 2) ? mA : mB;
-    int sh = (c & 1) * 16;
-    sc0 = __fmul_rn(d, (float)((S >> sh) & 0xFFu));
-    sc1 = __fmul_rn(d, (float)((S >> (sh + 8)) & 0xFFu));
-    uint32_t mp = (Mn >> sh) & 0xFFFFu;                        // bytes (m0, m1)
-    mins_bf2 = bf2_sub(__byte_perm(mp, 0x43434343u, 0x4140), kBf128);  // bf16x2 (m0, m1)
+// Decodes one row's header words for the lane's two sub-blocks 2c, 2c+1.
+__device__ __forceinline__ void q4_header(uint32_t dm, uint32_t sm, float &sc0, float &sc1, uint32_t &mins_bf2, float &dmin) {
+    const float d = f16bits_to_f32(dm);
+    dmin = f16bits_to_f32(dm >> 16);
+    sc0 = __fmul_rn(d, (float)(sm & 0xFFu));
+    sc1 = __fmul_rn(d, (float)((sm >> 8) & 0xFFu));
+    mins_bf2 = bf2_sub(__byte_perm(sm, 0x43434343u, 0x4342), kBf128);  // bf16x2 (m0, m1)
 }
 
-template <int NT>
-__device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, const unsigned short *xb,
-                                             const uint32_t *xs32, int ncols, int lane, float (&acc)[NT][4],
-                                             float (&macc)[NT][4]) {
-    const int r8 = lane >> 2, c = lane & 3;
+template <int NC>
+__device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, const XView<NC> &xv, int lane,
+                                             float (&acc)[(NC + 7) / 8][4], float (&macc)[(NC + 7) / 8][4]) {
+    constexpr int NT = (NC + 7) / 8;
     float s_r[2], s_q[2], dmin_r, dmin_q;
     uint32_t mins_r, mins_q;
-    q4_header(R.h0, c, s_r[0], s_r[1], mins_r, dmin_r);
-    q4_header(R.h1, c, s_q[0], s_q[1], mins_q, dmin_q);
+    q4_header(R.dm0, R.sm0, s_r[0], s_r[1], mins_r, dmin_r);
+    q4_header(R.dm1, R.sm1, s_q[0], s_q[1], mins_q, dmin_q);
     const int s16base = sb * 16;
 #pragma unroll
     for (int g = 0; g < 4; g++) {
@@ -194,25 +193,23 @@ __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, cons
         q4_unpack(R.q[g].z, la_z, lb_z, ha_z, hb_z);
         q4_unpack(R.q[g].w, la_w, lb_w, ha_w, hb_w);
         const int src = (lane & ~3) | g;  // quad lane g owns sub-blocks 2g and 2g+1
-        float sr0 = __shfl_sync(0xffffffffu, s_r[0], src), sr1 = __shfl_sync(0xffffffffu, s_r[1], src);
-        float sq0 = __shfl_sync(0xffffffffu, s_q[0], src), sq1 = __shfl_sync(0xffffffffu, s_q[1], src);
+        const float sr0 = __shfl_sync(0xffffffffu, s_r[0], src), sr1 = __shfl_sync(0xffffffffu, s_r[1], src);
+        const float sq0 = __shfl_sync(0xffffffffu, s_q[0], src), sq1 = __shfl_sync(0xffffffffu, s_q[1], src);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const int col = nt * 8 + r8;
-            float ct[4] = {0.f, 0.f, 0.f, 0.f};
-            uint2 b = ld_xb(xb, s16base + 4 * g + 0, ncols, col, c);
-            mma16816(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
-            b = ld_xb(xb, s16base + 4 * g + 1, ncols, col, c);
+            float ct[4], ch[4];
+            uint2 b = xv.b(nt, s16base + 4 * g + 0);
+            mma16816_z(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
+            b = xv.b(nt, s16base + 4 * g + 1);
             mma16816(ct, la_y, la_w, lb_y, lb_w, b.x, b.y);
+            b = xv.b(nt, s16base + 4 * g + 2);
+            mma16816_z(ch, ha_x, ha_z, hb_x, hb_z, b.x, b.y);
+            b = xv.b(nt, s16base + 4 * g + 3);
+            mma16816(ch, ha_y, ha_w, hb_y, hb_w, b.x, b.y);
             acc[nt][0] = fmaf(sr0, ct[0], acc[nt][0]);
             acc[nt][1] = fmaf(sr0, ct[1], acc[nt][1]);
             acc[nt][2] = fmaf(sq0, ct[2], acc[nt][2]);
             acc[nt][3] = fmaf(sq0, ct[3], acc[nt][3]);
-            float ch[4] = {0.f, 0.f, 0.f, 0.f};
-            b = ld_xb(xb, s16base + 4 * g + 2, ncols, col, c);
-            mma16816(ch, ha_x, ha_z, hb_x, hb_z, b.x, b.y);
-            b = ld_xb(xb, s16base + 4 * g + 3, ncols, col, c);
-            mma16816(ch, ha_y, ha_w, hb_y, hb_w, b.x, b.y);
             acc[nt][0] = fmaf(sr1, ch[0], acc[nt][0]);
             acc[nt][1] = fmaf(sr1, ch[1], acc[nt][1]);
             acc[nt][2] = fmaf(sq1, ch[2], acc[nt][2]);
@@ -222,10 +219,8 @@ __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, cons
     // min term: sum_j (dmin*m_j) * sum_{c in sub-block j} x[c]
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-        const int col = nt * 8 + r8;
-        uint32_t bm = (col < ncols) ? xs32[(sb * ncols + col) * 4 + c] : 0u;
-        float cm[4] = {0.f, 0.f, 0.f, 0.f};
-        mma1688(cm, mins_r, mins_q, bm);
+        float cm[4];
+        mma1688_z(cm, mins_r, mins_q, xv.sums(nt, sb));
         macc[nt][0] = fmaf(dmin_r, cm[0], macc[nt][0]);
         macc[nt][1] = fmaf(dmin_r, cm[1], macc[nt][1]);
         macc[nt][2] = fmaf(dmin_q, cm[2], macc[nt][2]);
@@ -236,11 +231,10 @@ __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, cons
 // ── Q6_K tile ────────────────────────────────────────────────────────────────────────────
 __device__ __forceinline__ float i8_to_f32(uint32_t w, int k) { return (float)(int)(signed char)((w >> (8 * k)) & 0xFFu); }
 
-template <int NT>
-__device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, const unsigned short *xb,
-                                             const uint32_t * /*xs32*/, int ncols, int lane, float (&acc)[NT][4],
-                                             float (& /*macc*/)[NT][4]) {
-    const int r8 = lane >> 2, c = lane & 3;
+template <int NC>
+__device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, const XView<NC> &xv, int lane,
+                                             float (&acc)[(NC + 7) / 8][4], float (& /*macc*/)[(NC + 7) / 8][4]) {
+    constexpr int NT = (NC + 7) / 8;
     const float d_r = f16bits_to_f32(R.d01), d_q = f16bits_to_f32(R.d01 >> 16);
     float s_r[4], s_q[4];  // scales of sub-blocks 4c..4c+3 for rows r8 and r8+8
 #pragma unroll
@@ -274,10 +268,9 @@ __device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, cons
             const uint32_t a3 = bf2_sub(__byte_perm(V_q[k], 0x43434343u, 0x4342), kBf160);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const int col = nt * 8 + r8;
-                float ct[4] = {0.f, 0.f, 0.f, 0.f};
-                uint2 b = ld_xb(xb, s16base + 4 * m + k, ncols, col, c);
-                mma16816(ct, a0, a1, a2, a3, b.x, b.y);
+                float ct[4];
+                const uint2 b = xv.b(nt, s16base + 4 * m + k);
+                mma16816_z(ct, a0, a1, a2, a3, b.x, b.y);
                 acc[nt][0] = fmaf(sr, ct[0], acc[nt][0]);
                 acc[nt][1] = fmaf(sr, ct[1], acc[nt][1]);
                 acc[nt][2] = fmaf(sq, ct[2], acc[nt][2]);
@@ -296,11 +289,10 @@ __device__ __forceinline__ void q8_unpack(uint32_t w, uint32_t &l_a, uint32_t &l
     h_b = bf2_sub(((w >> 9) & MH) ^ kBf384, kBf384);      // 16*(b1>>4), 16*(b3>>4)
 }
 
-template <int NT>
-__device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const unsigned short *xb,
-                                             const uint32_t * /*xs32*/, int ncols, int lane, float (&acc)[NT][4],
-                                             float (& /*macc*/)[NT][4]) {
-    const int r8 = lane >> 2, c = lane & 3;
+template <int NC>
+__device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const XView<NC> &xv, int /*lane*/,
+                                             float (&acc)[(NC + 7) / 8][4], float (& /*macc*/)[(NC + 7) / 8][4]) {
+    constexpr int NT = (NC + 7) / 8;
     const int s16base = sb * 16;
     const uint32_t dr[4] = {R.d0.x, R.d0.y, R.d0.z, R.d0.w}, dq[4] = {R.d1.x, R.d1.y, R.d1.z, R.d1.w};
 #pragma unroll
@@ -313,12 +305,11 @@ __device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const
         q8_unpack(R.q[j].w, la_w, lb_w, ha_w, hb_w);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const int col = nt * 8 + r8;
-            float ct[4] = {0.f, 0.f, 0.f, 0.f};
-            uint2 b = ld_xb(xb, s16base + 2 * j, ncols, col, c);
-            mma16816(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
+            float ct[4];
+            uint2 b = xv.b(nt, s16base + 2 * j);
+            mma16816_z(ct, la_x, la_z, lb_x, lb_z, b.x, b.y);
             mma16816(ct, ha_x, ha_z, hb_x, hb_z, b.x, b.y);
-            b = ld_xb(xb, s16base + 2 * j + 1, ncols, col, c);
+            b = xv.b(nt, s16base + 2 * j + 1);
             mma16816(ct, la_y, la_w, lb_y, lb_w, b.x, b.y);
             mma16816(ct, ha_y, ha_w, hb_y, hb_w, b.x, b.y);
             acc[nt][0] = fmaf(d_r, ct[0], acc[nt][0]);
@@ -329,180 +320,262 @@ __device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const
     }
 }
 
-// ───────────────────────────── the kernel ─────────────────────────────────────────────────
+// ───────────────────────────── activation staging ─────────────────────────────────────────
+// One CTA per batch row writes that row's three limb columns (and 32-column sums) of the staged image.
+struct StageParams {
+    int mode;
+    const float *x;
+    int ldx;
+    const float *x_add, *normw;
+    float *x_out;
+    float eps;
+    int K, batch, bc;
+    size_t chunk_stride;  // bytes of a full chunk of bc rows
+    uint8_t *img;
+};
+
+size_t stage_chunk_bytes(int K, int rows_in_chunk) {
+    const size_t nc = 3 * (size_t)rows_in_chunk;
+    const size_t xb = (size_t)K * nc * 2;
+    const size_t xs = ((((size_t)(K / 32) * nc) + 7) & ~(size_t)7) * 2;
+    return xb + xs;
+}
+
+constexpr int kStageThreads = 256;
+
+__global__ void __launch_bounds__(kStageThreads) stage_kernel(const StageParams p) {
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = b / p.bc, nbc = min(p.bc, p.batch - chunk * p.bc), NC = 3 * nbc, col0 = 3 * (b - chunk * p.bc);
+    const int K = p.K;
+    unsigned short *xb = reinterpret_cast<unsigned short *>(p.img + (size_t)chunk * p.chunk_stride);
+    unsigned short *xs = xb + (size_t)K * NC;
+    const float *xrow = p.x + (size_t)b * p.ldx;
+    const float *arow = p.x_add ? p.x_add + (size_t)b * p.ldx : nullptr;
+    float scale = 1.f;
+    __shared__ float red[kStageThreads / 32];
+    if (p.mode == STAGE_RMSNORM) {
+        float part = 0.f;
+        for (int i = tid; i < K; i += kStageThreads) {
+            float r = xrow[i];
+            if (arow) r = __fadd_rn(r, arow[i]);
+            part = fmaf(r, r, part);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        float ss = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < kStageThreads / 32; w8++) ss += red[w8];
+        // rmsNorm (:818-828): 1f / (float) Math.sqrt(ss / n + eps)
+        scale = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(ss, (float)K), p.eps)));
+    }
+    // each thread handles 4 consecutive columns = one (s16, c) group of the feed order
+    for (int i4 = tid * 4; i4 < K; i4 += kStageThreads * 4) {
+        float v[4];
+        const float4 xv = *reinterpret_cast<const float4 *>(xrow + i4);
+        v[0] = xv.x; v[1] = xv.y; v[2] = xv.z; v[3] = xv.w;
+        if (p.mode == STAGE_RMSNORM) {
+            if (arow) {
+                const float4 av = *reinterpret_cast<const float4 *>(arow + i4);
+                v[0] = __fadd_rn(v[0], av.x); v[1] = __fadd_rn(v[1], av.y);
+                v[2] = __fadd_rn(v[2], av.z); v[3] = __fadd_rn(v[3], av.w);
+            }
+            if (p.x_out) *reinterpret_cast<float4 *>(p.x_out + (size_t)b * p.ldx + i4) = make_float4(v[0], v[1], v[2], v[3]);
+            const float4 wv = *reinterpret_cast<const float4 *>(p.normw + i4);
+            v[0] = __fmul_rn(__fmul_rn(wv.x, v[0]), scale);
+            v[1] = __fmul_rn(__fmul_rn(wv.y, v[1]), scale);
+            v[2] = __fmul_rn(__fmul_rn(wv.z, v[2]), scale);
+            v[3] = __fmul_rn(__fmul_rn(wv.w, v[3]), scale);
+        }
+        unsigned short l[3][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) split3(v[t], l[0][t], l[1][t], l[2][t]);
+        const int s16 = i4 >> 4, c = (i4 >> 2) & 3;
+        unsigned short *dst = xb + ((size_t)(s16 * NC + col0) * 4 + c) * 4;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {  // feed order: columns (4c, 4c+2, 4c+1, 4c+3)
+            uint2 w;
+            w.x = (uint32_t)l[k][0] | ((uint32_t)l[k][2] << 16);
+            w.y = (uint32_t)l[k][1] | ((uint32_t)l[k][3] << 16);
+            *reinterpret_cast<uint2 *>(dst + k * 16) = w;
+        }
+        // sums over 32 columns = 8 consecutive threads
+        float s = (v[0] + v[1]) + (v[2] + v[3]);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        unsigned short s3[3];
+        split3(s, s3[0], s3[1], s3[2]);
+        if ((lane & 7) == 0) {
+#pragma unroll
+            for (int k = 0; k < 3; k++) xs[xs_index(i4 >> 5, NC, col0 + k)] = s3[k];
+        }
+    }
+}
+
+// ───────────────────────────── the GEMV kernel ────────────────────────────────────────────
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 
+struct GemvParams {
+    const uint8_t *w[3];
+    float *out[3];
+    int rows[3];
+    int rt_begin[4];  // cumulative row-tile starts, rt_begin[nseg] = total
+    int nseg, total_rt;
+    int K, nb;
+    int kin, tpt, groups, n_ctasks;  // warps per row tile, tiles per warp per task, row tiles per CTA task
+    int ld_out, epi;
+    const uint8_t *ximg;
+    unsigned img_bytes;
+    unsigned *counters;  // {next task, CTAs done}
+};
+
 template <int TYPE>
-__device__ __forceinline__ const uint8_t *tile_ptr(const GemvParams &p, int task, int tile_in_task, int &R, int &kj,
-                                                   int &sb) {
-    R = task / p.kw;
-    kj = task - R * p.kw;
-    sb = kj * p.tiles_per_task + tile_in_task;
+__device__ __forceinline__ const uint8_t *tile_addr(const GemvParams &p, int R, int sb) {
     int s = 0;
     if (p.nseg > 1 && R >= p.rt_begin[1]) s = 1;
     if (p.nseg > 2 && R >= p.rt_begin[2]) s = 2;
     return p.w[s] + ((size_t)(R - p.rt_begin[s]) * p.nb + sb) * (size_t)tile_bytes(TYPE);
 }
 
-template <int TYPE, int NT>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
+template <int TYPE, int NB>
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
+    constexpr int NC = 3 * NB, NT = (NC + 7) / 8, LD = 8 * NT;
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int K = p.K, ncols = p.ncols, batch = p.batch;
-    unsigned short *xb = reinterpret_cast<unsigned short *>(smem);                 // K*ncols bf16
-    unsigned short *xs = xb + (size_t)K * ncols;                                   // (K/32)*ncols bf16 (padded to 8 B)
-    size_t xs_elems = (((size_t)(K / 32) * ncols) + 7) & ~(size_t)7;
-    float *cs = reinterpret_cast<float *>(xs + xs_elems);                          // kWarps * 16 * 8NT
-    float *red = cs + kWarps * 16 * 8 * NT;                                        // batch * kWarps
+    const int K = p.K;
+    unsigned short *xb = reinterpret_cast<unsigned short *>(smem);  // K*NC bf16, then (K/32)*NC sums (padded to 16 B)
+    unsigned short *xs = xb + (size_t)K * NC;
+    float *cs = reinterpret_cast<float *>(smem + p.img_bytes);      // [2][kWarps][16][LD]
+    int *next_task = reinterpret_cast<int *>(cs + 2 * kWarps * 16 * LD);
 
-    // work assignment: task = (row tile, K chunk); warp gw takes tasks gw, gw+W, ...
-    const int W = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
-    const int my_tasks = (gw < p.ntasks) ? (p.ntasks - gw + W - 1) / W : 0;
-    const int total_it = my_tasks * p.tiles_per_task;
+    // A CTA task is `groups` row tiles; the kin warps of a group split K.  Task ids beyond the first come
+    // from a device counter, so CTAs that finish early take more.
+    const int grp = warp / p.kin, kj = warp - grp * p.kin;
+    const int sb0 = kj * p.tpt;
+    int ct = blockIdx.x;
+    if (tid == 0) next_task[0] = gridDim.x + (int)atomicAdd(p.counters, 1u);
 
     // Issue the first tile's loads before touching x: the weights do not depend on the producer of x.
-    TileRegs<TYPE> cur;
-    int R = 0, kj = 0, sb = 0;
-    int task = gw, tin = 0;
-    if (total_it > 0) load_tile<TYPE>(cur, tile_ptr<TYPE>(p, task, 0, R, kj, sb), lane);
+    TileRegs<TYPE> bufA, bufB;
+    int R = ct * p.groups + grp;
+    bool have = (ct < p.n_ctasks) && (R < p.total_rt);
+    const uint8_t *cur_ptr = have ? tile_addr<TYPE>(p, R, sb0) : nullptr;
+    if (have) load_tile<TYPE>(bufA, cur_ptr, lane);
 
-    // ── stage x: prologue transform, three bf16 limbs in MMA feed order, sub-block sums ──
-    if (p.pro == PRO_RMSNORM) {
-        for (int b = 0; b < batch; b++) {
-            float part = 0.f;
-            for (int i = tid; i < K; i += kThreads) {
-                float r = p.x[(size_t)b * p.ldx + i];
-                if (p.x_add) r = __fadd_rn(r, p.x_add[(size_t)b * p.ldx + i]);
-                part = fmaf(r, r, part);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (lane == 0) red[b * kWarps + warp] = part;
-        }
-        __syncthreads();
-    }
-    for (int b = 0; b < batch; b++) {
-        float scale = 1.f;
-        if (p.pro == PRO_RMSNORM) {
-            float ss = 0.f;
-#pragma unroll
-            for (int w8 = 0; w8 < kWarps; w8++) ss += red[b * kWarps + w8];
-            // rmsNorm (:818-828): 1f / (float) Math.sqrt(ss / n + eps)
-            scale = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(ss, (float)K), p.eps)));
-        }
-        for (int i = tid; i < K; i += kThreads) {
-            float v;
-            const size_t gi = (size_t)b * p.ldx + i;
-            if (p.pro == PRO_RMSNORM) {
-                float r = p.x[gi];
-                if (p.x_add) r = __fadd_rn(r, p.x_add[gi]);
-                if (p.x_out && blockIdx.x == 0) p.x_out[gi] = r;
-                v = __fmul_rn(__fmul_rn(p.normw[i], r), scale);
-            } else if (p.pro == PRO_SILU) {
-                v = __fmul_rn(silu_ref(p.x[gi]), p.up[gi]);
-            } else {
-                v = p.x[gi];
-            }
-            unsigned short hi, mid, lo;
-            split3(v, hi, mid, lo);
-            const int s16 = i >> 4, c = (i >> 2) & 3, pos = feed_pos(i & 3);
-            unsigned short *dst = xb + ((size_t)(s16 * ncols + 3 * b) * 4 + c) * 4 + pos;
-            dst[0] = hi;
-            dst[16] = mid;  // next column: +4*4 elements
-            dst[32] = lo;
-            if (TYPE == 12) {
-                float s = v;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane < 3) {
-                    unsigned short l3[3];
-                    split3(s, l3[0], l3[1], l3[2]);
-                    xs[xs_index(i >> 5, ncols, 3 * b + lane)] = l3[lane];
-                }
-            }
-        }
+    // staged activation -> shared memory
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.ximg);
+        uint4 *dst = reinterpret_cast<uint4 *>(smem);
+        const int n16 = (int)(p.img_bytes >> 4);
+        for (int i = tid; i < n16; i += kThreads) dst[i] = src[i];
     }
     __syncthreads();
-    const uint32_t *xs32 = reinterpret_cast<const uint32_t *>(xs);
-    float *mycs = cs + warp * 16 * 8 * NT;
 
+    XView<NC> xv;
+    {
+        const int r8 = lane >> 2, c = lane & 3;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int colc = min(nt * 8 + r8, NC - 1);
+            xv.xb_lane[nt] = xb + (colc * 4 + c) * 4;
+            xv.xs_lane[nt] = reinterpret_cast<const uint32_t *>(xs) + colc * 4 + c;
+        }
+    }
     float acc[NT][4], macc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[nt][i] = macc[nt][i] = 0.f;
 
-    for (int it = 0; it < total_it; it++) {
-        // prefetch the next tile of this warp's stream
-        TileRegs<TYPE> nxt;
-        int nR = R, nkj = kj, nsb = sb, ntask = task, ntin = tin + 1;
-        if (ntin == p.tiles_per_task) {
-            ntin = 0;
-            ntask = task + W;
+    int phase = 0, it = 0;
+    while (ct < p.n_ctasks) {
+        const int nct = next_task[it & 1];
+        if (tid == 0) next_task[(it + 1) & 1] = gridDim.x + (int)atomicAdd(p.counters, 1u);
+        const int nR = nct * p.groups + grp;
+        const bool nhave = (nct < p.n_ctasks) && (nR < p.total_rt);
+        // first tile of this warp in the next task (prefetched while the last tile of this one is computed)
+        const uint8_t *next_base = nhave ? tile_addr<TYPE>(p, nR, sb0) : nullptr;
+        if (have) {
+            for (int j = 0; j < p.tpt; j++) {
+                const uint8_t *np = (j + 1 < p.tpt) ? cur_ptr + tile_bytes(TYPE) : next_base;
+                if (phase == 0) {
+                    if (np) load_tile<TYPE>(bufB, np, lane);
+                    compute_tile<NC>(bufA, sb0 + j, xv, lane, acc, macc);
+                } else {
+                    if (np) load_tile<TYPE>(bufA, np, lane);
+                    compute_tile<NC>(bufB, sb0 + j, xv, lane, acc, macc);
+                }
+                cur_ptr = np;
+                phase ^= 1;
+            }
+        } else if (nhave) {  // idle in this task, but the next one has work: fetch its first tile
+            if (phase == 0)
+                load_tile<TYPE>(bufA, next_base, lane);
+            else
+                load_tile<TYPE>(bufB, next_base, lane);
+            cur_ptr = next_base;
         }
-        if (it + 1 < total_it) load_tile<TYPE>(nxt, tile_ptr<TYPE>(p, ntask, ntin, nR, nkj, nsb), lane);
-
-        compute_tile<NT>(cur, sb, xb, xs32, ncols, lane, acc, macc);
-
-        if (tin == p.tiles_per_task - 1) {
-            // ── flush this task: fragment -> per-warp smem tile -> limb sums ──
+        // fragments -> shared memory (double-buffered: one barrier per task)
+        float *mycs = cs + ((it & 1) * kWarps + warp) * 16 * LD;
+        {
             const int r8 = lane >> 2, c = lane & 3;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                float *row0 = mycs + r8 * (8 * NT) + nt * 8 + 2 * c;
-                float *row1 = mycs + (r8 + 8) * (8 * NT) + nt * 8 + 2 * c;
-                row0[0] = acc[nt][0] - macc[nt][0];
-                row0[1] = acc[nt][1] - macc[nt][1];
-                row1[0] = acc[nt][2] - macc[nt][2];
-                row1[1] = acc[nt][3] - macc[nt][3];
+                float *row0 = mycs + r8 * LD + nt * 8 + 2 * c;
+                float *row1 = mycs + (r8 + 8) * LD + nt * 8 + 2 * c;
+                *reinterpret_cast<float2 *>(row0) = make_float2(acc[nt][0] - macc[nt][0], acc[nt][1] - macc[nt][1]);
+                *reinterpret_cast<float2 *>(row1) = make_float2(acc[nt][2] - macc[nt][2], acc[nt][3] - macc[nt][3]);
                 acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
                 macc[nt][0] = macc[nt][1] = macc[nt][2] = macc[nt][3] = 0.f;
             }
-            __syncwarp();
-            int s = 0;
-            if (p.nseg > 1 && R >= p.rt_begin[1]) s = 1;
-            if (p.nseg > 2 && R >= p.rt_begin[2]) s = 2;
-            const int row_base = (R - p.rt_begin[s]) * 16;
-            if (p.kw == 1) {
-                for (int idx = lane; idx < 16 * batch; idx += 32) {
-                    const int row = idx & 15, b = idx >> 4;
-                    const float *cr = mycs + row * (8 * NT) + 3 * b;
-                    float v = (cr[2] + cr[1]) + cr[0];
-                    if (row_base + row < p.rows[s]) p.out[s][(size_t)b * p.ld_out + row_base + row] = v;
-                }
-            } else {
-                for (int idx = lane; idx < 16 * batch; idx += 32) {
-                    const int row = idx & 15, b = idx >> 4;
-                    const float *cr = mycs + row * (8 * NT) + 3 * b;
-                    float v = (cr[2] + cr[1]) + cr[0];
-                    __stcg(p.partial + ((size_t)kj * batch + b) * p.rows_pad_total + R * 16 + row, v);
-                }
-                __threadfence();
-                __syncwarp();
-                unsigned old = 0;
-                if (lane == 0) old = atomicAdd(p.counters + R, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == (unsigned)(p.kw - 1)) {  // last K chunk to arrive reduces in fixed order
-                    __threadfence();
-                    for (int idx = lane; idx < 16 * batch; idx += 32) {
-                        const int row = idx & 15, b = idx >> 4;
-                        float v = 0.f;
-                        for (int k2 = 0; k2 < p.kw; k2++)
-                            v += __ldcg(p.partial + ((size_t)k2 * batch + b) * p.rows_pad_total + R * 16 + row);
-                        if (row_base + row < p.rows[s]) p.out[s][(size_t)b * p.ld_out + row_base + row] = v;
+        }
+        __syncthreads();
+        // cooperative epilogue: add the K chunks of each row in warp order, then the three limbs
+        {
+            const float *csb = cs + (it & 1) * kWarps * 16 * LD;
+            const int rows_out = (p.epi == EPI_SILU_PAIR) ? 8 : 16;
+            const int total = p.groups * rows_out * NB;
+            for (int idx = tid; idx < total; idx += kThreads) {
+                const int row = idx % rows_out, rest = idx / rows_out, b = rest % NB, g = rest / NB;
+                const int Rg = ct * p.groups + g;
+                if (Rg >= p.total_rt) continue;
+                int s = 0;
+                if (p.nseg > 1 && Rg >= p.rt_begin[1]) s = 1;
+                if (p.nseg > 2 && Rg >= p.rt_begin[2]) s = 2;
+                const int tile_in_seg = Rg - p.rt_begin[s];
+                float v = 0.f, v2 = 0.f;
+                for (int k2 = 0; k2 < p.kin; k2++) {
+                    const float *cr = csb + ((g * p.kin + k2) * 16 + row) * LD + 3 * b;
+                    v += (cr[2] + cr[1]) + cr[0];
+                    if (p.epi == EPI_SILU_PAIR) {
+                        const float *cu = cr + 8 * LD;
+                        v2 += (cu[2] + cu[1]) + cu[0];
                     }
-                    if (lane == 0) p.counters[R] = 0u;  // ready for the next launch
+                }
+                if (p.epi == EPI_SILU_PAIR) {
+                    const int orow = tile_in_seg * 8 + row;
+                    if (orow < p.rows[s]) p.out[s][(size_t)b * p.ld_out + orow] = __fmul_rn(silu_ref(v), v2);
+                } else {
+                    const int orow = tile_in_seg * 16 + row;
+                    if (orow < p.rows[s]) p.out[s][(size_t)b * p.ld_out + orow] = v;
                 }
             }
-            __syncwarp();
         }
-        cur = nxt;
+        ct = nct;
         R = nR;
-        kj = nkj;
-        sb = nsb;
-        task = ntask;
-        tin = ntin;
+        have = nhave;
+        it++;
+    }
+    // the last CTA to leave zeroes the counters for the next launch that uses this pair
+    if (tid == 0) {
+        const unsigned done = atomicAdd(p.counters + 1, 1u);
+        if (done == gridDim.x - 1) {
+            p.counters[0] = 0u;
+            p.counters[1] = 0u;
+        }
     }
 }
 
@@ -512,15 +585,47 @@ static int env_int(const char *name, int dflt) {
     return (v && *v) ? atoi(v) : dflt;
 }
 
-static size_t gemv_smem_bytes(int K, int ncols, int NT, int batch) {
-    size_t xb = (size_t)K * ncols * 2;
-    size_t xs = ((((size_t)(K / 32) * ncols) + 7) & ~(size_t)7) * 2;
-    size_t cs = (size_t)kWarps * 16 * 8 * NT * 4;
-    size_t red = (size_t)batch * kWarps * 4;
-    return xb + xs + cs + red;
+static size_t gemv_smem_bytes(int K, int nb_batch) {
+    const int NT = (3 * nb_batch + 7) / 8;
+    return stage_chunk_bytes(K, nb_batch) + (size_t)2 * kWarps * 16 * 8 * NT * 4 + 16;
 }
 
-template <int TYPE, int NT>
+int gemv_batch_chunk(const juno_ctx *ctx, int K, int batch) {
+    int bc = std::min(batch, 8);
+    while (bc > 1 && gemv_smem_bytes(K, bc) > ctx->smem_optin) bc--;
+    return bc;
+}
+
+size_t stage_image_bytes(const juno_ctx *ctx, int K, int batch) {
+    const int bc = gemv_batch_chunk(ctx, K, batch);
+    const int chunks = (batch + bc - 1) / bc;
+    return (size_t)chunks * stage_chunk_bytes(K, bc);
+}
+
+int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t st) {
+    JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0 && a.batch >= 1 && a.x && a.img, "stage: bad arguments (K=%d)", a.K);
+    JUNO_REQUIRE(a.ldx % 4 == 0, "stage: row stride %d must be a multiple of 4", a.ldx);
+    StageParams p;
+    p.mode = a.mode;
+    p.x = a.x;
+    p.ldx = a.ldx;
+    p.x_add = a.x_add;
+    p.normw = a.normw;
+    p.x_out = a.x_out;
+    p.eps = a.eps;
+    p.K = a.K;
+    p.batch = a.batch;
+    p.bc = gemv_batch_chunk(ctx, a.K, a.batch);
+    p.chunk_stride = stage_chunk_bytes(a.K, p.bc);
+    p.img = a.img;
+    ProfScope prof(ctx, st, PROF_OTHER, 0);
+    stage_kernel<<<a.batch, kStageThreads, 0, st>>>(p);
+    JUNO_CUDA_TRY(cudaGetLastError());
+    ctx->kernel_launches++;
+    return JUNO_OK;
+}
+
+template <int TYPE, int NB>
 static int launch_inst(juno_ctx *ctx, const GemvParams &p, int grid, size_t smem, cudaStream_t st) {
     static std::mutex mu;
     static size_t configured[16] = {0};  // per device
@@ -528,98 +633,43 @@ static int launch_inst(juno_ctx *ctx, const GemvParams &p, int grid, size_t smem
         std::lock_guard<std::mutex> g(mu);
         int dev = ctx->device & 15;
         if (smem > 48 * 1024 && smem > configured[dev]) {
-            JUNO_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<TYPE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            JUNO_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)ctx->smem_optin));
             configured[dev] = ctx->smem_optin;
         }
     }
-    gemv_kernel<TYPE, NT><<<grid, kThreads, smem, st>>>(p);
+    gemv_kernel<TYPE, NB><<<grid, kThreads, smem, st>>>(p);
     JUNO_CUDA_TRY(cudaGetLastError());
     ctx->kernel_launches++;
     return JUNO_OK;
 }
 
 template <int TYPE>
-static int launch_type(juno_ctx *ctx, const GemvParams &p, int NT, int grid, size_t smem, cudaStream_t st) {
-    switch (NT) {
+static int launch_type(juno_ctx *ctx, const GemvParams &p, int NB, int grid, size_t smem, cudaStream_t st) {
+    switch (NB) {
     case 1: return launch_inst<TYPE, 1>(ctx, p, grid, smem, st);
     case 2: return launch_inst<TYPE, 2>(ctx, p, grid, smem, st);
     case 3: return launch_inst<TYPE, 3>(ctx, p, grid, smem, st);
     case 4: return launch_inst<TYPE, 4>(ctx, p, grid, smem, st);
     case 5: return launch_inst<TYPE, 5>(ctx, p, grid, smem, st);
     case 6: return launch_inst<TYPE, 6>(ctx, p, grid, smem, st);
+    case 7: return launch_inst<TYPE, 7>(ctx, p, grid, smem, st);
+    case 8: return launch_inst<TYPE, 8>(ctx, p, grid, smem, st);
     default: break;
     }
-    set_error("gemv: unsupported column-tile count %d", NT);
+    set_error("gemv: unsupported batch chunk %d", NB);
     return JUNO_ERR_UNSUPPORTED;
 }
-
-constexpr int kMaxBatchChunk = 16;  // 48 limb columns = 6 n-tiles
 
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
     JUNO_REQUIRE(a.nseg >= 1 && a.nseg <= 3, "gemv: nseg %d", a.nseg);
     JUNO_REQUIRE(a.type == 12 || a.type == 14 || a.type == 8, "gemv: type %d has no tiled kernel", a.type);
     JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0, "gemv: K=%d must be a multiple of 256", a.K);
-    JUNO_REQUIRE(a.batch >= 1, "gemv: batch %d", a.batch);
+    JUNO_REQUIRE(a.batch >= 1 && a.ximg, "gemv: batch %d / missing staged activation", a.batch);
     const int nb = a.K / 256;
     int total_rt = 0;
     for (int s = 0; s < a.nseg; s++) total_rt += a.seg[s].row_tiles;
-
-    // batch chunk: limb columns must fit shared memory and 6 n-tiles
-    const size_t smem_cap = ctx->smem_optin;
-    int bc = std::min(a.batch, kMaxBatchChunk);
-    while (bc > 1 && gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) > smem_cap) bc--;
-    JUNO_REQUIRE(gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) <= smem_cap, "gemv: K=%d does not fit shared memory",
-                 a.K);
-
-    // K split: enough tasks to give every resident warp work, using divisors of nb only
-    const int ctas_per_sm = (gemv_smem_bytes(a.K, 3 * bc, (3 * bc + 7) / 8, bc) * 2 <= smem_cap) ? 2 : 1;
-    const int max_grid = ctx->sm_count * ctas_per_sm;
-    const int want_tasks = max_grid * kWarps * 2;
-    int kw = 1;
-    for (int d = 1; d <= nb; d++) {
-        if (nb % d) continue;
-        kw = d;
-        if ((long long)total_rt * d >= want_tasks) break;
-    }
-    kw = env_int("JUNO_GEMV_KW", kw);
-    if (kw < 1 || nb % kw) kw = 1;
-    const int ntasks = total_rt * kw;
-    // grid: best balance of tasks over warps, preferring more CTAs
-    int grid = std::min(max_grid, (ntasks + kWarps - 1) / kWarps);
-    {
-        double best = -1;
-        int best_g = grid;
-        for (int g = grid; g >= std::min(grid, ctx->sm_count); g--) {
-            long long wps = (long long)g * kWarps;
-            long long rounds = (ntasks + wps - 1) / wps;
-            double eff = (double)ntasks / (double)(rounds * wps);
-            if (eff > best + 1e-9) {
-                best = eff;
-                best_g = g;
-            }
-        }
-        grid = best_g;
-    }
-    grid = env_int("JUNO_GEMV_GRID", grid);
-    if (grid < 1) grid = 1;
-
-    int rows_pad_total = total_rt * 16;
-    if (kw > 1) {
-        size_t need = (size_t)kw * bc * rows_pad_total * sizeof(float);
-        void *pp = ctx->gemv_scratch.partial;
-        JUNO_TRY(ensure_device(&pp, &ctx->gemv_scratch.partial_bytes, need));
-        ctx->gemv_scratch.partial = (float *)pp;
-        if ((size_t)total_rt > ctx->gemv_scratch.n_counters) {
-            void *cp = ctx->gemv_scratch.counters;
-            size_t curb = ctx->gemv_scratch.n_counters * sizeof(unsigned);
-            size_t wantb = (size_t)std::max(total_rt, 16384) * sizeof(unsigned);
-            JUNO_TRY(ensure_device(&cp, &curb, wantb));
-            ctx->gemv_scratch.counters = (unsigned *)cp;
-            ctx->gemv_scratch.n_counters = curb / sizeof(unsigned);
-            JUNO_CUDA_TRY(cudaMemsetAsync(cp, 0, curb, st));
-        }
-    }
+    JUNO_REQUIRE(gemv_smem_bytes(a.K, 1) <= ctx->smem_optin, "gemv: K=%d does not fit shared memory", a.K);
 
     double algo_bytes = (double)a.batch * a.K * 4;
     {
@@ -627,8 +677,25 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
         for (int s = 0; s < a.nseg; s++) algo_bytes += (double)a.seg[s].rows * a.K * bpw + (double)a.batch * a.seg[s].rows * 4;
     }
     ProfScope prof(ctx, st, a.type == 12 ? PROF_GEMV_Q4K : a.type == 14 ? PROF_GEMV_Q6K : PROF_GEMV_Q80, algo_bytes);
-    for (int b0 = 0; b0 < a.batch; b0 += bc) {
-        const int nbatch = std::min(bc, a.batch - b0);
+
+    const int bc_full = gemv_batch_chunk(ctx, a.K, a.batch);
+    const size_t chunk_stride = stage_chunk_bytes(a.K, bc_full);
+    for (int b0 = 0, chunk = 0; b0 < a.batch; b0 += bc_full, chunk++) {
+        const int bc = std::min(bc_full, a.batch - b0);
+        const size_t smem = gemv_smem_bytes(a.K, bc);
+        const int ctas_per_sm = (smem * 2 + 2048 <= ctx->smem_optin) ? 2 : 1;
+        const int max_grid = ctx->sm_count * ctas_per_sm;
+        // warps per row tile (K split inside the CTA): the smallest split that still yields several CTA tasks per
+        // resident CTA (for balance), else the largest one (for parallelism); at least two tiles per warp per task
+        int kin = 1;
+        for (int d = 1; d <= kWarps; d *= 2) {
+            if (nb % d || (d > 1 && nb / d < 2)) break;
+            kin = d;
+            const int groups = kWarps / d;
+            if ((total_rt + groups - 1) / groups >= 4 * max_grid) break;
+        }
+        kin = env_int("JUNO_GEMV_KIN", kin);
+        if (kin < 1 || kin > kWarps || (kin & (kin - 1)) || nb % kin) kin = 1;
         GemvParams p;
         memset(&p, 0, sizeof(p));
         int rt = 0;
@@ -641,34 +708,27 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
         }
         for (int s = a.nseg; s < 4; s++) p.rt_begin[s] = rt;
         p.nseg = a.nseg;
+        p.total_rt = total_rt;
         p.K = a.K;
         p.nb = nb;
-        p.batch = nbatch;
-        p.ncols = 3 * nbatch;
-        p.kw = kw;
-        p.tiles_per_task = nb / kw;
-        p.ntasks = ntasks;
+        p.kin = kin;
+        p.tpt = nb / kin;
+        p.groups = kWarps / kin;
+        p.n_ctasks = (total_rt + p.groups - 1) / p.groups;
         p.ld_out = a.ld_out;
-        p.pro = a.pro;
-        p.x = a.x + (size_t)b0 * a.ldx;
-        p.ldx = a.ldx;
-        p.x_add = a.x_add ? a.x_add + (size_t)b0 * a.ldx : nullptr;
-        p.normw = a.normw;
-        p.up = a.up ? a.up + (size_t)b0 * a.ldx : nullptr;
-        p.x_out = a.x_out ? a.x_out + (size_t)b0 * a.ldx : nullptr;
-        p.eps = a.eps;
-        p.partial = ctx->gemv_scratch.partial;
-        p.counters = ctx->gemv_scratch.counters;
-        p.rows_pad_total = rows_pad_total;
-        const int NT = (p.ncols + 7) / 8;
-        const size_t smem = gemv_smem_bytes(a.K, p.ncols, NT, nbatch);
+        p.epi = a.epi;
+        p.ximg = a.ximg + (size_t)chunk * chunk_stride;
+        p.img_bytes = (unsigned)stage_chunk_bytes(a.K, bc);
+        p.counters = ctx->gemv_scratch.counters + 2 * (ctx->gemv_scratch.next_slot++ % kGemvCounterSlots);
+        int grid = std::min(max_grid, p.n_ctasks);
+        grid = std::max(1, std::min(env_int("JUNO_GEMV_GRID", grid), p.n_ctasks));
         int rc;
         if (a.type == 12)
-            rc = launch_type<12>(ctx, p, NT, grid, smem, st);
+            rc = launch_type<12>(ctx, p, bc, grid, smem, st);
         else if (a.type == 14)
-            rc = launch_type<14>(ctx, p, NT, grid, smem, st);
+            rc = launch_type<14>(ctx, p, bc, grid, smem, st);
         else
-            rc = launch_type<8>(ctx, p, NT, grid, smem, st);
+            rc = launch_type<8>(ctx, p, bc, grid, smem, st);
         JUNO_TRY(rc);
     }
     return JUNO_OK;
@@ -677,6 +737,31 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
 // ───────────────────────────── repack (raw GGUF blocks -> tiles) ───────────────────────────
 // raw: device copy of rows [0,nrows) of the source tensor, row stride raw_row_bytes; the tile matrix covers
 // super-blocks [sb0, sb0+nsb) of each row.  One thread per 32-bit output word.
+__host__ __device__ inline uint32_t q4k_out_word(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb_abs, int R,
+                                                 int w) {
+    // w: 32-bit word index inside the 2368-byte tile (0..591)
+    if (w < 16) {  // d | dmin
+        int row = R * 16 + w;
+        if (row >= nrows) return 0;
+        const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 144;
+        return (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    } else if (w < 80) {  // scales and mins of sub-blocks 2c, 2c+1 as bytes
+        int v = w - 16, row16 = v >> 2, c = v & 3;
+        int row = R * 16 + row16;
+        if (row >= nrows) return 0;
+        const uint8_t *sc = raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 144 + 4;
+        return (uint32_t)q4k_scale6(sc, 2 * c) | ((uint32_t)q4k_scale6(sc, 2 * c + 1) << 8) |
+               ((uint32_t)q4k_min6(sc, 2 * c) << 16) | ((uint32_t)q4k_min6(sc, 2 * c + 1) << 24);
+    } else {
+        int row16, off;
+        q4k_qs_word_src(w - 80, row16, off);
+        int row = R * 16 + row16;
+        if (row >= nrows) return 0;
+        const uint8_t *s = raw + (size_t)row * raw_row_bytes + (size_t)sb_abs * 144 + off;
+        return (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    }
+}
+
 __global__ void repack_q4k_kernel(const uint8_t *raw, size_t raw_row_bytes, int nrows, int sb0, int nsb, uint8_t *out) {
     const size_t words_per_tile = kQ4KTileBytes / 4;
     size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -685,15 +770,7 @@ __global__ void repack_q4k_kernel(const uint8_t *raw, size_t raw_row_bytes, int 
     size_t tile = gidx / words_per_tile;
     int w = (int)(gidx - tile * words_per_tile);
     int R = (int)(tile / nsb), b = (int)(tile - (size_t)R * nsb);
-    int row16, off;
-    q4k_word_src(w, row16, off);
-    int row = R * 16 + row16;
-    uint32_t v = 0;
-    if (row < nrows) {
-        const uint8_t *src = raw + (size_t)row * raw_row_bytes + (size_t)(sb0 + b) * 144 + off;
-        v = (uint32_t)src[0] | ((uint32_t)src[1] << 8) | ((uint32_t)src[2] << 16) | ((uint32_t)src[3] << 24);
-    }
-    reinterpret_cast<uint32_t *>(out)[gidx] = v;
+    reinterpret_cast<uint32_t *>(out)[gidx] = q4k_out_word(raw, raw_row_bytes, nrows, sb0 + b, R, w);
 }
 
 __host__ __device__ inline uint32_t q6k_tile_word(const uint8_t *blk_row /* raw block of (row, sb) or null */, int w,
@@ -811,13 +888,7 @@ extern "C" int juno_dbg_repack_host(int type, const uint8_t *raw, int64_t rows, 
             for (int w = 0; w < wpt; w++) {
                 uint32_t v = 0;
                 if (type == 12) {
-                    int row16, off;
-                    q4k_word_src(w, row16, off);
-                    int row = R * 16 + row16;
-                    if (row < rows) {
-                        const uint8_t *s = raw + (size_t)row * rrb + (size_t)b * 144 + off;
-                        v = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
-                    }
+                    v = q4k_out_word(raw, rrb, (int)rows, b, R, w);
                 } else if (type == 14) {
                     v = q6k_out_word(raw, rrb, (int)rows, b, R, w);
                 } else {

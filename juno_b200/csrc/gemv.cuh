@@ -17,10 +17,32 @@ struct juno_qmat {
 
 namespace juno {
 
-enum GemvPrologue {
-    PRO_PLAIN = 0,   // v = x[i]
-    PRO_RMSNORM = 1, // r = x[i] (+ x_add[i]); optional store of r to x_out by block 0; v = (normw[i]*r)*rsqrt-scale
-    PRO_SILU = 2,    // v = silu(x[i]) * up[i]
+enum StageMode {
+    STAGE_PLAIN = 0,    // v = x[i]
+    STAGE_RMSNORM = 1,  // r = x[i] (+ x_add[i]); optional store of r to x_out; v = (normw[i]*r)*scale  (rmsNorm :818-828)
+};
+
+// The activation as the GEMV kernels consume it: three bf16 limbs per value in MMA feed order plus the
+// per-32-column sums (layout.cuh), for batch chunks of at most `bc` rows.  Written once per product by
+// launch_stage (or by a producer kernel) and copied into shared memory by every GEMV CTA.
+struct StageArgs {
+    int mode = STAGE_PLAIN;
+    const float *x = nullptr;  // [batch][ldx]
+    int ldx = 0;
+    const float *x_add = nullptr, *normw = nullptr;
+    float *x_out = nullptr;
+    float eps = 0.f;
+    int K = 0, batch = 1;
+    uint8_t *img = nullptr;    // at least stage_image_bytes(K, batch)
+};
+int gemv_batch_chunk(const juno_ctx *ctx, int K, int batch);   // rows per chunk (1..8)
+size_t stage_chunk_bytes(int K, int rows_in_chunk);
+size_t stage_image_bytes(const juno_ctx *ctx, int K, int batch);
+int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t stream);
+
+enum GemvEpilogue {
+    EPI_STORE = 0,      // out[b][row] = y
+    EPI_SILU_PAIR = 1,  // tile rows 0-7 are gate rows, 8-15 the matching up rows: out[b][8*tile+row] = silu(gate)*up
 };
 
 struct GemvSeg {
@@ -37,12 +59,8 @@ struct GemvArgs {
     int K = 0;
     int batch = 1;
     int ld_out = 0;   // stride between batch rows of every seg.out
-    int pro = PRO_PLAIN;
-    const float *x = nullptr;  // [batch][ldx]
-    int ldx = 0;
-    const float *x_add = nullptr, *normw = nullptr, *up = nullptr;
-    float *x_out = nullptr;
-    float eps = 0.f;
+    int epi = EPI_STORE;
+    const uint8_t *ximg = nullptr;  // staged activation (launch_stage) for this K and batch
 };
 
 // Enqueues the product on `stream`.  All pointers are device pointers.

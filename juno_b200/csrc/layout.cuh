@@ -24,7 +24,7 @@ namespace juno {
 
 constexpr int kTileRows = 16;
 constexpr int kTileCols = 256;
-constexpr int kQ4KTileBytes = 2304;  // 16 x 144
+constexpr int kQ4KTileBytes = 2368;  // 16 x 148: scales and mins widened to bytes
 constexpr int kQ6KTileBytes = 3360;  // 16 x 210
 constexpr int kQ80TileBytes = 4352;  // 16 x 8 x 34
 
@@ -37,23 +37,20 @@ JHD int raw_block_elems(int ggml_type) { return ggml_type == 8 ? 32 : ggml_type 
 // Position of column-in-s16 t (0..3 inside a lane's group of four) in MMA feed order.
 JHD int feed_pos(int t) { return ((t & 1) << 1) | (t >> 1); }
 
-// ── Q4_K tile (2304 B) ──────────────────────────────────────────────────────────
-//   [0,256)    hdr[row16]   : the raw 16-byte block header (d:f16, dmin:f16, scales:12)
-//   [256,2304) qs[g4][lane32] 16 B : word0 = row r8   raw qs[32g+4c .. +4)      (cols 64g+4c..   lo nibble, 64g+32+4c.. hi nibble)
+// ── Q4_K tile (2368 B) ──────────────────────────────────────────────────────────
+//   [0,64)     dm[row16]      : d:f16 | dmin:f16 << 16
+//   [64,320)   sm[row16][c4]  : the two sub-blocks 2c, 2c+1 that lane column c decodes, widened from 6 bits to bytes:
+//                               scale(2c) | scale(2c+1) << 8 | min(2c) << 16 | min(2c+1) << 24
+//   [320,2368) qs[g4][lane32] 16 B : word0 = row r8   raw qs[32g+4c .. +4)      (cols 64g+4c..   lo nibble, 64g+32+4c.. hi nibble)
 //                                    word1 = row r8   raw qs[32g+16+4c .. +4)
 //                                    word2 = row r8+8 raw qs[32g+4c .. +4)
 //                                    word3 = row r8+8 raw qs[32g+16+4c .. +4)
-// Source of output 32-bit word w (0..575): row in tile and byte offset inside that row's raw block.
-JHD void q4k_word_src(int w, int &row16, int &raw_off) {
-    if (w < 64) {
-        row16 = w >> 2;
-        raw_off = (w & 3) * 4;
-    } else {
-        int v = w - 64;
-        int g = v >> 7, lane = (v >> 2) & 31, k = v & 3;
-        row16 = (lane >> 2) + 8 * (k >> 1);
-        raw_off = 16 + 32 * g + 16 * (k & 1) + 4 * (lane & 3);
-    }
+constexpr int kQ4KQsOff = 320;
+// Source of qs output word v (0..511): row in tile and byte offset inside that row's raw block.
+JHD void q4k_qs_word_src(int v, int &row16, int &raw_off) {
+    int g = v >> 7, lane = (v >> 2) & 31, k = v & 3;
+    row16 = (lane >> 2) + 8 * (k >> 1);
+    raw_off = 16 + 32 * g + 16 * (k & 1) + 4 * (lane & 3);
 }
 // Location of element (row16, e in 0..255) in the tile: byte offset of its qs byte, and which nibble.
 JHD void q4k_elem_loc(int row16, int e, int &byte_off, int &hi_nibble) {
@@ -61,7 +58,7 @@ JHD void q4k_elem_loc(int row16, int e, int &byte_off, int &hi_nibble) {
     hi_nibble = (e >> 5) & 1;
     int half16 = idx >> 4, c = (idx >> 2) & 3, bw = idx & 3;
     int lane = ((row16 & 7) << 2) | c, k = 2 * (row16 >> 3) + half16;
-    byte_off = 256 + g * 512 + lane * 16 + k * 4 + bw;
+    byte_off = kQ4KQsOff + g * 512 + lane * 16 + k * 4 + bw;
 }
 // 6-bit scale / min j of the 12 packed bytes (LlamaTransformerHandler.java:1471-1482).
 JHD int q4k_scale6(const uint8_t *sc, int j) {

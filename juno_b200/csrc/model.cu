@@ -180,7 +180,9 @@ __global__ void ungather_logits_kernel(LogitsView lv, float *out) {
 
 // ───────────────────────────── model object ───────────────────────────────────────────────
 struct JunoLayer {
-    juno_qmat *w[12] = {nullptr};  // indexed by tensor kind (ATTN_Q .. FFN_DOWN)
+    juno_qmat *w[12] = {nullptr};  // indexed by tensor kind (ATTN_Q .. FFN_DOWN); gate and up share w[FFN_GATE]
+    std::vector<uint8_t> gate_host, up_host;  // row slices waiting for their partner
+    int gate_type = -1, up_type = -1;
     float *attn_norm = nullptr, *ffn_norm = nullptr;
 };
 
@@ -206,7 +208,8 @@ struct juno_model {
     juno_kvpool *pool = nullptr;
     juno::NcclComm comm = nullptr;
     // activations
-    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *gu = nullptr;
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *hdn = nullptr;
+    uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
     size_t attn_scratch_floats = 0;
@@ -288,7 +291,7 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->gu, m->logits_loc, m->logits_gather, m->logits_full,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->hdn, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
                     m->attn_scratch, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
@@ -412,6 +415,29 @@ int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void
         JUNO_REQUIRE(type == JUNO_TYPE_Q4_K || type == JUNO_TYPE_Q6_K || type == JUNO_TYPE_Q8_0,
                      "projection weights must be Q4_K, Q6_K or Q8_0 (got GGML type %d)", type);
     if (m->world == 1) sb0 = nsb = 0;
+    if (kind == JUNO_T_FFN_GATE || kind == JUNO_T_FFN_UP) {
+        // gate and up rows are interleaved in groups of eight (tile rows 0-7 gate, 8-15 up) so that the GEMV
+        // epilogue holds silu(gate_i) and up_i together; the first of the pair waits on the host for its partner
+        JunoLayer &L = m->layers[layer];
+        JUNO_REQUIRE(m->inter_loc % 8 == 0, "feed_forward_length per rank must be a multiple of 8");
+        const int64_t rb = cols / raw_block_elems(type) * raw_block_bytes(type);
+        const uint8_t *src = static_cast<const uint8_t *>(blocks) + row0 * rb;
+        std::vector<uint8_t> &mine = kind == JUNO_T_FFN_GATE ? L.gate_host : L.up_host;
+        mine.assign(src, src + nrows * rb);
+        (kind == JUNO_T_FFN_GATE ? L.gate_type : L.up_type) = type;
+        if (L.gate_host.empty() || L.up_host.empty()) return JUNO_OK;
+        JUNO_REQUIRE(L.gate_type == L.up_type, "layer %d: ffn_gate and ffn_up must share one block format", layer);
+        std::vector<uint8_t> both((size_t)2 * nrows * rb);
+        for (int64_t t = 0; t < nrows / 8; t++) {
+            memcpy(&both[(size_t)(2 * t) * 8 * rb], &L.gate_host[(size_t)t * 8 * rb], (size_t)8 * rb);
+            memcpy(&both[(size_t)(2 * t + 1) * 8 * rb], &L.up_host[(size_t)t * 8 * rb], (size_t)8 * rb);
+        }
+        free_qmat(L.w[JUNO_T_FFN_GATE]);
+        int rc = qmat_create(c, both.data(), type, 2 * nrows, cols, 0, 2 * nrows, 0, 0, &L.w[JUNO_T_FFN_GATE]);
+        std::vector<uint8_t>().swap(L.gate_host);
+        std::vector<uint8_t>().swap(L.up_host);
+        return rc;
+    }
     juno_qmat **slot = kind == JUNO_T_TOKEN_EMBD ? &m->tok_embd : kind == JUNO_T_OUTPUT ? &m->output : &m->layers[layer].w[kind];
     free_qmat(*slot);
     JUNO_TRY(qmat_create(c, blocks, type, rows, cols, row0, nrows, sb0, nsb, slot));
@@ -446,7 +472,8 @@ extern "C" int juno_model_finalize(juno_model *m) {
     for (int l = 0; l < f.n_layers; l++) {
         JunoLayer &L = m->layers[l];
         JUNO_REQUIRE(L.attn_norm && L.ffn_norm, "layer %d: norm weights missing", l);
-        for (int k = JUNO_T_ATTN_Q; k <= JUNO_T_FFN_DOWN; k++) JUNO_REQUIRE(L.w[k], "layer %d: tensor kind %d missing", l, k);
+        for (int k = JUNO_T_ATTN_Q; k <= JUNO_T_FFN_DOWN; k++)
+            if (k != JUNO_T_FFN_UP) JUNO_REQUIRE(L.w[k], "layer %d: tensor kind %d missing", l, k);
     }
     const int B = f.max_batch, H = f.hidden, hd = m->hd;
     const int max_pages_per_seq = (f.max_ctx + kPageTokens - 1) / kPageTokens;
@@ -460,7 +487,10 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->qkv, (size_t)B * m->qkv_ld * 4));
     JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
-    JUNO_TRY(dev_alloc((void **)&m->gu, (size_t)B * 2 * m->inter_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->img_h, stage_image_bytes(c, H, B)));
+    JUNO_TRY(dev_alloc((void **)&m->img_att, stage_image_bytes(c, m->heads_loc * hd, B)));
+    JUNO_TRY(dev_alloc((void **)&m->img_i, stage_image_bytes(c, m->inter_loc, B)));
     JUNO_TRY(dev_alloc((void **)&m->logits_loc, (size_t)B * m->vocab_loc * 4));
     if (m->vocab_sharded) {
         JUNO_TRY(dev_alloc((void **)&m->logits_gather, (size_t)B * f.vocab * 4));
@@ -483,29 +513,56 @@ namespace juno {
 
 // ───────────────────────────── one decode step, enqueued on the context stream ────────────
 static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, int ld_out, int batch,
-                      const GemvArgs &proto, cudaStream_t st) {
+                      const uint8_t *ximg, int epi, cudaStream_t st) {
     // consecutive matrices of one block format share a launch (they share the staged activation)
     int i = 0;
     while (i < count) {
         int j = i + 1;
         while (j < count && j - i < 3 && mats[j]->type == mats[i]->type) j++;
-        GemvArgs a = proto;
+        GemvArgs a;
         a.nseg = j - i;
         for (int s = 0; s < a.nseg; s++) {
             a.seg[s].w = mats[i + s]->dev;
             a.seg[s].out = outs[i + s];
-            a.seg[s].rows = (int)mats[i + s]->rows;
+            a.seg[s].rows = epi == EPI_SILU_PAIR ? (int)mats[i + s]->rows / 2 : (int)mats[i + s]->rows;
             a.seg[s].row_tiles = (int)mats[i + s]->row_tiles;
         }
         a.type = mats[i]->type;
         a.K = (int)mats[i]->cols;
         a.batch = batch;
         a.ld_out = ld_out;
-        if (i > 0) a.x_out = nullptr;  // the residual stream is written once
+        a.epi = epi;
+        a.ximg = ximg;
         JUNO_TRY(launch_gemv(m->ctx, a, st));
         i = j;
     }
     return JUNO_OK;
+}
+
+static int stage_rms(juno_model *m, int n, const float *x, const float *add, float *x_out, const float *normw,
+                     cudaStream_t st) {
+    StageArgs a;
+    a.mode = STAGE_RMSNORM;
+    a.x = x;
+    a.ldx = m->cfg.hidden;
+    a.x_add = add;
+    a.x_out = x_out;
+    a.normw = normw;
+    a.eps = m->cfg.rms_eps;
+    a.K = m->cfg.hidden;
+    a.batch = n;
+    a.img = m->img_h;
+    return launch_stage(m->ctx, a, st);
+}
+static int stage_plain(juno_model *m, int n, const float *x, int K, uint8_t *img, cudaStream_t st) {
+    StageArgs a;
+    a.mode = STAGE_PLAIN;
+    a.x = x;
+    a.ldx = K;
+    a.K = K;
+    a.batch = n;
+    a.img = img;
+    return launch_stage(m->ctx, a, st);
 }
 
 static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
@@ -526,23 +583,16 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
     }
     JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
 
-    int cur = 0;                   // x[cur] holds the residual stream entering the layer
-    const float *pending = nullptr; // projection still to be added to it (fused into the next RMSNorm prologue)
+    int cur = 0;                    // x[cur] holds the residual stream entering the layer
+    const float *pending = nullptr; // projection still to be added to it (done by the next RMSNorm staging)
     for (int l = 0; l < f.n_layers; l++) {
         JunoLayer &L = m->layers[l];
         // xn = rmsNorm(x (+ pending)); q,k,v = W·xn
-        GemvArgs a;
-        a.pro = PRO_RMSNORM;
-        a.x = m->x[cur];
-        a.ldx = H;
-        a.x_add = pending;
-        a.x_out = pending ? m->x[cur ^ 1] : nullptr;
-        a.normw = L.attn_norm;
-        a.eps = f.rms_eps;
+        JUNO_TRY(stage_rms(m, n, m->x[cur], pending, pending ? m->x[cur ^ 1] : nullptr, L.attn_norm, st));
+        if (pending) cur ^= 1;
         juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
         float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
-        JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, m->qkv_ld, n, a, st));
-        if (pending) cur ^= 1;
+        JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, m->qkv_ld, n, m->img_h, EPI_STORE, st));
         JUNO_TRY(launch_rope_append(c, m->pool, l, n, m->heads_loc, m->qkv, m->qkv_ld, m->qkv + Hl, m->qkv + Hl + KVl,
                                     m->qkv_ld, d_slot, d_pos, m->rope_cs, st));
         AttnArgs at;
@@ -561,51 +611,30 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         at.algo_bytes = m->step_kv_bytes;
         JUNO_TRY(launch_attn(c, at, st));
         // proj = Wo·att  (row-parallel under TP: partial sums, all-reduced)
-        GemvArgs o;
-        o.pro = PRO_PLAIN;
-        o.x = m->att;
-        o.ldx = Hl;
+        JUNO_TRY(stage_plain(m, n, m->att, Hl, m->img_att, st));
         juno_qmat *o_m[1] = {L.w[JUNO_T_ATTN_OUT]};
         float *o_o[1] = {m->proj};
-        JUNO_TRY(gemv_group(m, o_m, o_o, 1, H, n, o, st));
+        JUNO_TRY(gemv_group(m, o_m, o_o, 1, H, n, m->img_att, EPI_STORE, st));
         if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
-        // x2 = x + proj ; xn2 = rmsNorm(x2) ; gate, up = W·xn2
-        GemvArgs gu;
-        gu.pro = PRO_RMSNORM;
-        gu.x = m->x[cur];
-        gu.ldx = H;
-        gu.x_add = m->proj;
-        gu.x_out = m->x[cur ^ 1];
-        gu.normw = L.ffn_norm;
-        gu.eps = f.rms_eps;
-        juno_qmat *gu_m[2] = {L.w[JUNO_T_FFN_GATE], L.w[JUNO_T_FFN_UP]};
-        float *gu_o[2] = {m->gu, m->gu + Il};
-        JUNO_TRY(gemv_group(m, gu_m, gu_o, 2, 2 * Il, n, gu, st));
+        // x2 = x + proj ; xn2 = rmsNorm(x2) ; hdn = silu(Wgate·xn2) * (Wup·xn2)
+        JUNO_TRY(stage_rms(m, n, m->x[cur], m->proj, m->x[cur ^ 1], L.ffn_norm, st));
         cur ^= 1;
-        // proj = Wdown·(silu(gate)*up)
-        GemvArgs d;
-        d.pro = PRO_SILU;
-        d.x = m->gu;
-        d.up = m->gu + Il;
-        d.ldx = 2 * Il;
+        juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
+        float *gu_o[1] = {m->hdn};
+        JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, Il, n, m->img_h, EPI_SILU_PAIR, st));
+        // proj = Wdown·hdn
+        JUNO_TRY(stage_plain(m, n, m->hdn, Il, m->img_i, st));
         juno_qmat *d_m[1] = {L.w[JUNO_T_FFN_DOWN]};
         float *d_o[1] = {m->proj};
-        JUNO_TRY(gemv_group(m, d_m, d_o, 1, H, n, d, st));
+        JUNO_TRY(gemv_group(m, d_m, d_o, 1, H, n, m->img_i, EPI_STORE, st));
         if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
         pending = m->proj;
     }
     // logits = Wout · rmsNorm(x + pending, output_norm)
-    GemvArgs lo;
-    lo.pro = PRO_RMSNORM;
-    lo.x = m->x[cur];
-    lo.ldx = H;
-    lo.x_add = pending;
-    lo.x_out = m->x[cur ^ 1];
-    lo.normw = m->output_norm;
-    lo.eps = f.rms_eps;
+    JUNO_TRY(stage_rms(m, n, m->x[cur], pending, m->x[cur ^ 1], m->output_norm, st));
     juno_qmat *l_m[1] = {m->output};
     float *l_o[1] = {m->logits_loc};
-    JUNO_TRY(gemv_group(m, l_m, l_o, 1, m->vocab_loc, n, lo, st));
+    JUNO_TRY(gemv_group(m, l_m, l_o, 1, m->vocab_loc, n, m->img_h, EPI_STORE, st));
     m->last_x = cur ^ 1;
     LogitsView lv;
     lv.n = n;

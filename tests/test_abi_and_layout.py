@@ -54,7 +54,7 @@ def test_tile_layout_round_trip_bit_exact(oracle, t, rows, cols):
     L.juno_dbg_dequant_tiled_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
     raw = synth.random_blocks(np.random.default_rng(t), t, rows, cols)
     n = L.juno_dbg_tiled_bytes(t, rows, cols)
-    assert n == ((rows + 15) // 16) * (cols // 256) * {12: 2304, 14: 3360, 8: 4352}[t]
+    assert n == ((rows + 15) // 16) * (cols // 256) * {12: 2368, 14: 3360, 8: 4352}[t]
     tiles = np.zeros(n, dtype=np.uint8)
     assert L.juno_dbg_repack_host(t, raw.ctypes.data, rows, cols, tiles.ctypes.data) == 0
     out = np.empty((rows, cols), dtype=np.float32)
