@@ -195,6 +195,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="start decoding at an empty context (quick runs)")
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="start at position ctx-1 over a zero-filled KV cache (same bytes per step; for profiler runs)")
     args = ap.parse_args()
     arch, seed = MODELS[args.model]
     rank = int(os.environ.get("RANK", "0"))
@@ -237,7 +239,7 @@ def main():
     names = [f"s{i}" for i in range(B)]
     prompts = rng.integers(0, arch.vocab, (B, max(1, args.ctx)))
     # prefill token by token, as GenerationLoop does (positions 0..ctx-2, logits discarded)
-    for p in range(start):
+    for p in ([] if args.skip_prefill else range(start)):
         h.forward_batch(names, [[int(prompts[i, p])] for i in range(B)], [p] * B, want_logits=False, want_argmax=True)
     stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", local_rank))
     pos = start

@@ -10,6 +10,7 @@
 #include <cmath>
 
 #include "attn.cuh"
+#include "stage.cuh"
 
 namespace juno {
 
@@ -22,6 +23,13 @@ struct AttnParams {
     int ldq;
     const int32_t *slots, *seq_lens;
     float *part_o, *part_ml, *out;
+    StageImage stage;  // img == nullptr: not requested
+    // fused RoPE + KV append (rope_cs != nullptr): q is rotated on load, and the CTA whose split holds the newest
+    // position rotates k, rounds k and v to the cache type, uses them and writes them to their page
+    const float2 *rope_cs;
+    const float *knew, *vnew;
+    int ldkv;
+    void *kw, *vw;
 };
 
 template <typename T>
@@ -31,36 +39,43 @@ __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 
-template <typename T, int EPL>
-__device__ __forceinline__ void load_vec(const T *p, float (&o)[EPL]);
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
 template <>
-__device__ __forceinline__ void load_vec<__half, 4>(const __half *p, float (&o)[4]) {
-    uint2 u = *reinterpret_cast<const uint2 *>(p);
-    float2 a = __half22float2(*reinterpret_cast<__half2 *>(&u.x)), b = __half22float2(*reinterpret_cast<__half2 *>(&u.y));
-    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Eight consecutive head dimensions of one cached position, widened to FP32.
+template <typename T>
+__device__ __forceinline__ void load8(const T *p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8<__half>(const __half *p, float (&o)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        o[2 * i] = f.x;
+        o[2 * i + 1] = f.y;
+    }
 }
 template <>
-__device__ __forceinline__ void load_vec<__half, 2>(const __half *p, float (&o)[2]) {
-    uint32_t u = *reinterpret_cast<const uint32_t *>(p);
-    float2 a = __half22float2(*reinterpret_cast<__half2 *>(&u));
-    o[0] = a.x; o[1] = a.y;
-}
-template <>
-__device__ __forceinline__ void load_vec<float, 4>(const float *p, float (&o)[4]) {
-    float4 u = *reinterpret_cast<const float4 *>(p);
-    o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w;
-}
-template <>
-__device__ __forceinline__ void load_vec<float, 2>(const float *p, float (&o)[2]) {
-    float2 u = *reinterpret_cast<const float2 *>(p);
-    o[0] = u.x; o[1] = u.y;
+__device__ __forceinline__ void load8<float>(const float *p, float (&o)[8]) {
+    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+    o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
 }
 
 constexpr int kAttnWarps = 4;
+constexpr int kAttnUnroll = 4;  // positions in flight per token slot
 
+// One CTA = (kv head, context split, sequence).  HD/8 lanes share one cached position (eight head dimensions
+// each, one 128-bit load for K and one for V), so a warp works on 32/(HD/8) positions at a time and every lane
+// keeps an online-softmax state for the G query heads of the group; the states are merged through shared memory.
 template <typename T, int HD, int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnParams p) {
-    constexpr int EPL = HD / 32;
+    constexpr int LPT = HD / 8, TPW = 32 / LPT, SLOTS = kAttnWarps * TPW;
     const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int len = p.seq_lens[seq];
@@ -76,103 +91,170 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
         }
         return;
     }
-    const float scale = (float)(1.0 / sqrt((double)HD));
-    float qr[G][EPL], o[G][EPL], m[G], l[G];
+    const int sub = lane % LPT, slot = warp * TPW + lane / LPT;
+    const unsigned gmask = (LPT == 32) ? 0xffffffffu : (((1u << LPT) - 1u) << (lane - sub));
+    // scores in the log2 domain: exp(x) = exp2(x * log2(e))
+    const float scale = (float)(1.0 / sqrt((double)HD)) * 1.4426950408889634f;
+    float qr[G][8], o[G][8], m[G], l[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
-        const float *qp = p.q + (size_t)seq * p.ldq + (size_t)(h0 + g) * HD + lane * EPL;
+        const float *qp = p.q + (size_t)seq * p.ldq + (size_t)(h0 + g) * HD + sub * 8;
 #pragma unroll
-        for (int e = 0; e < EPL; e++) {
-            qr[g][e] = qp[e];
-            o[g][e] = 0.f;
+        for (int e = 0; e < 8; e += 2) {
+            float x0 = qp[e], x1 = qp[e + 1];
+            if (p.rope_cs) {  // adjacent-pair rotation, each product rounded (rope :1657-1671)
+                const float2 cs = p.rope_cs[seq * (HD / 2) + sub * 4 + (e >> 1)];
+                const float y0 = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+                const float y1 = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+                x0 = y0;
+                x1 = y1;
+            }
+            qr[g][e] = x0 * scale;
+            qr[g][e + 1] = x1 * scale;
+            o[g][e] = o[g][e + 1] = 0.f;
         }
         m[g] = -INFINITY;
         l[g] = 0.f;
     }
     const int32_t *table = p.table + (size_t)p.slots[seq] * p.max_pages_per_seq;
     const T *kbase = static_cast<const T *>(p.k), *vbase = static_cast<const T *>(p.v);
-    for (int t = t0 + warp; t < t1; t += kAttnWarps) {
-        const int page = table[t >> 4];
-        const size_t off = ((((size_t)p.layer * p.n_pages + page) * p.n_kv_heads + kvh) * kPageTokens + (t & 15)) * HD +
-                           lane * EPL;
-        float kv[EPL], vv[EPL];
-        load_vec<T, EPL>(kbase + off, kv);
-        load_vec<T, EPL>(vbase + off, vv);
-        float s[G];
+    const size_t head_off = (size_t)kvh * kPageTokens * HD + sub * 8;
+    const size_t page_stride = (size_t)p.n_kv_heads * kPageTokens * HD;
+    const size_t layer_off = (size_t)p.layer * p.n_pages * page_stride;
+    for (int tb = t0 + slot; tb < t1; tb += SLOTS * kAttnUnroll) {
+        float kv[kAttnUnroll][8], vv[kAttnUnroll][8];
 #pragma unroll
-        for (int g = 0; g < G; g++) {
-            float d = 0.f;
+        for (int u = 0; u < kAttnUnroll; u++) {
+            const int t = tb + u * SLOTS;
+            if (t < t1) {
+                const size_t off = layer_off + (size_t)table[t >> 4] * page_stride + head_off + (size_t)(t & 15) * HD;
+                if (p.rope_cs && t == len - 1) {  // the position being decoded: rotate, round, use and append
+                    const float *kx = p.knew + (size_t)seq * p.ldkv + kvh * HD + sub * 8;
+                    const float *vx = p.vnew + (size_t)seq * p.ldkv + kvh * HD + sub * 8;
+                    T *kd = static_cast<T *>(p.kw) + off, *vd = static_cast<T *>(p.vw) + off;
 #pragma unroll
-            for (int e = 0; e < EPL; e++) d = fmaf(qr[g][e], kv[e], d);
-            s[g] = d;
+                    for (int e = 0; e < 8; e += 2) {
+                        const float2 cs = p.rope_cs[seq * (HD / 2) + sub * 4 + (e >> 1)];
+                        const float x0 = kx[e], x1 = kx[e + 1];
+                        const T k0 = from_f32<T>(__fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y)));
+                        const T k1 = from_f32<T>(__fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x)));
+                        const T v0 = from_f32<T>(vx[e]), v1 = from_f32<T>(vx[e + 1]);
+                        kd[e] = k0; kd[e + 1] = k1;
+                        vd[e] = v0; vd[e + 1] = v1;
+                        kv[u][e] = to_f32<T>(k0); kv[u][e + 1] = to_f32<T>(k1);
+                        vv[u][e] = to_f32<T>(v0); vv[u][e + 1] = to_f32<T>(v1);
+                    }
+                } else {
+                    load8<T>(kbase + off, kv[u]);
+                    load8<T>(vbase + off, vv[u]);
+                }
+            }
         }
 #pragma unroll
-        for (int ofs = 16; ofs > 0; ofs >>= 1)
+        for (int u = 0; u < kAttnUnroll; u++) {
+            const int t = tb + u * SLOTS;
+            if (t < t1) {  // uniform over the LPT lanes of this position
+                float s[G];
 #pragma unroll
-            for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], ofs);
+                for (int g = 0; g < G; g++) {
+                    float d = 0.f;
 #pragma unroll
-        for (int g = 0; g < G; g++) {
-            const float sc = s[g] * scale;
-            const float mn = fmaxf(m[g], sc);
-            const float corr = expf(m[g] - mn), pe = expf(sc - mn);
-            l[g] = fmaf(l[g], corr, pe);
+                    for (int e = 0; e < 8; e++) d = fmaf(qr[g][e], kv[u][e], d);
+                    s[g] = d;
+                }
 #pragma unroll
-            for (int e = 0; e < EPL; e++) o[g][e] = fmaf(o[g][e], corr, pe * vv[e]);
-            m[g] = mn;
+                for (int ofs = LPT / 2; ofs > 0; ofs >>= 1)
+#pragma unroll
+                    for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(gmask, s[g], ofs);
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    const float mn = fmaxf(m[g], s[g]);
+                    const float corr = exp2f(m[g] - mn), pe = exp2f(s[g] - mn);
+                    l[g] = fmaf(l[g], corr, pe);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) o[g][e] = fmaf(o[g][e], corr, pe * vv[u][e]);
+                    m[g] = mn;
+                }
+            }
         }
     }
-    // merge the warps of this CTA
-    __shared__ float sm_m[kAttnWarps][G], sm_l[kAttnWarps][G];
-    __shared__ float sm_o[kAttnWarps][G][HD];
+    // merge the token slots of this CTA
+    __shared__ float sm_m[SLOTS][G], sm_l[SLOTS][G];
+    __shared__ float sm_o[SLOTS][G][HD];
 #pragma unroll
     for (int g = 0; g < G; g++) {
-        if (lane == 0) {
-            sm_m[warp][g] = m[g];
-            sm_l[warp][g] = l[g];
+        if (sub == 0) {
+            sm_m[slot][g] = m[g];
+            sm_l[slot][g] = l[g];
         }
 #pragma unroll
-        for (int e = 0; e < EPL; e++) sm_o[warp][g][lane * EPL + e] = o[g][e];
+        for (int e = 0; e < 8; e++) sm_o[slot][g][sub * 8 + e] = o[g][e];
     }
     __syncthreads();
     for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) {
         const int g = idx / HD, d = idx - g * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; w++) M = fmaxf(M, sm_m[w][g]);
+        for (int w = 0; w < SLOTS; w++) M = fmaxf(M, sm_m[w][g]);
         float L = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; w++) {
+        for (int w = 0; w < SLOTS; w++) {
             if (sm_l[w][g] > 0.f) {
-                const float f = expf(sm_m[w][g] - M);
+                const float f = exp2f(sm_m[w][g] - M);
                 L = fmaf(sm_l[w][g], f, L);
                 acc = fmaf(sm_o[w][g][d], f, acc);
             }
         }
         po[(size_t)g * p.n_splits * HD + d] = acc;
         if (d == 0) {
-            pml[(size_t)g * p.n_splits * 2 + 0] = M;
+            pml[(size_t)g * p.n_splits * 2 + 0] = M;  // log2 domain
             pml[(size_t)g * p.n_splits * 2 + 1] = L;
         }
     }
 }
 
+// Merges the context splits of one (sequence, head): blockDim = HD threads, one output dimension each.
+// The split weights are computed once in parallel (one split per thread) instead of once per output element.
 template <int HD>
 __global__ void attn_combine_kernel(const AttnParams p) {
-    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
     const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h) * p.n_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < p.n_splits; s++) M = fmaxf(M, pml[2 * s]);
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < p.n_splits; s++) {
-        const float ls = pml[2 * s + 1];
-        if (ls > 0.f) {
-            const float f = expf(pml[2 * s] - M);
-            L = fmaf(ls, f, L);
-            acc = fmaf(po[(size_t)s * HD + d], f, acc);
-        }
+    __shared__ float f[64], red[HD / 32], red2[HD / 32];
+    float ms = -INFINITY, ls = 0.f;
+    if (d < p.n_splits) {  // n_splits <= 64 <= HD
+        ms = pml[2 * d];
+        ls = pml[2 * d + 1];
     }
-    p.out[(size_t)(seq * p.n_heads + h) * HD + d] = (L > 0.f) ? acc / L : 0.f;
+    float M = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = red[0];
+#pragma unroll
+    for (int w = 1; w < HD / 32; w++) M = fmaxf(M, red[w]);
+    const float fs = (ls > 0.f) ? exp2f(ms - M) : 0.f;  // maxima are kept in the log2 domain
+    if (d < 64) f[d] = fs;
+    float L = ls * fs;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) red2[warp] = L;
+    __syncthreads();
+    L = 0.f;
+#pragma unroll
+    for (int w = 0; w < HD / 32; w++) L += red2[w];
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < p.n_splits; s++) acc = fmaf(po[(size_t)s * HD + d], f[s], acc);
+    const float outv = (L > 0.f) ? acc / L : 0.f;
+    p.out[(size_t)(seq * p.n_heads + h) * HD + d] = outv;
+    if (p.stage.img) {
+        unsigned short *xb;
+        int NC, col0;
+        p.stage.locate(seq, xb, NC, col0);
+        stage_store1(xb, NC, col0, h * HD + d, outv);
+    }
 }
 
 // cos/sin of pos * theta^(-2i/hd) in binary64, cast to float, as LlamaTransformerHandler.rope (:1662-1666).
@@ -185,13 +267,6 @@ __global__ void rope_table_kernel(const int32_t *positions, int n, int hd, float
     double angle = positions[seq] * freq;
     table[idx] = make_float2((float)cos(angle), (float)sin(angle));
 }
-
-template <typename T>
-__device__ __forceinline__ T from_f32(float v);
-template <>
-__device__ __forceinline__ float from_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
 struct RopeParams {
     void *k, *v;
@@ -300,6 +375,18 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     p.part_o = a.part_o;
     p.part_ml = a.part_ml;
     p.out = a.out;
+    p.rope_cs = a.rope_cs;
+    p.knew = a.knew;
+    p.vnew = a.vnew;
+    p.ldkv = a.ldkv;
+    p.kw = pool->k;
+    p.vw = pool->v;
+    p.stage.img = a.stage_img;
+    p.stage.K = a.n_heads * hd;
+    p.stage.batch = a.n;
+    p.stage.bc = a.stage_bc;
+    p.stage.b0 = 0;
+    p.stage.chunk_stride = a.stage_chunk_stride;
     ProfScope prof(ctx, st, PROF_ATTN, a.algo_bytes);
     int rc;
     if (pool->dtype == 0)

@@ -47,6 +47,15 @@ struct AttnArgs {
     float *part_o;       // [n][n_heads][n_splits][hd]
     float *part_ml;      // [n][n_heads][n_splits][2]
     double algo_bytes = 0;  // K+V bytes the call has to read (for the profiler)
+    // optional: fused RoPE + KV append.  q [n][ldq] is unrotated, knew/vnew [n][ldkv] hold this step's k and v,
+    // rope_cs the table of launch_rope_table; the newest position (seq_lens-1) is rotated, rounded and appended.
+    const float2 *rope_cs = nullptr;
+    const float *knew = nullptr, *vnew = nullptr;
+    int ldkv = 0;
+    // optional: also emit the output as a staged GEMV activation (K = n_heads*hd columns per sequence)
+    uint8_t *stage_img = nullptr;
+    int stage_bc = 1;
+    size_t stage_chunk_stride = 0;
 };
 size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits);
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len);

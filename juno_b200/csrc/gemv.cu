@@ -22,11 +22,26 @@
 #include "gemv.cuh"
 #include "layout.cuh"
 #include "dequant.cuh"
+#include "stage.cuh"
 
 namespace juno {
 
 // ───────────────────────────── device helpers ─────────────────────────────────────────────
 __device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
+
+// (a & b) | c in ONE logic instruction.  Written as lop3 with register operands: left to the compiler, a mask and
+// a magic constant that are both immediates become two instructions on the half-rate integer pipe.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// ((a & b) ^ c) in one instruction.
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
 __device__ __forceinline__ uint32_t bf2_sub(uint32_t v, uint32_t c) {
     __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&v);
@@ -56,18 +71,6 @@ __device__ __forceinline__ float f16bits_to_f32(uint32_t bits) {
 constexpr uint32_t kBf128 = 0x43004300u;  // (128, 128)
 constexpr uint32_t kBf160 = 0x43204320u;  // (160, 160)
 constexpr uint32_t kBf384 = 0x43C043C0u;  // (384, 384)
-
-// Splits v into three bf16 limbs with hi + mid + lo == v.
-__device__ __forceinline__ void split3(float v, unsigned short &hi, unsigned short &mid, unsigned short &lo) {
-    __nv_bfloat16 h = __float2bfloat16_rn(v);
-    float r1 = v - __bfloat162float(h);
-    __nv_bfloat16 m = __float2bfloat16_rn(r1);
-    float r2 = r1 - __bfloat162float(m);
-    __nv_bfloat16 l = __float2bfloat16_rn(r2);
-    hi = __bfloat16_as_ushort(h);
-    mid = __bfloat16_as_ushort(m);
-    lo = __bfloat16_as_ushort(l);
-}
 
 // SiLU as LlamaTransformerHandler.silu (:1733-1735): x / (1f + (float) Math.exp(-x)).
 __device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.f, (float)exp((double)(-x)))); }
@@ -159,12 +162,12 @@ struct XView {
 };
 
 // ── Q4_K tile ────────────────────────────────────────────────────────────────────────────
-__device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t &lo_a, uint32_t &lo_b, uint32_t &hi_a, uint32_t &hi_b) {
-    const uint32_t M = 0x000F000Fu;
-    lo_a = bf2_sub((w & M) | kBf128, kBf128);          // (byte0.lo, byte2.lo)
-    hi_a = bf2_sub(((w >> 4) & M) | kBf128, kBf128);   // (byte0.hi, byte2.hi)
-    lo_b = bf2_sub(((w >> 8) & M) | kBf128, kBf128);   // (byte1.lo, byte3.lo)
-    hi_b = bf2_sub(((w >> 12) & M) | kBf128, kBf128);  // (byte1.hi, byte3.hi)
+__device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t M, uint32_t K, uint32_t &lo_a, uint32_t &lo_b,
+                                          uint32_t &hi_a, uint32_t &hi_b) {
+    lo_a = bf2_sub(and_or(w, M, K), K);        // (byte0.lo, byte2.lo)
+    hi_a = bf2_sub(and_or(w >> 4, M, K), K);   // (byte0.hi, byte2.hi)
+    lo_b = bf2_sub(and_or(w >> 8, M, K), K);   // (byte1.lo, byte3.lo)
+    hi_b = bf2_sub(and_or(w >> 12, M, K), K);  // (byte1.hi, byte3.hi)
 }
 
 // Decodes one row's header words for the lane's two sub-blocks 2c, 2c+1.
@@ -185,13 +188,16 @@ __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, cons
     q4_header(R.dm0, R.sm0, s_r[0], s_r[1], mins_r, dmin_r);
     q4_header(R.dm1, R.sm1, s_q[0], s_q[1], mins_q, dmin_q);
     const int s16base = sb * 16;
+    // held in registers on purpose (see and_or)
+    uint32_t M4 = 0x000F000Fu, K128 = kBf128;
+    asm volatile("" : "+r"(M4), "+r"(K128));
 #pragma unroll
     for (int g = 0; g < 4; g++) {
         uint32_t la_x, lb_x, ha_x, hb_x, la_y, lb_y, ha_y, hb_y, la_z, lb_z, ha_z, hb_z, la_w, lb_w, ha_w, hb_w;
-        q4_unpack(R.q[g].x, la_x, lb_x, ha_x, hb_x);
-        q4_unpack(R.q[g].y, la_y, lb_y, ha_y, hb_y);
-        q4_unpack(R.q[g].z, la_z, lb_z, ha_z, hb_z);
-        q4_unpack(R.q[g].w, la_w, lb_w, ha_w, hb_w);
+        q4_unpack(R.q[g].x, M4, K128, la_x, lb_x, ha_x, hb_x);
+        q4_unpack(R.q[g].y, M4, K128, la_y, lb_y, ha_y, hb_y);
+        q4_unpack(R.q[g].z, M4, K128, la_z, lb_z, ha_z, hb_z);
+        q4_unpack(R.q[g].w, M4, K128, la_w, lb_w, ha_w, hb_w);
         const int src = (lane & ~3) | g;  // quad lane g owns sub-blocks 2g and 2g+1
         const float sr0 = __shfl_sync(0xffffffffu, s_r[0], src), sr1 = __shfl_sync(0xffffffffu, s_r[1], src);
         const float sq0 = __shfl_sync(0xffffffffu, s_q[0], src), sq1 = __shfl_sync(0xffffffffu, s_q[1], src);
@@ -243,21 +249,22 @@ __device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, cons
         s_q[k] = __fmul_rn(d_q, i8_to_f32(R.sc1, k));
     }
     const int s16base = sb * 16;
-    const uint32_t NIB = 0x0F0F0F0Fu, HI = 0x30303030u;
+    uint32_t NIB = 0x0F0F0F0Fu, HI = 0x30303030u;
+    asm volatile("" : "+r"(NIB), "+r"(HI));
 #pragma unroll
     for (int m = 0; m < 4; m++) {
         const uint32_t WA_r = R.ql[m].x, WB_r = R.ql[m].y, WA_q = R.ql[m].z, WB_q = R.ql[m].w;
         const uint4 hq = R.qh[m >> 1];
         const uint32_t H_r = (m & 1) ? hq.y : hq.x, H_q = (m & 1) ? hq.w : hq.z;
         uint32_t V_r[4], V_q[4];  // four 6-bit values per word, for sub-blocks 4m+0..3
-        V_r[0] = (WA_r & NIB) | (H_r & HI);
-        V_r[1] = ((WA_r >> 4) & NIB) | ((H_r >> 2) & HI);
-        V_r[2] = (WB_r & NIB) | ((H_r << 2) & HI);
-        V_r[3] = ((WB_r >> 4) & NIB) | ((H_r << 4) & HI);
-        V_q[0] = (WA_q & NIB) | (H_q & HI);
-        V_q[1] = ((WA_q >> 4) & NIB) | ((H_q >> 2) & HI);
-        V_q[2] = (WB_q & NIB) | ((H_q << 2) & HI);
-        V_q[3] = ((WB_q >> 4) & NIB) | ((H_q << 4) & HI);
+        V_r[0] = and_or(WA_r, NIB, H_r & HI);
+        V_r[1] = and_or(WA_r >> 4, NIB, (H_r >> 2) & HI);
+        V_r[2] = and_or(WB_r, NIB, (H_r << 2) & HI);
+        V_r[3] = and_or(WB_r >> 4, NIB, (H_r << 4) & HI);
+        V_q[0] = and_or(WA_q, NIB, H_q & HI);
+        V_q[1] = and_or(WA_q >> 4, NIB, (H_q >> 2) & HI);
+        V_q[2] = and_or(WB_q, NIB, (H_q << 2) & HI);
+        V_q[3] = and_or(WB_q >> 4, NIB, (H_q << 4) & HI);
         const int src = (lane & ~3) | m;  // quad lane m owns the scales of sub-blocks 4m..4m+3
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -281,12 +288,12 @@ __device__ __forceinline__ void compute_tile(const TileRegs<14> &R, int sb, cons
 }
 
 // ── Q8_0 tile: int8 q = 16*h + l, both nibble planes exact in bf16 ────────────────────────
-__device__ __forceinline__ void q8_unpack(uint32_t w, uint32_t &l_a, uint32_t &l_b, uint32_t &h_a, uint32_t &h_b) {
-    const uint32_t M = 0x000F000Fu, MH = 0x00780078u;
-    l_a = bf2_sub((w & M) | kBf128, kBf128);              // (b0&15, b2&15)
-    l_b = bf2_sub(((w >> 8) & M) | kBf128, kBf128);       // (b1&15, b3&15)
-    h_a = bf2_sub(((w >> 1) & MH) ^ kBf384, kBf384);      // 16*(b0>>4), 16*(b2>>4)  (arithmetic >>)
-    h_b = bf2_sub(((w >> 9) & MH) ^ kBf384, kBf384);      // 16*(b1>>4), 16*(b3>>4)
+__device__ __forceinline__ void q8_unpack(uint32_t w, uint32_t M, uint32_t K, uint32_t MH, uint32_t KH, uint32_t &l_a,
+                                          uint32_t &l_b, uint32_t &h_a, uint32_t &h_b) {
+    l_a = bf2_sub(and_or(w, M, K), K);          // (b0&15, b2&15)
+    l_b = bf2_sub(and_or(w >> 8, M, K), K);     // (b1&15, b3&15)
+    h_a = bf2_sub(and_xor(w >> 1, MH, KH), KH); // 16*(b0>>4), 16*(b2>>4)  (arithmetic >>)
+    h_b = bf2_sub(and_xor(w >> 9, MH, KH), KH); // 16*(b1>>4), 16*(b3>>4)
 }
 
 template <int NC>
@@ -295,14 +302,16 @@ __device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const
     constexpr int NT = (NC + 7) / 8;
     const int s16base = sb * 16;
     const uint32_t dr[4] = {R.d0.x, R.d0.y, R.d0.z, R.d0.w}, dq[4] = {R.d1.x, R.d1.y, R.d1.z, R.d1.w};
+    uint32_t M4 = 0x000F000Fu, K128 = kBf128, MH = 0x00780078u, KH = kBf384;
+    asm volatile("" : "+r"(M4), "+r"(K128), "+r"(MH), "+r"(KH));
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const float d_r = f16bits_to_f32(dr[j >> 1] >> ((j & 1) * 16)), d_q = f16bits_to_f32(dq[j >> 1] >> ((j & 1) * 16));
         uint32_t la_x, lb_x, ha_x, hb_x, la_y, lb_y, ha_y, hb_y, la_z, lb_z, ha_z, hb_z, la_w, lb_w, ha_w, hb_w;
-        q8_unpack(R.q[j].x, la_x, lb_x, ha_x, hb_x);
-        q8_unpack(R.q[j].y, la_y, lb_y, ha_y, hb_y);
-        q8_unpack(R.q[j].z, la_z, lb_z, ha_z, hb_z);
-        q8_unpack(R.q[j].w, la_w, lb_w, ha_w, hb_w);
+        q8_unpack(R.q[j].x, M4, K128, MH, KH, la_x, lb_x, ha_x, hb_x);
+        q8_unpack(R.q[j].y, M4, K128, MH, KH, la_y, lb_y, ha_y, hb_y);
+        q8_unpack(R.q[j].z, M4, K128, MH, KH, la_z, lb_z, ha_z, hb_z);
+        q8_unpack(R.q[j].w, M4, K128, MH, KH, la_w, lb_w, ha_w, hb_w);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             float ct[4];
@@ -321,7 +330,7 @@ __device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const
 }
 
 // ───────────────────────────── activation staging ─────────────────────────────────────────
-// One CTA per batch row writes that row's three limb columns (and 32-column sums) of the staged image.
+// One CTA per batch row writes that row's three limb columns of the staged image.
 struct StageParams {
     int mode;
     const float *x;
@@ -329,26 +338,19 @@ struct StageParams {
     const float *x_add, *normw;
     float *x_out;
     float eps;
-    int K, batch, bc;
-    size_t chunk_stride;  // bytes of a full chunk of bc rows
-    uint8_t *img;
+    StageImage im;
 };
 
-size_t stage_chunk_bytes(int K, int rows_in_chunk) {
-    const size_t nc = 3 * (size_t)rows_in_chunk;
-    const size_t xb = (size_t)K * nc * 2;
-    const size_t xs = ((((size_t)(K / 32) * nc) + 7) & ~(size_t)7) * 2;
-    return xb + xs;
-}
+size_t stage_chunk_bytes(int K, int rows_in_chunk) { return (size_t)K * 3 * rows_in_chunk * 2; }
 
 constexpr int kStageThreads = 256;
 
 __global__ void __launch_bounds__(kStageThreads) stage_kernel(const StageParams p) {
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int chunk = b / p.bc, nbc = min(p.bc, p.batch - chunk * p.bc), NC = 3 * nbc, col0 = 3 * (b - chunk * p.bc);
-    const int K = p.K;
-    unsigned short *xb = reinterpret_cast<unsigned short *>(p.img + (size_t)chunk * p.chunk_stride);
-    unsigned short *xs = xb + (size_t)K * NC;
+    const int K = p.im.K;
+    unsigned short *xb;
+    int NC, col0;
+    p.im.locate(b, xb, NC, col0);
     const float *xrow = p.x + (size_t)b * p.ldx;
     const float *arow = p.x_add ? p.x_add + (size_t)b * p.ldx : nullptr;
     float scale = 1.f;
@@ -400,23 +402,13 @@ __global__ void __launch_bounds__(kStageThreads) stage_kernel(const StageParams 
             w.y = (uint32_t)l[k][1] | ((uint32_t)l[k][3] << 16);
             *reinterpret_cast<uint2 *>(dst + k * 16) = w;
         }
-        // sums over 32 columns = 8 consecutive threads
-        float s = (v[0] + v[1]) + (v[2] + v[3]);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        unsigned short s3[3];
-        split3(s, s3[0], s3[1], s3[2]);
-        if ((lane & 7) == 0) {
-#pragma unroll
-            for (int k = 0; k < 3; k++) xs[xs_index(i4 >> 5, NC, col0 + k)] = s3[k];
-        }
     }
 }
 
 // ───────────────────────────── the GEMV kernel ────────────────────────────────────────────
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+constexpr int kMaxEpiItems = kWarps * 16 * 8;  // groups * 16 rows * batch chunk
 
 struct GemvParams {
     const uint8_t *w[3];
@@ -430,6 +422,18 @@ struct GemvParams {
     const uint8_t *ximg;
     unsigned img_bytes;
     unsigned *counters;  // {next task, CTAs done}
+    // RMSNorm scale of the input, applied to the outputs: 1/sqrt(sum(ss_parts[b][0..n_parts))/scale_n + eps)
+    const float *ss_parts;
+    int n_parts, ss_ld, scale_n;
+    float eps;
+    // EPI_RESID_NORM: x_out = resid + y; image of normw_next*x_out; per-task sums of squares
+    const float *resid;
+    float *x_out;
+    int ldx;
+    const float *normw_next;
+    float *ss_out;
+    int ss_out_ld;
+    StageImage img_next;  // also used by EPI_SILU_PAIR / EPI_STORE to emit the output as a staged activation
 };
 
 template <int TYPE>
@@ -446,10 +450,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = p.K;
-    unsigned short *xb = reinterpret_cast<unsigned short *>(smem);  // K*NC bf16, then (K/32)*NC sums (padded to 16 B)
-    unsigned short *xs = xb + (size_t)K * NC;
-    float *cs = reinterpret_cast<float *>(smem + p.img_bytes);      // [2][kWarps][16][LD]
-    int *next_task = reinterpret_cast<int *>(cs + 2 * kWarps * 16 * LD);
+    unsigned short *xb = reinterpret_cast<unsigned short *>(smem);  // K*NC bf16 limbs
+    unsigned short *xs = xb + (size_t)K * NC;                       // (K/32)*NC bf16: 32-column sums (Q4_K only)
+    const size_t xs_bytes = (TYPE == 12) ? ((((size_t)(K / 32) * NC * 2) + 15) & ~(size_t)15) : 0;
+    float *cs = reinterpret_cast<float *>(smem + p.img_bytes + xs_bytes);  // [2][kWarps][16][LD]
+    float *sqbuf = cs + 2 * kWarps * 16 * LD;                               // [groups*16*NB] (EPI_RESID_NORM)
+    float *scale_s = sqbuf + kWarps * 16 * NB;                              // [NB]
+    int *next_task = reinterpret_cast<int *>(scale_s + 8);
 
     // A CTA task is `groups` row tiles; the kin warps of a group split K.  Task ids beyond the first come
     // from a device counter, so CTAs that finish early take more.
@@ -472,7 +479,47 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         const int n16 = (int)(p.img_bytes >> 4);
         for (int i = tid; i < n16; i += kThreads) dst[i] = src[i];
     }
+    // RMSNorm scale of the input from the producer's per-task sums of squares (fixed summation order)
+    if (warp < NB) {
+        float sc = 1.f;
+        if (p.ss_parts) {
+            float s = 0.f;
+            for (int i = lane; i < p.n_parts; i += 32) s += p.ss_parts[(size_t)warp * p.ss_ld + i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            sc = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(s, (float)p.scale_n), p.eps)));
+        }
+        if (lane == 0) scale_s[warp] = sc;
+    }
     __syncthreads();
+    if (TYPE == 12) {
+        // sums of x over 32 columns, from the limbs (hi + mid + lo is x exactly): eight threads per sum
+        const int total = (K / 4) * NB;
+        for (int item = tid; item < total; item += kThreads) {
+            const int b = item / (K / 4), r = item - b * (K / 4), sub32 = r >> 3, q = r & 7;
+            const int s16 = sub32 * 2 + (q >> 2), c = q & 3;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 2; k >= 0; k--) {  // lo + mid first, then hi
+                const uint2 u = *reinterpret_cast<const uint2 *>(xb + ((size_t)(s16 * NC + 3 * b + k) * 4 + c) * 4);
+                x4[0] += __uint_as_float(u.x << 16);
+                x4[1] += __uint_as_float(u.x & 0xFFFF0000u);
+                x4[2] += __uint_as_float(u.y << 16);
+                x4[3] += __uint_as_float(u.y & 0xFFFF0000u);
+            }
+            float s = (x4[0] + x4[1]) + (x4[2] + x4[3]);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            unsigned short s3[3];
+            split3(s, s3[0], s3[1], s3[2]);
+            if (q == 0) {
+#pragma unroll
+                for (int k = 0; k < 3; k++) xs[xs_index(sub32, NC, 3 * b + k)] = s3[k];
+            }
+        }
+        __syncthreads();
+    }
 
     XView<NC> xv;
     {
@@ -537,30 +584,55 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         {
             const float *csb = cs + (it & 1) * kWarps * 16 * LD;
             const int rows_out = (p.epi == EPI_SILU_PAIR) ? 8 : 16;
-            const int total = p.groups * rows_out * NB;
+            const int per_b = p.groups * rows_out, total = per_b * NB;
             for (int idx = tid; idx < total; idx += kThreads) {
-                const int row = idx % rows_out, rest = idx / rows_out, b = rest % NB, g = rest / NB;
+                const int b = idx / per_b, rg = idx - b * per_b, g = rg / rows_out, row = rg - g * rows_out;
                 const int Rg = ct * p.groups + g;
-                if (Rg >= p.total_rt) continue;
-                int s = 0;
-                if (p.nseg > 1 && Rg >= p.rt_begin[1]) s = 1;
-                if (p.nseg > 2 && Rg >= p.rt_begin[2]) s = 2;
-                const int tile_in_seg = Rg - p.rt_begin[s];
-                float v = 0.f, v2 = 0.f;
-                for (int k2 = 0; k2 < p.kin; k2++) {
-                    const float *cr = csb + ((g * p.kin + k2) * 16 + row) * LD + 3 * b;
-                    v += (cr[2] + cr[1]) + cr[0];
-                    if (p.epi == EPI_SILU_PAIR) {
-                        const float *cu = cr + 8 * LD;
-                        v2 += (cu[2] + cu[1]) + cu[0];
+                float sq = 0.f;
+                if (Rg < p.total_rt) {
+                    int s = 0;
+                    if (p.nseg > 1 && Rg >= p.rt_begin[1]) s = 1;
+                    if (p.nseg > 2 && Rg >= p.rt_begin[2]) s = 2;
+                    const int tile_in_seg = Rg - p.rt_begin[s];
+                    float v = 0.f, v2 = 0.f;
+                    for (int k2 = 0; k2 < p.kin; k2++) {
+                        const float *cr = csb + ((g * p.kin + k2) * 16 + row) * LD + 3 * b;
+                        v += (cr[2] + cr[1]) + cr[0];
+                        if (p.epi == EPI_SILU_PAIR) {
+                            const float *cu = cr + 8 * LD;
+                            v2 += (cu[2] + cu[1]) + cu[0];
+                        }
+                    }
+                    const float sc = scale_s[b];
+                    v = __fmul_rn(v, sc);
+                    const int orow = tile_in_seg * rows_out + row;
+                    if (orow < p.rows[s]) {
+                        float o = v;
+                        if (p.epi == EPI_SILU_PAIR) {
+                            o = __fmul_rn(silu_ref(v), __fmul_rn(v2, sc));
+                        } else if (p.epi == EPI_RESID_NORM) {
+                            o = __fadd_rn(p.resid[(size_t)b * p.ldx + orow], v);
+                            p.x_out[(size_t)b * p.ldx + orow] = o;
+                            sq = __fmul_rn(o, o);
+                            o = __fmul_rn(p.normw_next[orow], o);
+                        }
+                        if (p.epi != EPI_RESID_NORM && p.out[s]) p.out[s][(size_t)b * p.ld_out + orow] = o;
+                        if (p.img_next.img) {
+                            unsigned short *nxb;
+                            int nNC, ncol0;
+                            p.img_next.locate(b, nxb, nNC, ncol0);
+                            stage_store1(nxb, nNC, ncol0, orow, o);
+                        }
                     }
                 }
-                if (p.epi == EPI_SILU_PAIR) {
-                    const int orow = tile_in_seg * 8 + row;
-                    if (orow < p.rows[s]) p.out[s][(size_t)b * p.ld_out + orow] = __fmul_rn(silu_ref(v), v2);
-                } else {
-                    const int orow = tile_in_seg * 16 + row;
-                    if (orow < p.rows[s]) p.out[s][(size_t)b * p.ld_out + orow] = v;
+                if (p.epi == EPI_RESID_NORM) sqbuf[idx] = sq;
+            }
+            if (p.epi == EPI_RESID_NORM) {  // per-task sum of squares, rows in order
+                __syncthreads();
+                if (tid < NB) {
+                    float s = 0.f;
+                    for (int i = 0; i < per_b; i++) s += sqbuf[tid * per_b + i];
+                    p.ss_out[(size_t)tid * p.ss_out_ld + ct] = s;
                 }
             }
         }
@@ -587,7 +659,9 @@ static int env_int(const char *name, int dflt) {
 
 static size_t gemv_smem_bytes(int K, int nb_batch) {
     const int NT = (3 * nb_batch + 7) / 8;
-    return stage_chunk_bytes(K, nb_batch) + (size_t)2 * kWarps * 16 * 8 * NT * 4 + 16;
+    const size_t xs = ((((size_t)(K / 32) * 3 * nb_batch * 2) + 15) & ~(size_t)15);
+    return stage_chunk_bytes(K, nb_batch) + xs + (size_t)2 * kWarps * 16 * 8 * NT * 4 + (size_t)kWarps * 16 * nb_batch * 4 +
+           32 + 16;
 }
 
 int gemv_batch_chunk(const juno_ctx *ctx, int K, int batch) {
@@ -602,6 +676,17 @@ size_t stage_image_bytes(const juno_ctx *ctx, int K, int batch) {
     return (size_t)chunks * stage_chunk_bytes(K, bc);
 }
 
+StageImage stage_image_desc(const juno_ctx *ctx, uint8_t *img, int K, int batch) {
+    StageImage im;
+    im.img = img;
+    im.K = K;
+    im.batch = batch;
+    im.bc = gemv_batch_chunk(ctx, K, batch);
+    im.b0 = 0;
+    im.chunk_stride = stage_chunk_bytes(K, im.bc);
+    return im;
+}
+
 int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t st) {
     JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0 && a.batch >= 1 && a.x && a.img, "stage: bad arguments (K=%d)", a.K);
     JUNO_REQUIRE(a.ldx % 4 == 0, "stage: row stride %d must be a multiple of 4", a.ldx);
@@ -613,11 +698,7 @@ int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t st) {
     p.normw = a.normw;
     p.x_out = a.x_out;
     p.eps = a.eps;
-    p.K = a.K;
-    p.batch = a.batch;
-    p.bc = gemv_batch_chunk(ctx, a.K, a.batch);
-    p.chunk_stride = stage_chunk_bytes(a.K, p.bc);
-    p.img = a.img;
+    p.im = stage_image_desc(ctx, a.img, a.K, a.batch);
     ProfScope prof(ctx, st, PROF_OTHER, 0);
     stage_kernel<<<a.batch, kStageThreads, 0, st>>>(p);
     JUNO_CUDA_TRY(cudaGetLastError());
@@ -661,6 +742,34 @@ static int launch_type(juno_ctx *ctx, const GemvParams &p, int NB, int grid, siz
     return JUNO_ERR_UNSUPPORTED;
 }
 
+// CTA-task geometry of a product; producers and consumers of per-task sums of squares must agree on it.
+void gemv_task_geometry(const juno_ctx *ctx, int K, int batch_chunk, int total_rt, int *kin_out, int *n_ctasks_out) {
+    const int nb = K / 256;
+    const size_t smem = gemv_smem_bytes(K, batch_chunk);
+    const int ctas_per_sm = (smem * 2 + 2048 <= ctx->smem_optin) ? 2 : 1;
+    const int max_grid = ctx->sm_count * ctas_per_sm;
+    // warps per row tile (K split inside the CTA): the smallest split that still yields several CTA tasks per
+    // resident CTA (for balance), else the largest one (for parallelism); at least two tiles per warp per task
+    int kin = 1;
+    for (int d = 1; d <= kWarps; d *= 2) {
+        if (nb % d || (d > 1 && nb / d < 2)) break;
+        kin = d;
+        const int groups = kWarps / d;
+        if ((total_rt + groups - 1) / groups >= 4 * max_grid) break;
+    }
+    kin = env_int("JUNO_GEMV_KIN", kin);
+    if (kin < 1 || kin > kWarps || (kin & (kin - 1)) || nb % kin) kin = 1;
+    const int groups = kWarps / kin;
+    *kin_out = kin;
+    *n_ctasks_out = (total_rt + groups - 1) / groups;
+}
+
+int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_rt) {
+    int kin, n;
+    gemv_task_geometry(ctx, K, gemv_batch_chunk(ctx, K, batch), total_rt, &kin, &n);
+    return n;
+}
+
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
     JUNO_REQUIRE(a.nseg >= 1 && a.nseg <= 3, "gemv: nseg %d", a.nseg);
     JUNO_REQUIRE(a.type == 12 || a.type == 14 || a.type == 8, "gemv: type %d has no tiled kernel", a.type);
@@ -670,6 +779,8 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
     int total_rt = 0;
     for (int s = 0; s < a.nseg; s++) total_rt += a.seg[s].row_tiles;
     JUNO_REQUIRE(gemv_smem_bytes(a.K, 1) <= ctx->smem_optin, "gemv: K=%d does not fit shared memory", a.K);
+    if (a.epi == EPI_RESID_NORM)
+        JUNO_REQUIRE(a.nseg == 1 && a.resid && a.x_out && a.normw_next && a.ss_out && a.img_next, "gemv: residual epilogue needs its buffers");
 
     double algo_bytes = (double)a.batch * a.K * 4;
     {
@@ -680,28 +791,19 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
 
     const int bc_full = gemv_batch_chunk(ctx, a.K, a.batch);
     const size_t chunk_stride = stage_chunk_bytes(a.K, bc_full);
+    int kin = 1, n_ctasks = 1;
+    gemv_task_geometry(ctx, a.K, bc_full, total_rt, &kin, &n_ctasks);
     for (int b0 = 0, chunk = 0; b0 < a.batch; b0 += bc_full, chunk++) {
         const int bc = std::min(bc_full, a.batch - b0);
         const size_t smem = gemv_smem_bytes(a.K, bc);
-        const int ctas_per_sm = (smem * 2 + 2048 <= ctx->smem_optin) ? 2 : 1;
+        const int ctas_per_sm = (gemv_smem_bytes(a.K, bc_full) * 2 + 2048 <= ctx->smem_optin) ? 2 : 1;
         const int max_grid = ctx->sm_count * ctas_per_sm;
-        // warps per row tile (K split inside the CTA): the smallest split that still yields several CTA tasks per
-        // resident CTA (for balance), else the largest one (for parallelism); at least two tiles per warp per task
-        int kin = 1;
-        for (int d = 1; d <= kWarps; d *= 2) {
-            if (nb % d || (d > 1 && nb / d < 2)) break;
-            kin = d;
-            const int groups = kWarps / d;
-            if ((total_rt + groups - 1) / groups >= 4 * max_grid) break;
-        }
-        kin = env_int("JUNO_GEMV_KIN", kin);
-        if (kin < 1 || kin > kWarps || (kin & (kin - 1)) || nb % kin) kin = 1;
         GemvParams p;
         memset(&p, 0, sizeof(p));
         int rt = 0;
         for (int s = 0; s < a.nseg; s++) {
             p.w[s] = a.seg[s].w;
-            p.out[s] = a.seg[s].out + (size_t)b0 * a.ld_out;
+            p.out[s] = a.seg[s].out ? a.seg[s].out + (size_t)b0 * a.ld_out : nullptr;
             p.rows[s] = a.seg[s].rows;
             p.rt_begin[s] = rt;
             rt += a.seg[s].row_tiles;
@@ -714,12 +816,28 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
         p.kin = kin;
         p.tpt = nb / kin;
         p.groups = kWarps / kin;
-        p.n_ctasks = (total_rt + p.groups - 1) / p.groups;
+        p.n_ctasks = n_ctasks;
         p.ld_out = a.ld_out;
         p.epi = a.epi;
         p.ximg = a.ximg + (size_t)chunk * chunk_stride;
         p.img_bytes = (unsigned)stage_chunk_bytes(a.K, bc);
         p.counters = ctx->gemv_scratch.counters + 2 * (ctx->gemv_scratch.next_slot++ % kGemvCounterSlots);
+        p.ss_parts = a.ss_parts ? a.ss_parts + (size_t)b0 * a.ss_ld : nullptr;
+        p.n_parts = a.n_parts;
+        p.ss_ld = a.ss_ld;
+        p.scale_n = a.scale_n;
+        p.eps = a.eps;
+        p.resid = a.resid ? a.resid + (size_t)b0 * a.ldx : nullptr;
+        p.x_out = a.x_out ? a.x_out + (size_t)b0 * a.ldx : nullptr;
+        p.ldx = a.ldx;
+        p.normw_next = a.normw_next;
+        p.ss_out = a.ss_out ? a.ss_out + (size_t)b0 * a.ss_out_ld : nullptr;
+        p.ss_out_ld = a.ss_out_ld;
+        if (a.img_next) {
+            // the next product chunks the batch by ITS K; rows b0.. of this launch map to rows b0.. of that image
+            p.img_next = stage_image_desc(ctx, a.img_next, a.img_next_K, a.batch);
+            p.img_next.b0 = b0;
+        }
         int grid = std::min(max_grid, p.n_ctasks);
         grid = std::max(1, std::min(env_int("JUNO_GEMV_GRID", grid), p.n_ctasks));
         int rc;

@@ -41,8 +41,9 @@ size_t stage_image_bytes(const juno_ctx *ctx, int K, int batch);
 int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t stream);
 
 enum GemvEpilogue {
-    EPI_STORE = 0,      // out[b][row] = y
-    EPI_SILU_PAIR = 1,  // tile rows 0-7 are gate rows, 8-15 the matching up rows: out[b][8*tile+row] = silu(gate)*up
+    EPI_STORE = 0,       // out[b][row] = y
+    EPI_SILU_PAIR = 1,   // tile rows 0-7 are gate rows, 8-15 the matching up rows: out[b][8*tile+row] = silu(gate)*up
+    EPI_RESID_NORM = 2,  // x_out = resid + y; next image = normw_next * x_out; per-task sums of x_out^2 to ss_out
 };
 
 struct GemvSeg {
@@ -61,7 +62,24 @@ struct GemvArgs {
     int ld_out = 0;   // stride between batch rows of every seg.out
     int epi = EPI_STORE;
     const uint8_t *ximg = nullptr;  // staged activation (launch_stage) for this K and batch
+    // RMSNorm of the input folded into the output: when the image holds normw*x (not yet scaled), the outputs are
+    // multiplied by 1/sqrt(sum(ss_parts[b][0..n_parts))/scale_n + eps)
+    const float *ss_parts = nullptr;
+    int n_parts = 0, ss_ld = 0, scale_n = 0;
+    float eps = 0.f;
+    // EPI_RESID_NORM
+    const float *resid = nullptr;
+    float *x_out = nullptr;
+    int ldx = 0;
+    const float *normw_next = nullptr;
+    float *ss_out = nullptr;
+    int ss_out_ld = 0;
+    // any epilogue: also emit the output as the staged activation of the next product (K = img_next_K)
+    uint8_t *img_next = nullptr;
+    int img_next_K = 0;
 };
+// Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
+int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
 
 // Enqueues the product on `stream`.  All pointers are device pointers.
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);

@@ -100,6 +100,7 @@ struct LogitsView {
     }
 };
 
+constexpr int kSsLd = 1024;  // capacity of one row of per-task sums of squares
 constexpr int kArgmaxBlocks = 32;
 // First maximum (lowest index among equal values), as SampleStep.greedy (sampler/.../SampleStep.java:51-58)
 // picks after a monotone softmax.
@@ -208,7 +209,7 @@ struct juno_model {
     juno_kvpool *pool = nullptr;
     juno::NcclComm comm = nullptr;
     // activations
-    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *hdn = nullptr;
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *ss = nullptr;
     uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
@@ -291,7 +292,7 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->hdn, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
                     m->attn_scratch, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
@@ -487,7 +488,7 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->qkv, (size_t)B * m->qkv_ld * 4));
     JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
-    JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->ss, (size_t)2 * B * kSsLd * 4));
     JUNO_TRY(dev_alloc((void **)&m->img_h, stage_image_bytes(c, H, B)));
     JUNO_TRY(dev_alloc((void **)&m->img_att, stage_image_bytes(c, m->heads_loc * hd, B)));
     JUNO_TRY(dev_alloc((void **)&m->img_i, stage_image_bytes(c, m->inter_loc, B)));
@@ -512,27 +513,23 @@ extern "C" int juno_model_finalize(juno_model *m) {
 namespace juno {
 
 // ───────────────────────────── one decode step, enqueued on the context stream ────────────
-static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, int ld_out, int batch,
-                      const uint8_t *ximg, int epi, cudaStream_t st) {
+static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, const GemvArgs &proto,
+                      cudaStream_t st) {
     // consecutive matrices of one block format share a launch (they share the staged activation)
     int i = 0;
     while (i < count) {
         int j = i + 1;
         while (j < count && j - i < 3 && mats[j]->type == mats[i]->type) j++;
-        GemvArgs a;
+        GemvArgs a = proto;
         a.nseg = j - i;
         for (int s = 0; s < a.nseg; s++) {
             a.seg[s].w = mats[i + s]->dev;
             a.seg[s].out = outs[i + s];
-            a.seg[s].rows = epi == EPI_SILU_PAIR ? (int)mats[i + s]->rows / 2 : (int)mats[i + s]->rows;
+            a.seg[s].rows = a.epi == EPI_SILU_PAIR ? (int)mats[i + s]->rows / 2 : (int)mats[i + s]->rows;
             a.seg[s].row_tiles = (int)mats[i + s]->row_tiles;
         }
         a.type = mats[i]->type;
         a.K = (int)mats[i]->cols;
-        a.batch = batch;
-        a.ld_out = ld_out;
-        a.epi = epi;
-        a.ximg = ximg;
         JUNO_TRY(launch_gemv(m->ctx, a, st));
         i = j;
     }
@@ -554,15 +551,50 @@ static int stage_rms(juno_model *m, int n, const float *x, const float *add, flo
     a.img = m->img_h;
     return launch_stage(m->ctx, a, st);
 }
-static int stage_plain(juno_model *m, int n, const float *x, int K, uint8_t *img, cudaStream_t st) {
-    StageArgs a;
-    a.mode = STAGE_PLAIN;
-    a.x = x;
-    a.ldx = K;
-    a.K = K;
+
+// A row-parallel projection (Wo or Wdown) followed by "residual add, RMSNorm with the next norm weights, stage".
+// Single GPU: all fused into the GEMV epilogue (the 1/rms factor is applied by the consumer from per-task sums of
+// squares).  Tensor parallel: the partial products are all-reduced first, then one staging kernel does the rest.
+static int proj_resid_norm(juno_model *m, int n, juno_qmat *w, const uint8_t *ximg, int &cur, const float *normw_next,
+                           float *ss_out, bool *consumer_scales, cudaStream_t st) {
+    const int H = m->cfg.hidden;
+    GemvArgs a;
     a.batch = n;
-    a.img = img;
-    return launch_stage(m->ctx, a, st);
+    a.ximg = ximg;
+    juno_qmat *mats[1] = {w};
+    if (m->world == 1) {
+        a.epi = EPI_RESID_NORM;
+        a.resid = m->x[cur];
+        a.x_out = m->x[cur ^ 1];
+        a.ldx = H;
+        a.normw_next = normw_next;
+        a.ss_out = ss_out;
+        a.ss_out_ld = kSsLd;
+        a.img_next = m->img_h;
+        a.img_next_K = H;
+        float *outs[1] = {nullptr};
+        JUNO_TRY(gemv_group(m, mats, outs, 1, a, st));
+        *consumer_scales = true;
+    } else {
+        a.epi = EPI_STORE;
+        a.ld_out = H;
+        float *outs[1] = {m->proj};
+        JUNO_TRY(gemv_group(m, mats, outs, 1, a, st));
+        JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        JUNO_TRY(stage_rms(m, n, m->x[cur], m->proj, m->x[cur ^ 1], normw_next, st));
+        *consumer_scales = false;
+    }
+    cur ^= 1;
+    return JUNO_OK;
+}
+
+static void set_input_scale(juno_model *m, GemvArgs &a, bool scaled_by_consumer, const float *ss, int n_parts) {
+    if (!scaled_by_consumer) return;
+    a.ss_parts = ss;
+    a.n_parts = n_parts;
+    a.ss_ld = kSsLd;
+    a.scale_n = m->cfg.hidden;
+    a.eps = m->cfg.rms_eps;
 }
 
 static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
@@ -571,6 +603,9 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
     const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
     const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
+    float *ss_o = m->ss, *ss_d = m->ss + (size_t)B * kSsLd;  // sums of squares written by Wo / Wdown epilogues
+    const int parts_o = gemv_n_ctasks(c, Hl, n, H / 16), parts_d = gemv_n_ctasks(c, Il, n, H / 16);
+    JUNO_REQUIRE(parts_o <= kSsLd && parts_d <= kSsLd, "hidden size %d needs more than %d partial sums", H, kSsLd);
 
     // embedding lookup -> x[0]
     {
@@ -582,19 +617,23 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         c->kernel_launches++;
     }
     JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
+    JUNO_TRY(stage_rms(m, n, m->x[0], nullptr, nullptr, m->layers[0].attn_norm, st));
 
-    int cur = 0;                    // x[cur] holds the residual stream entering the layer
-    const float *pending = nullptr; // projection still to be added to it (done by the next RMSNorm staging)
+    int cur = 0;          // x[cur] holds the residual stream
+    bool scaled = false;  // img_h holds normw*x and the consumer still has to apply 1/rms
     for (int l = 0; l < f.n_layers; l++) {
         JunoLayer &L = m->layers[l];
-        // xn = rmsNorm(x (+ pending)); q,k,v = W·xn
-        JUNO_TRY(stage_rms(m, n, m->x[cur], pending, pending ? m->x[cur ^ 1] : nullptr, L.attn_norm, st));
-        if (pending) cur ^= 1;
-        juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
-        float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
-        JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, m->qkv_ld, n, m->img_h, EPI_STORE, st));
-        JUNO_TRY(launch_rope_append(c, m->pool, l, n, m->heads_loc, m->qkv, m->qkv_ld, m->qkv + Hl, m->qkv + Hl + KVl,
-                                    m->qkv_ld, d_slot, d_pos, m->rope_cs, st));
+        // q,k,v = W·rmsNorm(x)
+        {
+            GemvArgs a;
+            a.batch = n;
+            a.ximg = m->img_h;
+            a.ld_out = m->qkv_ld;
+            set_input_scale(m, a, scaled, ss_d, parts_d);
+            juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
+            float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
+            JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, a, st));
+        }
         AttnArgs at;
         at.pool = m->pool;
         at.layer = l;
@@ -609,33 +648,46 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         at.part_o = m->attn_scratch;
         at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
         at.algo_bytes = m->step_kv_bytes;
+        at.rope_cs = m->rope_cs;  // q, k are rotated and k, v appended inside the attention kernel
+        at.knew = m->qkv + Hl;
+        at.vnew = m->qkv + Hl + KVl;
+        at.ldkv = m->qkv_ld;
+        at.stage_img = m->img_att;  // the merge kernel writes Wo's staged input directly
+        at.stage_bc = gemv_batch_chunk(c, Hl, n);
+        at.stage_chunk_stride = stage_chunk_bytes(Hl, at.stage_bc);
         JUNO_TRY(launch_attn(c, at, st));
-        // proj = Wo·att  (row-parallel under TP: partial sums, all-reduced)
-        JUNO_TRY(stage_plain(m, n, m->att, Hl, m->img_att, st));
-        juno_qmat *o_m[1] = {L.w[JUNO_T_ATTN_OUT]};
-        float *o_o[1] = {m->proj};
-        JUNO_TRY(gemv_group(m, o_m, o_o, 1, H, n, m->img_att, EPI_STORE, st));
-        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
-        // x2 = x + proj ; xn2 = rmsNorm(x2) ; hdn = silu(Wgate·xn2) * (Wup·xn2)
-        JUNO_TRY(stage_rms(m, n, m->x[cur], m->proj, m->x[cur ^ 1], L.ffn_norm, st));
-        cur ^= 1;
-        juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
-        float *gu_o[1] = {m->hdn};
-        JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, Il, n, m->img_h, EPI_SILU_PAIR, st));
-        // proj = Wdown·hdn
-        JUNO_TRY(stage_plain(m, n, m->hdn, Il, m->img_i, st));
-        juno_qmat *d_m[1] = {L.w[JUNO_T_FFN_DOWN]};
-        float *d_o[1] = {m->proj};
-        JUNO_TRY(gemv_group(m, d_m, d_o, 1, H, n, m->img_i, EPI_STORE, st));
-        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
-        pending = m->proj;
+        // x2 = x + Wo·att ; staged rmsNorm(x2, ffn_norm)
+        JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled, st));
+        // hdn = silu(Wgate·xn2) * (Wup·xn2), emitted as Wdown's staged input
+        {
+            GemvArgs a;
+            a.batch = n;
+            a.ximg = m->img_h;
+            a.epi = EPI_SILU_PAIR;
+            a.ld_out = Il;
+            a.img_next = m->img_i;
+            a.img_next_K = Il;
+            set_input_scale(m, a, scaled, ss_o, parts_o);
+            juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
+            float *gu_o[1] = {nullptr};
+            JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, a, st));
+        }
+        // x = x2 + Wdown·hdn ; staged rmsNorm(x, next norm)
+        const float *next_norm = (l + 1 < f.n_layers) ? m->layers[l + 1].attn_norm : m->output_norm;
+        JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, st));
     }
-    // logits = Wout · rmsNorm(x + pending, output_norm)
-    JUNO_TRY(stage_rms(m, n, m->x[cur], pending, m->x[cur ^ 1], m->output_norm, st));
-    juno_qmat *l_m[1] = {m->output};
-    float *l_o[1] = {m->logits_loc};
-    JUNO_TRY(gemv_group(m, l_m, l_o, 1, m->vocab_loc, n, m->img_h, EPI_STORE, st));
-    m->last_x = cur ^ 1;
+    // logits = Wout · rmsNorm(x, output_norm)
+    {
+        GemvArgs a;
+        a.batch = n;
+        a.ximg = m->img_h;
+        a.ld_out = m->vocab_loc;
+        set_input_scale(m, a, scaled, ss_d, parts_d);
+        juno_qmat *l_m[1] = {m->output};
+        float *l_o[1] = {m->logits_loc};
+        JUNO_TRY(gemv_group(m, l_m, l_o, 1, a, st));
+    }
+    m->last_x = cur;
     LogitsView lv;
     lv.n = n;
     lv.vocab = f.vocab;
