@@ -1,0 +1,63 @@
+"""Tensor parallelism on real GPUs (needs at least two): two ranks, NCCL, logits against the unsharded oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from juno_b200 import synth
+
+pytestmark = pytest.mark.gpu
+ARCH = synth.Arch(hidden=512, n_layers=2, n_heads=4, n_kv_heads=2, inter=1024, vocab=1024, rope_theta=500000.0)
+
+
+def _gpu_count():
+    from juno_b200.matvec import GpuContext
+    return GpuContext.device_count()
+
+
+def _worker(rank, world, nccl_id, q):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from juno_b200.handler import B200TransformerHandler
+    from juno_b200.matvec import GpuContext
+    ctx = GpuContext(rank)
+    h = B200TransformerHandler(ARCH, ctx, max_batch=2, max_seqs=2, max_ctx=32, kv_dtype="f32", tp_rank=rank,
+                               tp_world=world, nccl_id=nccl_id)
+    h.load(synth.random_model(ARCH, 21))
+    outs = []
+    toks = [[5, 900], [17, 3], [512, 77], [1, 2]]
+    for p, t in enumerate(toks):
+        logits, ids = h.forward_batch(["a", "b"], [[t[0]], [t[1]]], [p, p], want_logits=True, want_argmax=True)
+        outs.append((logits.copy(), ids.copy()))
+    greedy = h.decode_greedy(["a", "b"], [7, 8], [len(toks), len(toks)], 6)
+    h.release_gpu_resources()
+    q.put((rank, outs, greedy))
+
+
+def test_two_gpu_tensor_parallel_matches_oracle(oracle):
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from juno_b200.handler import B200TransformerHandler
+    from modelutil import build_pair
+    nccl_id = B200TransformerHandler.nccl_unique_id()
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=_worker, args=(r, 2, nccl_id, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=300) for _ in range(2)], key=lambda r: r[0])
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    om, _ = build_pair(oracle, ARCH, 21, kv_dtype="f32", max_ctx=32, engine=False)
+    sa, sb = om.new_seq(), om.new_seq()
+    toks = [[5, 900], [17, 3], [512, 77], [1, 2]]
+    for p, t in enumerate(toks):
+        ra, rb = om.forward(sa, t[0], p), om.forward(sb, t[1], p)
+        for rank in range(2):
+            logits, ids = res[rank][1][p]
+            assert np.abs(logits[0] - ra).max() <= 1e-3 * np.abs(ra).max()
+            assert np.abs(logits[1] - rb).max() <= 1e-3 * np.abs(rb).max()
+            assert ids[0] == oracle.greedy(ra) and ids[1] == oracle.greedy(rb)
+    assert np.array_equal(res[0][2], res[1][2])  # both ranks pick the same tokens
