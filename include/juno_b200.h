@@ -121,6 +121,23 @@ int juno_seq_append_kv(juno_seq *s, int32_t layer, int32_t pos, int32_t n_tokens
 int juno_attn_decode(juno_ctx *ctx, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs,
                      int32_t n_heads, const float *q_host, float *out_host);
 
+/* The same attention for callers that must not allocate.  juno_attn_decode grows device staging buffers with
+ * cudaMalloc when a call is larger than any before it; a host that has handed all of the GPU's memory to its KV pool
+ * and weights (or that runs under a fixed reservation where a late cudaMalloc fails, or stalls the device with its
+ * implicit synchronisation) cannot afford that.  This variant takes q and out as DEVICE pointers
+ * ([n][n_heads*head_dim] FP32 each, caller-owned) and keeps its only working memory - per-split partial results and
+ * 2n words of sequence metadata - in an 8 MiB array that is part of the library image (each GPU that loads the
+ * library holds it until the process exits).  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ * Limits: n <= 256 and n * n_heads * (head_dim + 2) * 4 bytes must fit the array at least once (about 8 MiB minus
+ * 2 KiB); larger calls fail with JUNO_ERR_INVALID_ARG and a message that names both numbers.  Fewer context splits
+ * are used when the array is the constraint.  The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls share the array: it keeps
+ * the previous call's contents (every entry a call reads is rewritten by that call first), and two calls that
+ * overlap on the GPU race - this function serialises on the context and returns after the stream has drained.
+ * No counterpart in the reference. */
+int juno_attn_decode_static(juno_ctx *ctx, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs,
+                            int32_t n_heads, const float *q_dev, float *out_dev);
+
 /* ── forward-pass operator (boundaries B and C) ───────────────────────────────
  * juno_model_* replaces the device half of LlamaTransformerHandler
  * (ForwardPassHandler.java:33-70); juno_forward with n sequences is

@@ -67,6 +67,7 @@ SIGNATURES = {
     "juno_seq_length": (C.c_int, [P, C.POINTER(I32)]),
     "juno_seq_append_kv": (C.c_int, [P, I32, I32, I32, P, P]),
     "juno_attn_decode": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),
+    "juno_attn_decode_static": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),
     "juno_nccl_unique_id": (C.c_int, [P]),
     "juno_model_create": (C.c_int, [P, C.POINTER(ModelCfg), PP]),
     "juno_model_set_tensor": (C.c_int, [P, I32, I32, P, I32, I64, I64]),

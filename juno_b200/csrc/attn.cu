@@ -84,11 +84,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
     const int h0 = kvh * G;
     float *po = p.part_o + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * HD;   // head stride n_splits*HD
     float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
-    if (t0 >= t1) {  // empty split
+    if (t0 >= t1) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
         if (tid < G) {
             pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
             pml[(size_t)tid * p.n_splits * 2 + 1] = 0.f;
         }
+        for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) po[(size_t)(idx / HD) * p.n_splits * HD + (idx % HD)] = 0.f;
         return;
     }
     const int sub = lane % LPT, slot = warp * TPW + lane / LPT;
@@ -725,6 +726,92 @@ int juno_attn_decode(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));  // meta (pageable host memory) is consumed by now
     c->h2d_bytes += (int64_t)(qbytes + meta_bytes);
     c->d2h_bytes += (int64_t)qbytes;
+    return JUNO_OK;
+}
+
+
+// ── attention without any allocation ─────────────────────────────────────────────────────────
+// Scratch for juno_attn_decode_static: the per-split partial outputs, the (max, sum) pairs and the per-sequence
+// page-table row / length words.  It lives in the library image, so every GPU that loads the library holds these
+// 8 MiB until the process exits.
+constexpr size_t kStaticAttnScratchBytes = 8u << 20;
+constexpr int kStaticAttnMaxSeqs = 256;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
+static std::mutex g_static_attn_mu;
+static void *g_static_attn_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+
+int juno_attn_decode_static(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs, int32_t n_heads,
+                            const float *q_dev, float *out_dev) {
+    JUNO_TRY(ctx_check(c));
+    JUNO_REQUIRE(p && seqs && q_dev && out_dev, "null argument");
+    if (p->magic != kMagicPool) {
+        set_error("KV pool is closed");
+        return JUNO_ERR_CLOSED;
+    }
+    JUNO_REQUIRE(p->ctx == c, "pool belongs to another context");
+    JUNO_REQUIRE(n >= 1 && n <= kStaticAttnMaxSeqs, "n=%d outside [1,%d] (limit of the allocation-free entry point)", n,
+                 kStaticAttnMaxSeqs);
+    JUNO_REQUIRE(layer >= 0 && layer < p->n_layers, "layer %d out of range", layer);
+    JUNO_REQUIRE(n_heads > 0 && n_heads % p->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", n_heads,
+                 p->n_kv_heads);
+    JUNO_REQUIRE(c->device >= 0 && c->device < 64, "device ordinal %d not supported here", c->device);
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    // One-time set-up per device, with that device current: in host code the array's name is only a handle, the
+    // address a kernel can use comes from cudaGetSymbolAddress.
+    void *base = nullptr;
+    {
+        std::lock_guard<std::mutex> lk2(g_static_attn_mu);
+        if (!g_static_attn_ptr[c->device]) {
+            void *ptr = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
+            if (e != cudaSuccess || !ptr) {
+                set_error("cudaGetSymbolAddress(static attention scratch) failed: rc=%d (%s)", (int)e, cudaGetErrorString(e));
+                return JUNO_ERR_CUDA;
+            }
+            g_static_attn_ptr[c->device] = ptr;
+        }
+        base = g_static_attn_ptr[c->device];
+    }
+    int32_t meta[2 * kStaticAttnMaxSeqs];
+    int max_len = 0;
+    for (int i = 0; i < n; i++) {
+        JUNO_TRY(seq_check(seqs[i]));
+        JUNO_REQUIRE(seqs[i]->pool == p, "sequence %d belongs to another pool", i);
+        JUNO_REQUIRE(seqs[i]->len > 0, "sequence %d is empty", i);
+        meta[i] = seqs[i]->slot;
+        meta[n + i] = seqs[i]->len;
+        max_len = std::max(max_len, seqs[i]->len);
+    }
+    const int hd = p->head_dim;
+    const size_t meta_bytes = 2 * (size_t)kStaticAttnMaxSeqs * sizeof(int32_t);
+    const size_t per_split = (size_t)n * n_heads * (hd + 2) * sizeof(float);
+    const size_t room = kStaticAttnScratchBytes - meta_bytes;
+    if (per_split > room) {
+        set_error("n=%d sequences x %d heads x head_dim %d need %zu bytes of scratch per context split; the allocation-free "
+                  "entry point has %zu", n, n_heads, hd, per_split, room);
+        return JUNO_ERR_INVALID_ARG;
+    }
+    int n_splits = attn_pick_splits(c, n, p->n_kv_heads, max_len);
+    n_splits = (int)std::min<size_t>((size_t)n_splits, room / per_split);
+    int32_t *d_meta = static_cast<int32_t *>(base);
+    float *sc = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + meta_bytes);
+    JUNO_CUDA_TRY(cudaMemcpyAsync(d_meta, meta, 2 * (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
+    AttnArgs a;
+    a.pool = p;
+    a.layer = layer;
+    a.n = n;
+    a.n_heads = n_heads;
+    a.q = q_dev;
+    a.out = out_dev;
+    a.slots = d_meta;
+    a.seq_lens = d_meta + n;
+    a.n_splits = n_splits;
+    a.part_o = sc;  // every (sequence, head, split) entry is rewritten by this call: nothing has to start at zero
+    a.part_ml = sc + (size_t)n * n_heads * n_splits * hd;
+    for (int i = 0; i < n; i++) a.algo_bytes += (double)seqs[i]->len * p->n_kv_heads * hd * 2 * p->elem_bytes;
+    JUNO_TRY(launch_attn(c, a, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));  // `meta` lives on this stack frame
     return JUNO_OK;
 }
 
