@@ -76,6 +76,8 @@ constexpr int kAttnUnroll = 4;  // positions in flight per token slot
 template <typename T, int HD, int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnParams p) {
     constexpr int LPT = HD / 8, TPW = 32 / LPT, SLOTS = kAttnWarps * TPW;
+    pdl_launch_dependents();
+    pdl_wait();
     const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int len = p.seq_lens[seq];
@@ -218,6 +220,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
 // The split weights are computed once in parallel (one split per thread) instead of once per output element.
 template <int HD>
 __global__ void attn_combine_kernel(const AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
     const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h) * p.n_splits * 2;
@@ -337,7 +341,7 @@ int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
 template <typename T, int HD, int G>
 static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
     dim3 grid(p.n_kv_heads, p.n_splits, n);
-    attn_split_kernel<T, HD, G><<<grid, kAttnWarps * 32, 0, st>>>(p);
+    launch_pdl(attn_split_kernel<T, HD, G>, grid, dim3(kAttnWarps * 32), 0, st, p);
 }
 
 template <typename T, int HD>
@@ -398,9 +402,9 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     JUNO_CUDA_TRY(cudaGetLastError());
     dim3 cgrid(a.n_heads, a.n);
     if (hd == 128)
-        attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(p);
+        launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, st, p);
     else
-        attn_combine_kernel<64><<<cgrid, 64, 0, st>>>(p);
+        launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, st, p);
     JUNO_CUDA_TRY(cudaGetLastError());
     ctx->kernel_launches += 2;
     return JUNO_OK;

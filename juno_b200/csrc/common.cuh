@@ -7,7 +7,9 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
+#include <utility>
 #include <vector>
 
 #include "../../include/juno_b200.h"
@@ -119,6 +121,35 @@ struct ProfScope {
         c->prof_spans.push_back(sp);
     }
 };
+
+// Programmatic dependent launch: a kernel launched with the attribute may be scheduled while the previous kernel of
+// the stream is still running; it must execute pdl_wait() before it touches anything that kernel (or an earlier one)
+// produces.  Here only weight prefetches and a launch-private work counter happen before the wait.
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("JUNO_NO_PDL");
+        return !(v && *v == '1');
+    }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 struct DeviceGuard {
     int prev = -1;

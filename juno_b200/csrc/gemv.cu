@@ -346,6 +346,8 @@ size_t stage_chunk_bytes(int K, int rows_in_chunk) { return (size_t)K * 3 * rows
 constexpr int kStageThreads = 256;
 
 __global__ void __launch_bounds__(kStageThreads) stage_kernel(const StageParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.im.K;
     unsigned short *xb;
@@ -448,6 +450,7 @@ template <int TYPE, int NB>
 __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     constexpr int NC = 3 * NB, NT = (NC + 7) / 8, LD = 8 * NT;
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = p.K;
     unsigned short *xb = reinterpret_cast<unsigned short *>(smem);  // K*NC bf16 limbs
@@ -471,6 +474,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     bool have = (ct < p.n_ctasks) && (R < p.total_rt);
     const uint8_t *cur_ptr = have ? tile_addr<TYPE>(p, R, sb0) : nullptr;
     if (have) load_tile<TYPE>(bufA, cur_ptr, lane);
+    pdl_wait();  // everything below reads what earlier kernels of the stream wrote
 
     // staged activation -> shared memory
     {
@@ -700,8 +704,7 @@ int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t st) {
     p.eps = a.eps;
     p.im = stage_image_desc(ctx, a.img, a.K, a.batch);
     ProfScope prof(ctx, st, PROF_OTHER, 0);
-    stage_kernel<<<a.batch, kStageThreads, 0, st>>>(p);
-    JUNO_CUDA_TRY(cudaGetLastError());
+    JUNO_CUDA_TRY(launch_pdl(stage_kernel, dim3(a.batch), dim3(kStageThreads), 0, st, p));
     ctx->kernel_launches++;
     return JUNO_OK;
 }
@@ -719,8 +722,7 @@ static int launch_inst(juno_ctx *ctx, const GemvParams &p, int grid, size_t smem
             configured[dev] = ctx->smem_optin;
         }
     }
-    gemv_kernel<TYPE, NB><<<grid, kThreads, smem, st>>>(p);
-    JUNO_CUDA_TRY(cudaGetLastError());
+    JUNO_CUDA_TRY(launch_pdl(gemv_kernel<TYPE, NB>, dim3(grid), dim3(kThreads), smem, st, p));
     ctx->kernel_launches++;
     return JUNO_OK;
 }
