@@ -30,6 +30,9 @@ struct AttnParams {
     const float *knew, *vnew;
     int ldkv;
     void *kw, *vw;
+    // when set ([n][n_kv_heads], zero between launches): the last split CTA of a (sequence, kv head) to finish
+    // merges the splits itself and no separate merge kernel is launched
+    unsigned *merge_counters;
 };
 
 template <typename T>
@@ -70,6 +73,53 @@ __device__ __forceinline__ void load8<float>(const float *p, float (&o)[8]) {
 constexpr int kAttnWarps = 4;
 constexpr int kAttnUnroll = 4;  // positions in flight per token slot
 
+// Merge of the context splits of the G heads of one kv head by a block of 128 threads, all heads at once:
+// the split weights of head g are computed by warp g % 4 (one or two splits per lane), then every thread
+// accumulates G*HD/128 outputs.  One block barrier inside.
+template <int HD, int G>
+__device__ __forceinline__ void merge_splits_group(const AttnParams &p, int seq, int h0, int tid, float (*f)[64], float *Ls) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int g = warp; g < G; g += 4) {
+        const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h0 + g) * p.n_splits * 2;
+        float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
+        if (lane < p.n_splits) {
+            m0 = __ldcg(pml + 2 * lane);
+            l0 = __ldcg(pml + 2 * lane + 1);
+        }
+        if (lane + 32 < p.n_splits) {  // n_splits <= 64
+            m1 = __ldcg(pml + 2 * (lane + 32));
+            l1 = __ldcg(pml + 2 * (lane + 32) + 1);
+        }
+        float M = fmaxf(m0, m1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float f0 = (l0 > 0.f) ? exp2f(m0 - M) : 0.f, f1 = (l1 > 0.f) ? exp2f(m1 - M) : 0.f;  // log2 domain
+        f[g][lane] = f0;
+        f[g][lane + 32] = f1;
+        float L = fmaf(l0, f0, l1 * f1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (lane == 0) Ls[g] = L;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += 128) {
+        const int g = idx / HD, d = idx - g * HD, h = h0 + g;
+        const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < p.n_splits; s++) acc = fmaf(__ldcg(po + (size_t)s * HD + d), f[g][s], acc);
+        const float L = Ls[g];
+        const float outv = (L > 0.f) ? acc / L : 0.f;
+        p.out[(size_t)(seq * p.n_heads + h) * HD + d] = outv;
+        if (p.stage.img) {
+            unsigned short *xb;
+            int NC, col0;
+            p.stage.locate(seq, xb, NC, col0);
+            stage_store1(xb, NC, col0, h * HD + d, outv);
+        }
+    }
+}
+
 // One CTA = (kv head, context split, sequence).  HD/8 lanes share one cached position (eight head dimensions
 // each, one 128-bit load for K and one for V), so a warp works on 32/(HD/8) positions at a time and every lane
 // keeps an online-softmax state for the G query heads of the group; the states are merged through shared memory.
@@ -86,14 +136,17 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
     const int h0 = kvh * G;
     float *po = p.part_o + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * HD;   // head stride n_splits*HD
     float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
+    __shared__ float sm_m[SLOTS][G], sm_l[SLOTS][G];
+    __shared__ float sm_o[SLOTS][G][HD];
+    __shared__ float mg_f[G][64], mg_L[G];
+    __shared__ int is_last;
     if (t0 >= t1) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
         if (tid < G) {
             pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
             pml[(size_t)tid * p.n_splits * 2 + 1] = 0.f;
         }
         for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) po[(size_t)(idx / HD) * p.n_splits * HD + (idx % HD)] = 0.f;
-        return;
-    }
+    } else {
     const int sub = lane % LPT, slot = warp * TPW + lane / LPT;
     const unsigned gmask = (LPT == 32) ? 0xffffffffu : (((1u << LPT) - 1u) << (lane - sub));
     // scores in the log2 domain: exp(x) = exp2(x * log2(e))
@@ -182,8 +235,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
         }
     }
     // merge the token slots of this CTA
-    __shared__ float sm_m[SLOTS][G], sm_l[SLOTS][G];
-    __shared__ float sm_o[SLOTS][G][HD];
 #pragma unroll
     for (int g = 0; g < G; g++) {
         if (sub == 0) {
@@ -214,6 +265,21 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
             pml[(size_t)g * p.n_splits * 2 + 1] = L;
         }
     }
+    }  // non-empty split
+    if (!p.merge_counters) return;
+    // the last split of this (sequence, kv head) to get here merges all of them (no waiting: whoever is last does it)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned *ctr = p.merge_counters + seq * p.n_kv_heads + kvh;
+        const unsigned old = atomicAdd(ctr, 1u);
+        is_last = (old == (unsigned)p.n_splits - 1u);
+        if (is_last) *ctr = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    merge_splits_group<HD, G>(p, seq, h0, tid, mg_f, mg_L);
 }
 
 // Merges the context splits of one (sequence, head): blockDim = HD threads, one output dimension each.
@@ -335,6 +401,7 @@ int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
     int by_occupancy = (target + n * n_kv_heads - 1) / std::max(1, n * n_kv_heads);
     int by_length = std::max(1, (max_len + 63) / 64);  // at least 64 positions per split
     int s = std::max(1, std::min(by_occupancy, by_length));
+    if (const char *e = getenv("JUNO_ATTN_SPLITS")) s = std::max(1, std::min(s, atoi(e)));
     return std::min(s, 64);
 }
 
@@ -380,6 +447,7 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     p.part_o = a.part_o;
     p.part_ml = a.part_ml;
     p.out = a.out;
+    p.merge_counters = a.merge_counters;
     p.rope_cs = a.rope_cs;
     p.knew = a.knew;
     p.vnew = a.vnew;
@@ -400,6 +468,10 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
         rc = hd == 128 ? attn_launch_g<float, 128>(p, a.n, G, st) : attn_launch_g<float, 64>(p, a.n, G, st);
     JUNO_TRY(rc);
     JUNO_CUDA_TRY(cudaGetLastError());
+    if (a.merge_counters) {
+        ctx->kernel_launches += 1;
+        return JUNO_OK;
+    }
     dim3 cgrid(a.n_heads, a.n);
     if (hd == 128)
         launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, st, p);

@@ -52,6 +52,9 @@ struct AttnArgs {
     const float2 *rope_cs = nullptr;
     const float *knew = nullptr, *vnew = nullptr;
     int ldkv = 0;
+    // optional: [n][n_kv_heads] words, zero between launches; the last split CTA per (sequence, kv head) then merges
+    // the splits itself and the separate merge kernel is not launched
+    unsigned *merge_counters = nullptr;
     // optional: also emit the output as a staged GEMV activation (K = n_heads*hd columns per sequence)
     uint8_t *stage_img = nullptr;
     int stage_bc = 1;

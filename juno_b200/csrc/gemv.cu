@@ -162,31 +162,43 @@ struct XView {
 };
 
 // ── Q4_K tile ────────────────────────────────────────────────────────────────────────────
+// Nibbles -> bf16 pairs holding 128 + q exactly (mask | magic in one instruction).  The bias is not removed here:
+// sum((128+q)*x) = 128*sum(x) + sum(q*x), and the 128*scale*sum(x) part is subtracted once per tile together with
+// the min term (both are "per-sub-block constant times sum of x over the sub-block").
 __device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t M, uint32_t K, uint32_t &lo_a, uint32_t &lo_b,
                                           uint32_t &hi_a, uint32_t &hi_b) {
-    lo_a = bf2_sub(and_or(w, M, K), K);        // (byte0.lo, byte2.lo)
-    hi_a = bf2_sub(and_or(w >> 4, M, K), K);   // (byte0.hi, byte2.hi)
-    lo_b = bf2_sub(and_or(w >> 8, M, K), K);   // (byte1.lo, byte3.lo)
-    hi_b = bf2_sub(and_or(w >> 12, M, K), K);  // (byte1.hi, byte3.hi)
+    lo_a = and_or(w, M, K);        // (byte0.lo, byte2.lo)
+    hi_a = and_or(w >> 4, M, K);   // (byte0.hi, byte2.hi)
+    lo_b = and_or(w >> 8, M, K);   // (byte1.lo, byte3.lo)
+    hi_b = and_or(w >> 12, M, K);  // (byte1.hi, byte3.hi)
+}
+
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t v, uint32_t c) {
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&v);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&c);
+    __nv_bfloat162 r = __hmul2(a, b);
+    return *reinterpret_cast<uint32_t *>(&r);
 }
 
 // Decodes one row's header words for the lane's two sub-blocks 2c, 2c+1.
-__device__ __forceinline__ void q4_header(uint32_t dm, uint32_t sm, float &sc0, float &sc1, uint32_t &mins_bf2, float &dmin) {
-    const float d = f16bits_to_f32(dm);
+__device__ __forceinline__ void q4_header(uint32_t dm, uint32_t sm, float &sc0, float &sc1, uint32_t &mins_bf2,
+                                          uint32_t &sc128_bf2, float &d, float &dmin) {
+    d = f16bits_to_f32(dm);
     dmin = f16bits_to_f32(dm >> 16);
     sc0 = __fmul_rn(d, (float)(sm & 0xFFu));
     sc1 = __fmul_rn(d, (float)((sm >> 8) & 0xFFu));
-    mins_bf2 = bf2_sub(__byte_perm(sm, 0x43434343u, 0x4342), kBf128);  // bf16x2 (m0, m1)
+    mins_bf2 = bf2_sub(__byte_perm(sm, 0x43434343u, 0x4342), kBf128);                          // bf16x2 (m0, m1)
+    sc128_bf2 = bf2_mul(bf2_sub(__byte_perm(sm, 0x43434343u, 0x4140), kBf128), kBf128);       // (128*s0, 128*s1), exact
 }
 
 template <int NC>
 __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, const XView<NC> &xv, int lane,
                                              float (&acc)[(NC + 7) / 8][4], float (&macc)[(NC + 7) / 8][4]) {
     constexpr int NT = (NC + 7) / 8;
-    float s_r[2], s_q[2], dmin_r, dmin_q;
-    uint32_t mins_r, mins_q;
-    q4_header(R.dm0, R.sm0, s_r[0], s_r[1], mins_r, dmin_r);
-    q4_header(R.dm1, R.sm1, s_q[0], s_q[1], mins_q, dmin_q);
+    float s_r[2], s_q[2], dmin_r, dmin_q, d_r, d_q;
+    uint32_t mins_r, mins_q, off_r, off_q;
+    q4_header(R.dm0, R.sm0, s_r[0], s_r[1], mins_r, off_r, d_r, dmin_r);
+    q4_header(R.dm1, R.sm1, s_q[0], s_q[1], mins_q, off_q, d_q, dmin_q);
     const int s16base = sb * 16;
     // held in registers on purpose (see and_or)
     uint32_t M4 = 0x000F000Fu, K128 = kBf128;
@@ -225,12 +237,14 @@ __device__ __forceinline__ void compute_tile(const TileRegs<12> &R, int sb, cons
     // min term: sum_j (dmin*m_j) * sum_{c in sub-block j} x[c]
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-        float cm[4];
-        mma1688_z(cm, mins_r, mins_q, xv.sums(nt, sb));
-        macc[nt][0] = fmaf(dmin_r, cm[0], macc[nt][0]);
-        macc[nt][1] = fmaf(dmin_r, cm[1], macc[nt][1]);
-        macc[nt][2] = fmaf(dmin_q, cm[2], macc[nt][2]);
-        macc[nt][3] = fmaf(dmin_q, cm[3], macc[nt][3]);
+        float cm[4], co[4];
+        const uint32_t xsum = xv.sums(nt, sb);
+        mma1688_z(cm, mins_r, mins_q, xsum);
+        mma1688_z(co, off_r, off_q, xsum);  // sum_j 128*sc_j * sum(x over sub-block j): the bias of the nibbles
+        macc[nt][0] = fmaf(dmin_r, cm[0], fmaf(d_r, co[0], macc[nt][0]));
+        macc[nt][1] = fmaf(dmin_r, cm[1], fmaf(d_r, co[1], macc[nt][1]));
+        macc[nt][2] = fmaf(dmin_q, cm[2], fmaf(d_q, co[2], macc[nt][2]));
+        macc[nt][3] = fmaf(dmin_q, cm[3], fmaf(d_q, co[3], macc[nt][3]));
     }
 }
 
@@ -329,6 +343,59 @@ __device__ __forceinline__ void compute_tile(const TileRegs<8> &R, int sb, const
     }
 }
 
+// ── mixed launches: Q4_K and Q6_K segments in one grid (the fused Q,K,V projection of a Q4_K_M model) ─────────
+// TYPE 0 keeps a tile in a format-neutral register image and dispatches per task on the segment's block format
+// (warp-uniform: a warp works on one row tile at a time).
+template <>
+struct TileRegs<0> {
+    uint4 v[6];
+    uint32_t s[4];
+};
+template <int TYPE>
+__device__ __forceinline__ void load_tile_t(TileRegs<TYPE> &r, const uint8_t *tile, int lane, int /*type*/) {
+    load_tile<TYPE>(r, tile, lane);
+}
+template <>
+__device__ __forceinline__ void load_tile_t<0>(TileRegs<0> &r, const uint8_t *tile, int lane, int type) {
+    if (type == 12) {
+        TileRegs<12> t;
+        load_tile<12>(t, tile, lane);
+#pragma unroll
+        for (int g = 0; g < 4; g++) r.v[g] = t.q[g];
+        r.s[0] = t.dm0; r.s[1] = t.dm1; r.s[2] = t.sm0; r.s[3] = t.sm1;
+    } else {
+        TileRegs<14> t;
+        load_tile<14>(t, tile, lane);
+#pragma unroll
+        for (int m = 0; m < 4; m++) r.v[m] = t.ql[m];
+        r.v[4] = t.qh[0]; r.v[5] = t.qh[1];
+        r.s[0] = t.sc0; r.s[1] = t.sc1; r.s[2] = t.d01;
+    }
+}
+template <int TYPE, int NC>
+__device__ __forceinline__ void compute_tile_t(const TileRegs<TYPE> &R, int /*type*/, int sb, const XView<NC> &xv, int lane,
+                                               float (&acc)[(NC + 7) / 8][4], float (&macc)[(NC + 7) / 8][4]) {
+    compute_tile<NC>(R, sb, xv, lane, acc, macc);
+}
+template <int NC>
+__device__ __forceinline__ void compute_tile_mixed(const TileRegs<0> &R, int type, int sb, const XView<NC> &xv, int lane,
+                                                   float (&acc)[(NC + 7) / 8][4], float (&macc)[(NC + 7) / 8][4]) {
+    if (type == 12) {
+        TileRegs<12> t;
+#pragma unroll
+        for (int g = 0; g < 4; g++) t.q[g] = R.v[g];
+        t.dm0 = R.s[0]; t.dm1 = R.s[1]; t.sm0 = R.s[2]; t.sm1 = R.s[3];
+        compute_tile<NC>(t, sb, xv, lane, acc, macc);
+    } else {
+        TileRegs<14> t;
+#pragma unroll
+        for (int m = 0; m < 4; m++) t.ql[m] = R.v[m];
+        t.qh[0] = R.v[4]; t.qh[1] = R.v[5];
+        t.sc0 = R.s[0]; t.sc1 = R.s[1]; t.d01 = R.s[2];
+        compute_tile<NC>(t, sb, xv, lane, acc, macc);
+    }
+}
+
 // ───────────────────────────── activation staging ─────────────────────────────────────────
 // One CTA per batch row writes that row's three limb columns of the staged image.
 struct StageParams {
@@ -416,6 +483,7 @@ struct GemvParams {
     const uint8_t *w[3];
     float *out[3];
     int rows[3];
+    int seg_type[3];  // block format per segment (used by mixed launches)
     int rt_begin[4];  // cumulative row-tile starts, rt_begin[nseg] = total
     int nseg, total_rt;
     int K, nb;
@@ -438,12 +506,18 @@ struct GemvParams {
     StageImage img_next;  // also used by EPI_SILU_PAIR / EPI_STORE to emit the output as a staged activation
 };
 
-template <int TYPE>
-__device__ __forceinline__ const uint8_t *tile_addr(const GemvParams &p, int R, int sb) {
+__device__ __forceinline__ int seg_of(const GemvParams &p, int R) {
     int s = 0;
     if (p.nseg > 1 && R >= p.rt_begin[1]) s = 1;
     if (p.nseg > 2 && R >= p.rt_begin[2]) s = 2;
-    return p.w[s] + ((size_t)(R - p.rt_begin[s]) * p.nb + sb) * (size_t)tile_bytes(TYPE);
+    return s;
+}
+// Address of tile (R, sb) and, for mixed launches, the block format of R's segment.
+template <int TYPE>
+__device__ __forceinline__ const uint8_t *tile_addr(const GemvParams &p, int R, int sb, int &type) {
+    const int s = seg_of(p, R);
+    type = (TYPE == 0) ? p.seg_type[s] : TYPE;
+    return p.w[s] + ((size_t)(R - p.rt_begin[s]) * p.nb + sb) * (size_t)tile_bytes(type);
 }
 
 template <int TYPE, int NB>
@@ -455,7 +529,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     const int K = p.K;
     unsigned short *xb = reinterpret_cast<unsigned short *>(smem);  // K*NC bf16 limbs
     unsigned short *xs = xb + (size_t)K * NC;                       // (K/32)*NC bf16: 32-column sums (Q4_K only)
-    const size_t xs_bytes = (TYPE == 12) ? ((((size_t)(K / 32) * NC * 2) + 15) & ~(size_t)15) : 0;
+    const size_t xs_bytes = (TYPE == 12 || TYPE == 0) ? ((((size_t)(K / 32) * NC * 2) + 15) & ~(size_t)15) : 0;
     float *cs = reinterpret_cast<float *>(smem + p.img_bytes + xs_bytes);  // [2][kWarps][16][LD]
     float *sqbuf = cs + 2 * kWarps * 16 * LD;                               // [groups*16*NB] (EPI_RESID_NORM)
     float *scale_s = sqbuf + kWarps * 16 * NB;                              // [NB]
@@ -472,8 +546,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     TileRegs<TYPE> bufA, bufB;
     int R = ct * p.groups + grp;
     bool have = (ct < p.n_ctasks) && (R < p.total_rt);
-    const uint8_t *cur_ptr = have ? tile_addr<TYPE>(p, R, sb0) : nullptr;
-    if (have) load_tile<TYPE>(bufA, cur_ptr, lane);
+    int cur_type = TYPE, next_type = TYPE;
+    const uint8_t *cur_ptr = have ? tile_addr<TYPE>(p, R, sb0, cur_type) : nullptr;
+    if (have) load_tile_t<TYPE>(bufA, cur_ptr, lane, cur_type);
     pdl_wait();  // everything below reads what earlier kernels of the stream wrote
 
     // staged activation -> shared memory
@@ -496,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         if (lane == 0) scale_s[warp] = sc;
     }
     __syncthreads();
-    if (TYPE == 12) {
+    if (TYPE == 12 || TYPE == 0) {
         // sums of x over 32 columns, from the limbs (hi + mid + lo is x exactly): eight threads per sum
         const int total = (K / 4) * NB;
         for (int item = tid; item < total; item += kThreads) {
@@ -548,26 +623,36 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         const int nR = nct * p.groups + grp;
         const bool nhave = (nct < p.n_ctasks) && (nR < p.total_rt);
         // first tile of this warp in the next task (prefetched while the last tile of this one is computed)
-        const uint8_t *next_base = nhave ? tile_addr<TYPE>(p, nR, sb0) : nullptr;
+        const uint8_t *next_base = nhave ? tile_addr<TYPE>(p, nR, sb0, next_type) : nullptr;
         if (have) {
             for (int j = 0; j < p.tpt; j++) {
-                const uint8_t *np = (j + 1 < p.tpt) ? cur_ptr + tile_bytes(TYPE) : next_base;
+                const bool more = j + 1 < p.tpt;
+                const uint8_t *np = more ? cur_ptr + tile_bytes(cur_type) : next_base;
+                const int np_type = more ? cur_type : next_type;
                 if (phase == 0) {
-                    if (np) load_tile<TYPE>(bufB, np, lane);
-                    compute_tile<NC>(bufA, sb0 + j, xv, lane, acc, macc);
+                    if (np) load_tile_t<TYPE>(bufB, np, lane, np_type);
+                    if constexpr (TYPE == 0)
+                        compute_tile_mixed<NC>(bufA, cur_type, sb0 + j, xv, lane, acc, macc);
+                    else
+                        compute_tile_t<TYPE, NC>(bufA, cur_type, sb0 + j, xv, lane, acc, macc);
                 } else {
-                    if (np) load_tile<TYPE>(bufA, np, lane);
-                    compute_tile<NC>(bufB, sb0 + j, xv, lane, acc, macc);
+                    if (np) load_tile_t<TYPE>(bufA, np, lane, np_type);
+                    if constexpr (TYPE == 0)
+                        compute_tile_mixed<NC>(bufB, cur_type, sb0 + j, xv, lane, acc, macc);
+                    else
+                        compute_tile_t<TYPE, NC>(bufB, cur_type, sb0 + j, xv, lane, acc, macc);
                 }
                 cur_ptr = np;
                 phase ^= 1;
             }
+            cur_type = next_type;
         } else if (nhave) {  // idle in this task, but the next one has work: fetch its first tile
             if (phase == 0)
-                load_tile<TYPE>(bufA, next_base, lane);
+                load_tile_t<TYPE>(bufA, next_base, lane, next_type);
             else
-                load_tile<TYPE>(bufB, next_base, lane);
+                load_tile_t<TYPE>(bufB, next_base, lane, next_type);
             cur_ptr = next_base;
+            cur_type = next_type;
         }
         // fragments -> shared memory (double-buffered: one barrier per task)
         float *mycs = cs + ((it & 1) * kWarps + warp) * 16 * LD;
@@ -774,7 +859,10 @@ int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_rt) {
 
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
     JUNO_REQUIRE(a.nseg >= 1 && a.nseg <= 3, "gemv: nseg %d", a.nseg);
-    JUNO_REQUIRE(a.type == 12 || a.type == 14 || a.type == 8, "gemv: type %d has no tiled kernel", a.type);
+    JUNO_REQUIRE(a.type == 0 || a.type == 12 || a.type == 14 || a.type == 8, "gemv: type %d has no tiled kernel", a.type);
+    if (a.type == 0)
+        for (int s = 0; s < a.nseg; s++)
+            JUNO_REQUIRE(a.seg[s].type == 12 || a.seg[s].type == 14, "gemv: mixed launches take Q4_K and Q6_K segments only");
     JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0, "gemv: K=%d must be a multiple of 256", a.K);
     JUNO_REQUIRE(a.batch >= 1 && a.ximg, "gemv: batch %d / missing staged activation", a.batch);
     const int nb = a.K / 256;
@@ -786,10 +874,13 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
 
     double algo_bytes = (double)a.batch * a.K * 4;
     {
-        const double bpw = a.type == 12 ? 144.0 / 256 : a.type == 14 ? 210.0 / 256 : 34.0 / 32;
-        for (int s = 0; s < a.nseg; s++) algo_bytes += (double)a.seg[s].rows * a.K * bpw + (double)a.batch * a.seg[s].rows * 4;
+        for (int s = 0; s < a.nseg; s++) {
+            const int t = a.seg[s].type ? a.seg[s].type : a.type;
+            const double bpw = t == 12 ? 144.0 / 256 : t == 14 ? 210.0 / 256 : 34.0 / 32;
+            algo_bytes += (double)a.seg[s].rows * a.K * bpw + (double)a.batch * a.seg[s].rows * 4;
+        }
     }
-    ProfScope prof(ctx, st, a.type == 12 ? PROF_GEMV_Q4K : a.type == 14 ? PROF_GEMV_Q6K : PROF_GEMV_Q80, algo_bytes);
+    ProfScope prof(ctx, st, (a.type == 12 || a.type == 0) ? PROF_GEMV_Q4K : a.type == 14 ? PROF_GEMV_Q6K : PROF_GEMV_Q80, algo_bytes);
 
     const int bc_full = gemv_batch_chunk(ctx, a.K, a.batch);
     const size_t chunk_stride = stage_chunk_bytes(a.K, bc_full);
@@ -807,6 +898,7 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
             p.w[s] = a.seg[s].w;
             p.out[s] = a.seg[s].out ? a.seg[s].out + (size_t)b0 * a.ld_out : nullptr;
             p.rows[s] = a.seg[s].rows;
+            p.seg_type[s] = a.seg[s].type ? a.seg[s].type : a.type;
             p.rt_begin[s] = rt;
             rt += a.seg[s].row_tiles;
         }
@@ -843,7 +935,9 @@ int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
         int grid = std::min(max_grid, p.n_ctasks);
         grid = std::max(1, std::min(env_int("JUNO_GEMV_GRID", grid), p.n_ctasks));
         int rc;
-        if (a.type == 12)
+        if (a.type == 0)
+            rc = launch_type<0>(ctx, p, bc, grid, smem, st);
+        else if (a.type == 12)
             rc = launch_type<12>(ctx, p, bc, grid, smem, st);
         else if (a.type == 14)
             rc = launch_type<14>(ctx, p, bc, grid, smem, st);

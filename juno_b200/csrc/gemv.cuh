@@ -51,12 +51,13 @@ struct GemvSeg {
     float *out;       // [batch][ld_out]
     int rows;         // valid rows
     int row_tiles;
+    int type = 0;     // block format of this segment; 0 = GemvArgs.type
 };
 
 struct GemvArgs {
     GemvSeg seg[3];
     int nseg = 1;
-    int type = 0;
+    int type = 0;     // 12 / 14 / 8, or 0 for a launch that mixes Q4_K and Q6_K segments
     int K = 0;
     int batch = 1;
     int ld_out = 0;   // stride between batch rows of every seg.out

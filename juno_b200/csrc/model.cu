@@ -213,6 +213,7 @@ struct juno_model {
     uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
+    unsigned *attn_counters = nullptr;  // [max_batch][kv heads], self-resetting
     size_t attn_scratch_floats = 0;
     float2 *rope_cs = nullptr;
     int32_t *d_step = nullptr;  // tokens | positions | slots | seq_lens, max_batch each
@@ -223,7 +224,8 @@ struct juno_model {
     int last_n = 0, last_x = 0;
     double step_kv_bytes = 0;  // K+V bytes one layer's attention reads in the current step
     std::map<uint64_t, JunoGraph> graphs;
-    bool use_graphs = true;
+    unsigned debug_skip = 0;  // JUNO_DEBUG_SKIP: leave kernels out of the step (results are wrong; for timing attribution only)
+    bool use_graphs = true, mix_formats = true, fused_merge = false;  // JUNO_NO_GRAPH / JUNO_NO_MIXED / JUNO_FUSED_MERGE
 };
 
 namespace juno {
@@ -293,7 +295,7 @@ static void model_release(juno_model *m) {
         kvpool_destroy(m->pool);
     }
     void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
-                    m->attn_scratch, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
+                    m->attn_scratch, m->attn_counters, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
         if (b) cudaFree(b);
@@ -360,6 +362,16 @@ int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) 
     m->layers.resize(cfg->n_layers);
     const char *ng = getenv("JUNO_NO_GRAPH");
     m->use_graphs = !(ng && *ng == '1');
+    if (const char *sk = getenv("JUNO_DEBUG_SKIP")) {
+        const char *names[6] = {"qkv", "attn", "wo", "gateup", "down", "logits"};
+        for (int i = 0; i < 6; i++)
+            if (strstr(sk, names[i])) m->debug_skip |= 1u << i;
+    }
+    // merging the splits inside the attention kernel (last CTA per kv head) measured slower than the separate merge
+    // kernel on B200 (fence + atomic in every CTA, serial tail): off unless JUNO_FUSED_MERGE=1
+    const char *nm = getenv("JUNO_NO_MIXED"), *nf = getenv("JUNO_FUSED_MERGE");
+    m->mix_formats = !(nm && *nm == '1');
+    m->fused_merge = (nf && *nf == '1');
     if (w > 1) {
         int rc = nccl_load();
         if (rc == JUNO_OK) {
@@ -499,6 +511,8 @@ extern "C" int juno_model_finalize(juno_model *m) {
     }
     m->attn_scratch_floats = (size_t)(c->sm_count * 4 + B * m->kv_loc) * (m->heads_loc / m->kv_loc) * (hd + 2) + 64;
     JUNO_TRY(dev_alloc((void **)&m->attn_scratch, m->attn_scratch_floats * 4));
+    JUNO_TRY(dev_alloc((void **)&m->attn_counters, (size_t)B * m->kv_loc * 4));
+    JUNO_CUDA_TRY(cudaMemset(m->attn_counters, 0, (size_t)B * m->kv_loc * 4));
     JUNO_TRY(dev_alloc((void **)&m->rope_cs, (size_t)B * (hd / 2) * sizeof(float2)));
     JUNO_TRY(dev_alloc((void **)&m->d_step, (size_t)4 * B * 4));
     JUNO_TRY(dev_alloc((void **)&m->d_argmax, (size_t)B * 4));
@@ -515,11 +529,18 @@ namespace juno {
 // ───────────────────────────── one decode step, enqueued on the context stream ────────────
 static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, const GemvArgs &proto,
                       cudaStream_t st) {
-    // consecutive matrices of one block format share a launch (they share the staged activation)
+    // matrices that share the staged activation share a launch: one block format, or Q4_K mixed with Q6_K
     int i = 0;
     while (i < count) {
         int j = i + 1;
-        while (j < count && j - i < 3 && mats[j]->type == mats[i]->type) j++;
+        bool mixed = false;
+        while (j < count && j - i < 3) {
+            const int ta = mats[i]->type, tb = mats[j]->type;
+            const bool k_quant = m->mix_formats && (ta == 12 || ta == 14) && (tb == 12 || tb == 14);
+            if (tb != ta && !k_quant) break;
+            if (tb != mats[j - 1]->type || tb != ta) mixed = mixed || (tb != ta);
+            j++;
+        }
         GemvArgs a = proto;
         a.nseg = j - i;
         for (int s = 0; s < a.nseg; s++) {
@@ -527,8 +548,9 @@ static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs,
             a.seg[s].out = outs[i + s];
             a.seg[s].rows = a.epi == EPI_SILU_PAIR ? (int)mats[i + s]->rows / 2 : (int)mats[i + s]->rows;
             a.seg[s].row_tiles = (int)mats[i + s]->row_tiles;
+            a.seg[s].type = mats[i + s]->type;
         }
-        a.type = mats[i]->type;
+        a.type = mixed ? 0 : mats[i]->type;
         a.K = (int)mats[i]->cols;
         JUNO_TRY(launch_gemv(m->ctx, a, st));
         i = j;
@@ -632,7 +654,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
             set_input_scale(m, a, scaled, ss_d, parts_d);
             juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
             float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
-            JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, a, st));
+            if (!(m->debug_skip & 1u)) JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, a, st));
         }
         AttnArgs at;
         at.pool = m->pool;
@@ -652,12 +674,14 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         at.knew = m->qkv + Hl;
         at.vnew = m->qkv + Hl + KVl;
         at.ldkv = m->qkv_ld;
-        at.stage_img = m->img_att;  // the merge kernel writes Wo's staged input directly
+        at.merge_counters = m->fused_merge ? m->attn_counters : nullptr;
+        at.stage_img = m->img_att;  // the merge writes Wo's staged input directly
         at.stage_bc = gemv_batch_chunk(c, Hl, n);
         at.stage_chunk_stride = stage_chunk_bytes(Hl, at.stage_bc);
-        JUNO_TRY(launch_attn(c, at, st));
+        if (!(m->debug_skip & 2u)) JUNO_TRY(launch_attn(c, at, st));
         // x2 = x + Wo·att ; staged rmsNorm(x2, ffn_norm)
-        JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled, st));
+        if (!(m->debug_skip & 4u))
+            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled, st));
         // hdn = silu(Wgate·xn2) * (Wup·xn2), emitted as Wdown's staged input
         {
             GemvArgs a;
@@ -670,11 +694,12 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
             set_input_scale(m, a, scaled, ss_o, parts_o);
             juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
             float *gu_o[1] = {nullptr};
-            JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, a, st));
+            if (!(m->debug_skip & 8u)) JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, a, st));
         }
         // x = x2 + Wdown·hdn ; staged rmsNorm(x, next norm)
         const float *next_norm = (l + 1 < f.n_layers) ? m->layers[l + 1].attn_norm : m->output_norm;
-        JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, st));
+        if (!(m->debug_skip & 16u))
+            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, st));
     }
     // logits = Wout · rmsNorm(x, output_norm)
     {
@@ -685,7 +710,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         set_input_scale(m, a, scaled, ss_d, parts_d);
         juno_qmat *l_m[1] = {m->output};
         float *l_o[1] = {m->logits_loc};
-        JUNO_TRY(gemv_group(m, l_m, l_o, 1, a, st));
+        if (!(m->debug_skip & 32u)) JUNO_TRY(gemv_group(m, l_m, l_o, 1, a, st));
     }
     m->last_x = cur;
     LogitsView lv;
