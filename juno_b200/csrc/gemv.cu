@@ -72,8 +72,10 @@ constexpr uint32_t kBf128 = 0x43004300u;  // (128, 128)
 constexpr uint32_t kBf160 = 0x43204320u;  // (160, 160)
 constexpr uint32_t kBf384 = 0x43C043C0u;  // (384, 384)
 
-// SiLU as LlamaTransformerHandler.silu (:1733-1735): x / (1f + (float) Math.exp(-x)).
-__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.f, (float)exp((double)(-x)))); }
+// SiLU as LlamaTransformerHandler.silu (:1733-1735): x / (1f + (float) Math.exp(-x)).  The exponential is taken in
+// FP32 (expf, <= 2 ulp) instead of binary64-then-cast: a binary64 exp on the few threads of a GEMV epilogue sat on the
+// critical path of every CTA task.
+__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.f, expf(-x))); }
 
 template <int TYPE>
 struct TileRegs;
@@ -674,7 +676,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
             const float *csb = cs + (it & 1) * kWarps * 16 * LD;
             const int rows_out = (p.epi == EPI_SILU_PAIR) ? 8 : 16;
             const int per_b = p.groups * rows_out, total = per_b * NB;
-            for (int idx = tid; idx < total; idx += kThreads) {
+            // successive tasks start their epilogue on successive warps, so no single warp carries it every time
+            const int etid = (tid + 32 * (it & 7)) & (kThreads - 1);
+            for (int idx = etid; idx < total; idx += kThreads) {
                 const int b = idx / per_b, rg = idx - b * per_b, g = rg / rows_out, row = rg - g * rows_out;
                 const int Rg = ct * p.groups + g;
                 float sq = 0.f;
@@ -718,10 +722,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
             }
             if (p.epi == EPI_RESID_NORM) {  // per-task sum of squares, rows in order
                 __syncthreads();
-                if (tid < NB) {
+                if (etid < NB) {
                     float s = 0.f;
-                    for (int i = 0; i < per_b; i++) s += sqbuf[tid * per_b + i];
-                    p.ss_out[(size_t)tid * p.ss_out_ld + ct] = s;
+                    for (int i = 0; i < per_b; i++) s += sqbuf[etid * per_b + i];
+                    p.ss_out[(size_t)etid * p.ss_out_ld + ct] = s;
                 }
             }
         }
