@@ -23,7 +23,9 @@ sys.path.insert(0, ROOT)
 
 from juno_b200 import synth  # noqa: E402
 
-MODELS = {"llama3-8b": (synth.LLAMA3_8B, 3), "tinyllama": (synth.TINYLLAMA, 0), "llama3-70b": (synth.LLAMA3_70B, 4)}
+MODELS = {"llama3-8b": (synth.LLAMA3_8B, 3), "tinyllama": (synth.TINYLLAMA, 0), "llama3-70b": (synth.LLAMA3_70B, 4),
+          # the 8B layer shapes with 4 layers and a 32000-row output: small enough for profiler captures
+          "llama3-8b-4layer": (synth.Arch(4096, 4, 32, 8, 14336, 32000, 1e-5, 500000.0), 3)}
 METRIC = "decode_tokens_per_s"
 BPW = {synth.Q4_K: 144 / 256, synth.Q6_K: 210 / 256, synth.Q8_0: 34 / 32}
 

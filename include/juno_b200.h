@@ -217,8 +217,9 @@ int juno_ctx_counters(juno_ctx *ctx, juno_counters *out, int32_t reset);
  * While enabled every launch is bracketed by CUDA events on the context stream and forward passes run
  * without CUDA graphs; juno_ctx_profile_read synchronises and returns, per category, launches, summed
  * milliseconds and the algorithmic bytes the launches had to move.  Categories: 0 Q4_K GEMV, 1 Q6_K GEMV,
- * 2 Q8_0 GEMV, 3 attention (split + merge), 4 RoPE + KV append, 5 other. */
-#define JUNO_PROF_COUNT 6
+ * 2 Q8_0 GEMV, 3 attention (split + merge), 4 RoPE + KV append, 5 other, 6 the persistent decode-step kernel
+ * (all products and attention of a step in one launch). */
+#define JUNO_PROF_COUNT 7
 typedef struct juno_profile_entry {
     int64_t launches;
     double ms;

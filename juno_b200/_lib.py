@@ -33,7 +33,7 @@ class ProfileEntry(C.Structure):
     _fields_ = [("launches", C.c_int64), ("ms", C.c_double), ("algo_bytes", C.c_double)]
 
 
-PROF_NAMES = ["gemv_q4k", "gemv_q6k", "gemv_q8_0", "attention", "rope_append", "other"]
+PROF_NAMES = ["gemv_q4k", "gemv_q6k", "gemv_q8_0", "attention", "rope_append", "other", "decode_step"]
 
 P = C.c_void_p
 PP = C.POINTER(C.c_void_p)

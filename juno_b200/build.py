@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libjuno_b200.so")
-SOURCES = ["context.cu", "gemv.cu", "attn.cu", "model.cu"]
+SOURCES = ["context.cu", "gemv.cu", "attn.cu", "step.cu", "model.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -38,7 +38,7 @@ def _newest_header() -> float:
 
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ, src.replace(".cu", ".o"))
-    cmd = [nvcc(), *ARCH, "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-O2", "-ccbin", "g++", "-c",
+    cmd = [nvcc(), *ARCH, "-O3", "-lineinfo", "-std=c++17", "--split-compile", "0", "-Xcompiler", "-fPIC,-O2", "-ccbin", "g++", "-c",
            os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd += ["-Xptxas", "-v"]

@@ -11,6 +11,7 @@
 
 #include "attn.cuh"
 #include "stage.cuh"
+#include "step.cuh"
 
 namespace juno {
 
@@ -425,6 +426,7 @@ static int attn_launch_g(const AttnParams &p, int n, int G, cudaStream_t st) {
 }
 
 int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
+    if (ctx->step_rec) return step_record_attn(ctx, a);
     const juno_kvpool *pool = a.pool;
     JUNO_REQUIRE(a.n_heads % pool->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", a.n_heads,
                  pool->n_kv_heads);

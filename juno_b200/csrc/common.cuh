@@ -64,13 +64,17 @@ struct GemvScratch {
 }  // namespace juno
 
 namespace juno {
-enum ProfCat { PROF_GEMV_Q4K = 0, PROF_GEMV_Q6K, PROF_GEMV_Q80, PROF_ATTN, PROF_ROPE_APPEND, PROF_OTHER, PROF_COUNT };
+enum ProfCat { PROF_GEMV_Q4K = 0, PROF_GEMV_Q6K, PROF_GEMV_Q80, PROF_ATTN, PROF_ROPE_APPEND, PROF_OTHER, PROF_STEP, PROF_COUNT };
 struct ProfSpan {
     int cat;
     double bytes;
     cudaEvent_t e0, e1;
 };
 }  // namespace juno
+
+namespace juno {
+struct StepRecorder;
+}
 
 struct juno_ctx {
     uint32_t magic;
@@ -80,6 +84,8 @@ struct juno_ctx {
     cudaStream_t stream;
     std::recursive_mutex mu;
     juno::GemvScratch gemv_scratch;
+    // while set, launch_gemv / launch_attn describe their work to the recorder instead of launching (step.cuh)
+    juno::StepRecorder *step_rec = nullptr;
     // staging buffers for the host-in/host-out entry points
     float *stage_x = nullptr, *stage_y = nullptr;
     size_t stage_x_bytes = 0, stage_y_bytes = 0;

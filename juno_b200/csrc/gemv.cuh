@@ -82,6 +82,12 @@ struct GemvArgs {
 // Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
 int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
 
+struct GemvParams;
+// Kernel-side description of rows [b0, b0+bc) of the batch (chunk index `chunk` of the staged activation) with the
+// given CTA-task geometry.
+int gemv_fill_params(juno_ctx *ctx, const GemvArgs &a, int b0, int bc, int chunk, int kin, int tpt, int groups, int n_ctasks,
+                     GemvParams *out);
+
 // Enqueues the product on `stream`.  All pointers are device pointers.
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 // Raw-layout / FP32 fallback (one warp per output), used for shapes the tile layout does not cover.

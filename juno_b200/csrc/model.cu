@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "attn.cuh"
+#include "step.cuh"
 #include "common.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
@@ -226,6 +227,9 @@ struct juno_model {
     std::map<uint64_t, JunoGraph> graphs;
     unsigned debug_skip = 0;  // JUNO_DEBUG_SKIP: leave kernels out of the step (results are wrong; for timing attribution only)
     bool use_graphs = true, mix_formats = true, fused_merge = false;  // JUNO_NO_GRAPH / JUNO_NO_MIXED / JUNO_FUSED_MERGE
+    bool use_step = false;                  // JUNO_STEP_KERNEL=1: the persistent step kernel instead of one kernel per product
+    std::map<int, juno::StepPlan> step_plans;  // by number of sequences
+    juno::StepPlan *last_plan = nullptr;
 };
 
 namespace juno {
@@ -299,6 +303,9 @@ static void model_release(juno_model *m) {
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
         if (b) cudaFree(b);
+    for (auto &kv : m->step_plans) step_plan_free(&kv.second);
+    m->step_plans.clear();
+    m->last_plan = nullptr;
     if (m->h_step) cudaFreeHost(m->h_step);
     m->magic = kMagicDead;
 }
@@ -371,6 +378,13 @@ int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) 
     // kernel on B200 (fence + atomic in every CTA, serial tail): off unless JUNO_FUSED_MERGE=1
     const char *nm = getenv("JUNO_NO_MIXED"), *nf = getenv("JUNO_FUSED_MERGE");
     m->mix_formats = !(nm && *nm == '1');
+    {
+        // The persistent step kernel (all products and the attention of a step in one cooperative launch) is
+        // correct but measured slower than one kernel per product on the 8B batch-1 workload (3.2-3.7 ms against
+        // 2.46 ms per step): its per-tile instruction overhead outweighs what it saves in launches.  Opt-in.
+        const char *ns = getenv("JUNO_STEP_KERNEL");
+        m->use_step = (ns && *ns == '1') && w == 1 && m->debug_skip == 0;
+    }
     m->fused_merge = (nf && *nf == '1');
     if (w > 1) {
         int rc = nccl_load();
@@ -511,8 +525,8 @@ extern "C" int juno_model_finalize(juno_model *m) {
     }
     m->attn_scratch_floats = (size_t)(c->sm_count * 4 + B * m->kv_loc) * (m->heads_loc / m->kv_loc) * (hd + 2) + 64;
     JUNO_TRY(dev_alloc((void **)&m->attn_scratch, m->attn_scratch_floats * 4));
-    JUNO_TRY(dev_alloc((void **)&m->attn_counters, (size_t)B * m->kv_loc * 4));
-    JUNO_CUDA_TRY(cudaMemset(m->attn_counters, 0, (size_t)B * m->kv_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->attn_counters, (size_t)B * m->heads_loc * 4));
+    JUNO_CUDA_TRY(cudaMemset(m->attn_counters, 0, (size_t)B * m->heads_loc * 4));
     JUNO_TRY(dev_alloc((void **)&m->rope_cs, (size_t)B * (hd / 2) * sizeof(float2)));
     JUNO_TRY(dev_alloc((void **)&m->d_step, (size_t)4 * B * 4));
     JUNO_TRY(dev_alloc((void **)&m->d_argmax, (size_t)B * 4));
@@ -619,12 +633,50 @@ static void set_input_scale(juno_model *m, GemvArgs &a, bool scaled_by_consumer,
     a.eps = m->cfg.rms_eps;
 }
 
+// Whether this model and batch size run through the persistent step kernel.
+static bool step_model_ok(juno_model *m, int n) {
+    if (m->world != 1) return false;
+    int max_K = std::max(m->cfg.hidden, std::max(m->heads_loc * m->hd, m->inter_loc));
+    int max_tile = 0;
+    auto visit = [&](const juno_qmat *q) {
+        if (!q) return true;
+        if (!q->tiled || (q->type != 12 && q->type != 14 && q->type != 8)) return false;
+        max_tile = std::max(max_tile, tile_bytes(q->type));
+        return true;
+    };
+    for (const JunoLayer &L : m->layers)
+        for (int k : {JUNO_T_ATTN_Q, JUNO_T_ATTN_K, JUNO_T_ATTN_V, JUNO_T_ATTN_OUT, JUNO_T_FFN_GATE, JUNO_T_FFN_DOWN})
+            if (!visit(L.w[k])) return false;
+    if (!visit(m->output)) return false;
+    // the staged activations must be single chunks (the step kernel copies one image per product)
+    for (int K : {m->cfg.hidden, m->heads_loc * m->hd, m->inter_loc})
+        if (gemv_batch_chunk(m->ctx, K, n) != n) return false;
+    return step_supported(m->ctx, n, m->hd, m->heads_loc, m->kv_loc, max_K, max_tile);
+}
+
 static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
     const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
     const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
+    // Persistent step kernel: the products and the attention below are recorded as phases (once per batch size) and
+    // run as one cooperative launch.
+    StepPlan *plan = nullptr;
+    StepRecorder rec;
+    if (m->use_step && step_model_ok(m, n)) {
+        plan = &m->step_plans[n];
+        if (!plan->d_phases) {
+            rec.grid = c->sm_count;
+            rec.n = n;
+            c->step_rec = &rec;
+        }
+    }
+    struct RecGuard {
+        juno_ctx *c;
+        ~RecGuard() { c->step_rec = nullptr; }
+    } rec_guard{c};
+    const bool replay = plan && plan->d_phases;
     float *ss_o = m->ss, *ss_d = m->ss + (size_t)B * kSsLd;  // sums of squares written by Wo / Wdown epilogues
     const int parts_o = gemv_n_ctasks(c, Hl, n, H / 16), parts_d = gemv_n_ctasks(c, Il, n, H / 16);
     JUNO_REQUIRE(parts_o <= kSsLd && parts_d <= kSsLd, "hidden size %d needs more than %d partial sums", H, kSsLd);
@@ -643,7 +695,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
 
     int cur = 0;          // x[cur] holds the residual stream
     bool scaled = false;  // img_h holds normw*x and the consumer still has to apply 1/rms
-    for (int l = 0; l < f.n_layers; l++) {
+    for (int l = 0; l < f.n_layers && !replay; l++) {
         JunoLayer &L = m->layers[l];
         // q,k,v = W·rmsNorm(x)
         {
@@ -674,7 +726,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         at.knew = m->qkv + Hl;
         at.vnew = m->qkv + Hl + KVl;
         at.ldkv = m->qkv_ld;
-        at.merge_counters = m->fused_merge ? m->attn_counters : nullptr;
+        at.merge_counters = (m->fused_merge || c->step_rec) ? m->attn_counters : nullptr;
         at.stage_img = m->img_att;  // the merge writes Wo's staged input directly
         at.stage_bc = gemv_batch_chunk(c, Hl, n);
         at.stage_chunk_stride = stage_chunk_bytes(Hl, at.stage_bc);
@@ -702,7 +754,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
             JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, st));
     }
     // logits = Wout · rmsNorm(x, output_norm)
-    {
+    if (!replay) {
         GemvArgs a;
         a.batch = n;
         a.ximg = m->img_h;
@@ -711,6 +763,16 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         juno_qmat *l_m[1] = {m->output};
         float *l_o[1] = {m->logits_loc};
         if (!(m->debug_skip & 32u)) JUNO_TRY(gemv_group(m, l_m, l_o, 1, a, st));
+    }
+    if (plan) {
+        if (c->step_rec) {
+            c->step_rec = nullptr;
+            JUNO_TRY(step_plan_build(c, rec, m->pool->dtype == 1, hd, m->heads_loc / m->kv_loc, plan));
+            plan->timeline_period = (plan->n_phases - 1) / std::max(1, f.n_layers);
+        }
+        JUNO_TRY(launch_step(c, *plan, st));
+        m->last_plan = plan;
+        cur = 0;  // every layer flips the residual buffer twice
     }
     m->last_x = cur;
     LogitsView lv;
@@ -781,6 +843,16 @@ static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
     JUNO_CUDA_TRY(cudaGraphLaunch(g.exec, st));
     c->kernel_launches += launches;
     return JUNO_OK;
+}
+
+// After a stream synchronise: did the last step kernel give up on a wait?
+static int step_check(juno_model *m) {
+    if (!m->last_plan) return JUNO_OK;
+    const unsigned code = step_plan_error(*m->last_plan);
+    if (!code) return JUNO_OK;
+    set_error("decode step kernel gave up waiting (code %u, warp %u of block %u; codes: 1 grid barrier, 2 weight tile, 4 activation, "
+              "5/6 partial sums, 7/8 task hand-over, 9 copy cursor)", code & 0xffu, (code >> 8) & 0xffu, code >> 16);
+    return JUNO_ERR_CUDA;
 }
 
 static int bucket_len(int len) {
@@ -863,6 +935,7 @@ int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t 
         c->d2h_bytes += n * 4;
     }
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JUNO_TRY(step_check(m));
     for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + 1);
     m->last_n = n;
     return JUNO_OK;
@@ -899,6 +972,7 @@ int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const in
     c->forward_calls += steps;
     JUNO_CUDA_TRY(cudaMemcpyAsync(out_ids, m->d_out_ids, (size_t)steps * n * 4, cudaMemcpyDeviceToHost, c->stream));
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JUNO_TRY(step_check(m));
     c->d2h_bytes += (int64_t)steps * n * 4;
     for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + steps);
     m->last_n = n;

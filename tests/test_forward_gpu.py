@@ -11,9 +11,20 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3
 
 
+@pytest.fixture(params=["per-product", "step-kernel"])
+def engine(request, monkeypatch):
+    """Both execution engines of a decode step: one kernel per product (the default) and the persistent step
+    kernel (read from the environment when the model is created)."""
+    if request.param == "step-kernel":
+        monkeypatch.setenv("JUNO_STEP_KERNEL", "1")
+    else:
+        monkeypatch.delenv("JUNO_STEP_KERNEL", raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize("arch", [TINY, SMALL128], ids=["hd64", "hd128"])
 @pytest.mark.parametrize("kv_dtype", ["f32", "f16"])
-def test_stepwise_logits_match_oracle(ctx, oracle, arch, kv_dtype):
+def test_stepwise_logits_match_oracle(ctx, oracle, arch, kv_dtype, engine):
     om, h = build_pair(oracle, arch, seed=11, kv_dtype=kv_dtype, max_ctx=64, ctx=ctx)
     rng = np.random.default_rng(0)
     toks = rng.integers(0, arch.vocab, 40).tolist()
@@ -40,7 +51,7 @@ def test_token_id_clamped_like_reference(ctx, oracle):
 
 
 @pytest.mark.parametrize("kv_dtype", ["f32", "f16"])
-def test_greedy_ids_identical(ctx, oracle, kv_dtype):
+def test_greedy_ids_identical(ctx, oracle, kv_dtype, engine):
     om, h = build_pair(oracle, SMALL128, seed=13, kv_dtype=kv_dtype, max_ctx=128, ctx=ctx)
     rng = np.random.default_rng(1)
     prompt = rng.integers(0, SMALL128.vocab, 24).tolist()
@@ -112,7 +123,7 @@ def test_all_q4k_and_q8_models(ctx, oracle):
         h.release_gpu_resources()
 
 
-def test_tinyllama_config0_greedy_64(ctx, oracle):
+def test_tinyllama_config0_greedy_64(ctx, oracle, engine):
     """TinyLlama-1.1B architecture, random-init Q4_K_M from seed 0, 128 random prompt ids, 64 greedy steps:
     token ids identical to the CPU path (FP32 KV as the reference stores it, and the FP16-page engine against
     the oracle run with FP16 KV)."""
