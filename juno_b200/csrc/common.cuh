@@ -59,6 +59,7 @@ struct GemvScratch {
     unsigned next_slot = 0;
     uint8_t *ximg = nullptr;       // staged activation for the host-level entry points
     size_t ximg_bytes = 0;
+    float *xscale = nullptr;       // per-row factors of an FP16 staged activation (batched path), 64 floats
 };
 
 }  // namespace juno

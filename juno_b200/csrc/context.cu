@@ -3,6 +3,8 @@
 #include <string>
 
 #include "common.cuh"
+#include <algorithm>
+
 #include "gemv.cuh"
 
 namespace juno {
@@ -142,6 +144,7 @@ int juno_ctx_destroy(juno_ctx *c) {
     DeviceGuard g(c->device);
     cudaStreamSynchronize(c->stream);
     if (c->gemv_scratch.ximg) cudaFree(c->gemv_scratch.ximg);
+    if (c->gemv_scratch.xscale) cudaFree(c->gemv_scratch.xscale);
     if (c->gemv_scratch.counters) cudaFree(c->gemv_scratch.counters);
     if (c->stage_x) cudaFree(c->stage_x);
     if (c->stage_y) cudaFree(c->stage_y);
@@ -273,30 +276,53 @@ int juno_qmat_shape(juno_qmat *m, int64_t *rows, int64_t *cols, int32_t *type) {
 
 static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, float *y, cudaStream_t st) {
     if (!m->tiled) return launch_gemv_raw(c, m, x, batch, y, st);
-    const size_t need = stage_image_bytes(c, (int)m->cols, batch);
+    const bool batched = batch >= gemm_min_batch();
+    const size_t need = batched ? gemm_image_bytes((int)m->cols, std::min(batch, kGemmMaxBatch)) : stage_image_bytes(c, (int)m->cols, batch);
     void *pi = c->gemv_scratch.ximg;
     JUNO_TRY(ensure_device(&pi, &c->gemv_scratch.ximg_bytes, need));
     c->gemv_scratch.ximg = (uint8_t *)pi;
-    StageArgs sa;
-    sa.mode = STAGE_PLAIN;
-    sa.x = x;
-    sa.ldx = (int)m->cols;
-    sa.K = (int)m->cols;
-    sa.batch = batch;
-    sa.img = c->gemv_scratch.ximg;
-    JUNO_TRY(launch_stage(c, sa, st));
     GemvArgs a;
     a.nseg = 1;
     a.seg[0].w = m->dev;
-    a.seg[0].out = y;
     a.seg[0].rows = (int)m->rows;
     a.seg[0].row_tiles = (int)m->row_tiles;
     a.type = m->type;
     a.K = (int)m->cols;
-    a.batch = batch;
     a.ld_out = (int)m->rows;
     a.ximg = c->gemv_scratch.ximg;
-    return launch_gemv(c, a, st);
+    StageArgs sa;
+    sa.mode = STAGE_PLAIN;
+    sa.ldx = (int)m->cols;
+    sa.K = (int)m->cols;
+    sa.img = c->gemv_scratch.ximg;
+    if (!batched) {
+        sa.x = x;
+        sa.batch = batch;
+        JUNO_TRY(launch_stage(c, sa, st));
+        a.seg[0].out = y;
+        a.batch = batch;
+        return launch_gemv(c, a, st);
+    }
+    // one pass over the weights per group of up to kGemmMaxBatch rows
+    if (!c->gemv_scratch.xscale) {
+        cudaError_t e = cudaMalloc((void **)&c->gemv_scratch.xscale, kGemmMaxBatch * sizeof(float));
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            set_error("cudaMalloc of %zu bytes failed: %s", kGemmMaxBatch * sizeof(float), cudaGetErrorString(e));
+            return JUNO_ERR_OOM;
+        }
+    }
+    for (int b0 = 0; b0 < batch; b0 += kGemmMaxBatch) {
+        const int bc = std::min(kGemmMaxBatch, batch - b0);
+        sa.x = x + (size_t)b0 * m->cols;
+        sa.batch = bc;
+        JUNO_TRY(launch_stage_f16(c, sa, c->gemv_scratch.xscale, st));
+        a.seg[0].out = y + (size_t)b0 * m->rows;
+        a.batch = bc;
+        a.xscale = c->gemv_scratch.xscale;
+        JUNO_TRY(launch_gemm(c, a, st));
+    }
+    return JUNO_OK;
 }
 
 int juno_gemv_device(juno_ctx *c, juno_qmat *m, const float *x_dev, int32_t batch, float *y_dev, void *stream) {

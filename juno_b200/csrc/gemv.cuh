@@ -78,6 +78,8 @@ struct GemvArgs {
     // any epilogue: also emit the output as the staged activation of the next product (K = img_next_K)
     uint8_t *img_next = nullptr;
     int img_next_K = 0;
+    // batched path (launch_gemm): ximg is an FP16 image (launch_stage_f16) and xscale its per-row factors
+    const float *xscale = nullptr;
 };
 // Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
 int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
@@ -87,6 +89,17 @@ struct GemvParams;
 // given CTA-task geometry.
 int gemv_fill_params(juno_ctx *ctx, const GemvArgs &a, int b0, int bc, int chunk, int kin, int tpt, int groups, int n_ctasks,
                      GemvParams *out);
+
+// Batched path: one pass over the weights for up to kGemmMaxBatch sequences (FP16 operands on mma.sync, gemm.cu).
+// The activation is staged as ONE FP16 column per sequence, pre-scaled per row by a power of two (xscale holds the
+// factors to multiply the products with).  Epilogues: EPI_STORE, EPI_SILU_PAIR, and EPI_RESID_NORM meaning only
+// x_out = resid + y.
+constexpr int kGemmMaxBatch = 64;
+int gemm_min_batch();               // smallest batch routed to the batched path (JUNO_GEMM_MIN_BATCH, default 9)
+int gemm_padded_batch(int batch);   // image columns: batch rounded up to a multiple of 8
+size_t gemm_image_bytes(int K, int batch);
+int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t stream);
+int launch_gemm(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 
 // Enqueues the product on `stream`.  All pointers are device pointers.
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);

@@ -211,6 +211,7 @@ struct juno_model {
     juno::NcclComm comm = nullptr;
     // activations
     float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *ss = nullptr;
+    float *hdn = nullptr, *xsc = nullptr;  // batched path: silu(gate)*up rows; per-row factors of the three FP16 images
     uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
@@ -298,7 +299,7 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->hdn, m->xsc, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
                     m->attn_scratch, m->attn_counters, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
@@ -515,9 +516,14 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
     JUNO_TRY(dev_alloc((void **)&m->ss, (size_t)2 * B * kSsLd * 4));
-    JUNO_TRY(dev_alloc((void **)&m->img_h, stage_image_bytes(c, H, B)));
-    JUNO_TRY(dev_alloc((void **)&m->img_att, stage_image_bytes(c, m->heads_loc * hd, B)));
-    JUNO_TRY(dev_alloc((void **)&m->img_i, stage_image_bytes(c, m->inter_loc, B)));
+    const int Bg = std::min(B, kGemmMaxBatch);
+    JUNO_TRY(dev_alloc((void **)&m->img_h, std::max(stage_image_bytes(c, H, B), gemm_image_bytes(H, Bg))));
+    JUNO_TRY(dev_alloc((void **)&m->img_att, std::max(stage_image_bytes(c, m->heads_loc * hd, B), gemm_image_bytes(m->heads_loc * hd, Bg))));
+    JUNO_TRY(dev_alloc((void **)&m->img_i, std::max(stage_image_bytes(c, m->inter_loc, B), gemm_image_bytes(m->inter_loc, Bg))));
+    if (B >= gemm_min_batch()) {
+        JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
+        JUNO_TRY(dev_alloc((void **)&m->xsc, (size_t)3 * B * 4));
+    }
     JUNO_TRY(dev_alloc((void **)&m->logits_loc, (size_t)B * m->vocab_loc * 4));
     if (m->vocab_sharded) {
         JUNO_TRY(dev_alloc((void **)&m->logits_gather, (size_t)B * f.vocab * 4));
@@ -566,7 +572,7 @@ static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs,
         }
         a.type = mixed ? 0 : mats[i]->type;
         a.K = (int)mats[i]->cols;
-        JUNO_TRY(launch_gemv(m->ctx, a, st));
+        JUNO_TRY(a.xscale ? launch_gemm(m->ctx, a, st) : launch_gemv(m->ctx, a, st));
         i = j;
     }
     return JUNO_OK;
@@ -633,6 +639,94 @@ static void set_input_scale(juno_model *m, GemvArgs &a, bool scaled_by_consumer,
     a.eps = m->cfg.rms_eps;
 }
 
+// Layers and output projection of one step on the batched path (n >= gemm_min_batch()): every product is ONE pass
+// over its weights for all n sequences (launch_gemm), with separate staging kernels in between (they need the
+// whole row for its power-of-two factor).  x[0] holds the embeddings on entry; the residual stream ends in x[cur].
+static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, const int32_t *d_len, int n_splits, int &cur,
+                                  cudaStream_t st) {
+    juno_ctx *c = m->ctx;
+    const juno_model_cfg &f = m->cfg;
+    const int H = f.hidden, hd = m->hd, B = f.max_batch;
+    const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
+    float *sc_h = m->xsc, *sc_att = m->xsc + B, *sc_i = m->xsc + 2 * B;
+    auto stage = [&](int mode, const float *x, int ldx, const float *add, float *x_out, const float *normw, int K, uint8_t *img,
+                     float *sc) {
+        StageArgs a;
+        a.mode = mode;
+        a.x = x;
+        a.ldx = ldx;
+        a.x_add = add;
+        a.x_out = x_out;
+        a.normw = normw;
+        a.eps = f.rms_eps;
+        a.K = K;
+        a.batch = n;
+        a.img = img;
+        return launch_stage_f16(c, a, sc, st);
+    };
+    auto product = [&](juno_qmat *const *mats, float *const *outs, int count, int epi, int ld_out, const uint8_t *img,
+                       const float *sc) {
+        GemvArgs a;
+        a.batch = n;
+        a.ximg = img;
+        a.xscale = sc;
+        a.epi = epi;
+        a.ld_out = ld_out;
+        return gemv_group(m, mats, outs, count, a, st);
+    };
+    JUNO_TRY(stage(STAGE_RMSNORM, m->x[0], H, nullptr, nullptr, m->layers[0].attn_norm, H, m->img_h, sc_h));
+    cur = 0;
+    for (int l = 0; l < f.n_layers; l++) {
+        JunoLayer &L = m->layers[l];
+        juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
+        float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
+        JUNO_TRY(product(qkv_m, qkv_o, 3, EPI_STORE, m->qkv_ld, m->img_h, sc_h));
+        AttnArgs at;
+        at.pool = m->pool;
+        at.layer = l;
+        at.n = n;
+        at.n_heads = m->heads_loc;
+        at.q = m->qkv;
+        at.ldq = m->qkv_ld;
+        at.out = m->att;
+        at.slots = d_slot;
+        at.seq_lens = d_len;
+        at.n_splits = n_splits;
+        at.part_o = m->attn_scratch;
+        at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
+        at.algo_bytes = m->step_kv_bytes;
+        at.rope_cs = m->rope_cs;
+        at.knew = m->qkv + Hl;
+        at.vnew = m->qkv + Hl + KVl;
+        at.ldkv = m->qkv_ld;
+        JUNO_TRY(launch_attn(c, at, st));
+        JUNO_TRY(stage(STAGE_PLAIN, m->att, Hl, nullptr, nullptr, nullptr, Hl, m->img_att, sc_att));
+        // x2 = x + Wo att (summed over ranks first when tensor parallel), staged rmsNorm(x2, ffn_norm)
+        juno_qmat *wo[1] = {L.w[JUNO_T_ATTN_OUT]};
+        float *po[1] = {m->proj};
+        JUNO_TRY(product(wo, po, 1, EPI_STORE, H, m->img_att, sc_att));
+        if (m->world > 1)
+            JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        JUNO_TRY(stage(STAGE_RMSNORM, m->x[cur], H, m->proj, m->x[cur ^ 1], L.ffn_norm, H, m->img_h, sc_h));
+        cur ^= 1;
+        // hdn = silu(Wgate xn2) * (Wup xn2)
+        juno_qmat *gu[1] = {L.w[JUNO_T_FFN_GATE]};
+        float *pg[1] = {m->hdn};
+        JUNO_TRY(product(gu, pg, 1, EPI_SILU_PAIR, Il, m->img_h, sc_h));
+        JUNO_TRY(stage(STAGE_PLAIN, m->hdn, Il, nullptr, nullptr, nullptr, Il, m->img_i, sc_i));
+        juno_qmat *wd[1] = {L.w[JUNO_T_FFN_DOWN]};
+        JUNO_TRY(product(wd, po, 1, EPI_STORE, H, m->img_i, sc_i));
+        if (m->world > 1)
+            JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        const float *next_norm = (l + 1 < f.n_layers) ? m->layers[l + 1].attn_norm : m->output_norm;
+        JUNO_TRY(stage(STAGE_RMSNORM, m->x[cur], H, m->proj, m->x[cur ^ 1], next_norm, H, m->img_h, sc_h));
+        cur ^= 1;
+    }
+    juno_qmat *lm[1] = {m->output};
+    float *lo[1] = {m->logits_loc};
+    return product(lm, lo, 1, EPI_STORE, m->vocab_loc, m->img_h, sc_h);
+}
+
 // Whether this model and batch size run through the persistent step kernel.
 static bool step_model_ok(juno_model *m, int n) {
     if (m->world != 1) return false;
@@ -676,7 +770,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         juno_ctx *c;
         ~RecGuard() { c->step_rec = nullptr; }
     } rec_guard{c};
-    const bool replay = plan && plan->d_phases;
+    const bool replay = (plan && plan->d_phases) || (m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0);
     float *ss_o = m->ss, *ss_d = m->ss + (size_t)B * kSsLd;  // sums of squares written by Wo / Wdown epilogues
     const int parts_o = gemv_n_ctasks(c, Hl, n, H / 16), parts_d = gemv_n_ctasks(c, Il, n, H / 16);
     JUNO_REQUIRE(parts_o <= kSsLd && parts_d <= kSsLd, "hidden size %d needs more than %d partial sums", H, kSsLd);
@@ -691,9 +785,11 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         c->kernel_launches++;
     }
     JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
-    JUNO_TRY(stage_rms(m, n, m->x[0], nullptr, nullptr, m->layers[0].attn_norm, st));
-
     int cur = 0;          // x[cur] holds the residual stream
+    const bool batched = m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0;
+    if (batched) JUNO_TRY(enqueue_layers_batched(m, n, d_slot, d_len, n_splits, cur, st));
+    else JUNO_TRY(stage_rms(m, n, m->x[0], nullptr, nullptr, m->layers[0].attn_norm, st));
+
     bool scaled = false;  // img_h holds normw*x and the consumer still has to apply 1/rms
     for (int l = 0; l < f.n_layers && !replay; l++) {
         JunoLayer &L = m->layers[l];

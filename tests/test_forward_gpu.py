@@ -138,3 +138,41 @@ def test_tinyllama_config0_greedy_64(ctx, oracle, engine):
         om.close()
         first_bad = next((i for i, (a, b) in enumerate(zip(got, ref_ids.tolist())) if a != b), None)
         assert first_bad is None, (kv, first_bad, float(margins.min()))
+
+
+@pytest.mark.parametrize("n_seq", [9, 16, 37])
+def test_forward_batched_path_matches_oracle(ctx, oracle, n_seq):
+    """Batches above eight sequences take the one-pass dequant-GEMM path.  Its operands are rounded to FP16, about
+    3e-4 relative per product; the random-init test model amplifies a perturbation by up to ~100x on some sequences
+    (the exact batch-1 path shows 1e-6 per product and up to 2e-4 on the logits of the same sequences), and a sequence
+    that has drifted keeps drifting through its own KV entries.  So the end-to-end bounds are statistical: median
+    below 3e-3, 85 % of the (sequence, step) pairs below 3e-2, and a clear winner is always reproduced.  The
+    per-product 1e-3 bound of this path is checked in test_gemv_gpu.py."""
+    arch = SMALL128
+    om, h = build_pair(oracle, arch, seed=21, kv_dtype="f16", max_ctx=48, max_batch=n_seq, max_seqs=n_seq, ctx=ctx)
+    rng = np.random.default_rng(5)
+    ids = [f"s{i}" for i in range(n_seq)]
+    lens = {r: int(rng.integers(3, 10)) for r in ids}
+    streams = {r: rng.integers(0, arch.vocab, lens[r]).tolist() for r in ids}
+    oseq = {r: om.new_seq() for r in ids}
+    # bring the sequences to different positions one by one (batch-1 path), then step them all together
+    for r in ids:
+        for p in range(lens[r] - 1):
+            om.forward(oseq[r], streams[r][p], p)
+            h.forward_batch([r], [[streams[r][p]]], [p])
+    errs = []
+    nxt = {}
+    for step in range(3):
+        pos = [lens[r] - 1 + step for r in ids]
+        toks = [streams[r][-1] if step == 0 else nxt[r] for r in ids]
+        logits, got = h.forward_batch(ids, [[t] for t in toks], pos, want_logits=True, want_argmax=True)
+        for i, r in enumerate(ids):
+            ref = om.forward(oseq[r], toks[i], pos[i])
+            errs.append(rel_err(logits[i], ref))
+            nxt[r] = oracle.greedy(ref)
+            top2 = np.sort(ref)[-2:]
+            if top2[1] - top2[0] > 0.1 * np.abs(ref).max():  # a clear winner must be reproduced
+                assert got[i] == nxt[r]
+    errs = np.sort(np.array(errs))
+    assert float(np.median(errs)) < 3e-3 and errs[int(0.85 * len(errs))] < 3e-2, (float(np.median(errs)), errs[-4:])
+    h.release_gpu_resources()
