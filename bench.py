@@ -197,6 +197,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="start decoding at an empty context (quick runs)")
+    ap.add_argument("--chunked-prefill", action="store_true",
+                    help="fill the prompt through juno_prefill (batched kernels, up to 64 positions per pass) instead of token by token")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="start at position ctx-1 over a zero-filled KV cache (same bytes per step; for profiler runs)")
     args = ap.parse_args()
@@ -231,8 +233,8 @@ def main():
     start = 0 if args.no_prefill else args.ctx - 1
     max_ctx = start + W + K + e2e_steps + prof_steps + 8
     tensors = list(synth.random_model(arch, seed))
-    h = B200TransformerHandler(arch, ctx, max_batch=B, max_seqs=B, max_ctx=max_ctx, kv_dtype="f16", tp_rank=rank,
-                               tp_world=world, nccl_id=nccl_id)
+    h = B200TransformerHandler(arch, ctx, max_batch=max(B, 64) if args.chunked_prefill else B, max_seqs=B, max_ctx=max_ctx,
+                               kv_dtype="f16", tp_rank=rank, tp_world=world, nccl_id=nccl_id)
     h.load(tensors)
     if not (rank == 0 and world == 1 and not args.no_cpu_baseline):
         tensors = None  # free host copies unless the CPU baseline needs them
@@ -240,9 +242,21 @@ def main():
     rng = np.random.default_rng(1234)
     names = [f"s{i}" for i in range(B)]
     prompts = rng.integers(0, arch.vocab, (B, max(1, args.ctx)))
-    # prefill token by token, as GenerationLoop does (positions 0..ctx-2, logits discarded)
-    for p in ([] if args.skip_prefill else range(start)):
-        h.forward_batch(names, [[int(prompts[i, p])] for i in range(B)], [p] * B, want_logits=False, want_argmax=True)
+    # prefill token by token, as GenerationLoop does (positions 0..ctx-2, logits discarded), or in chunks
+    prefill = None
+    if not args.skip_prefill and start > 0:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if args.chunked_prefill:
+            for i in range(B):
+                h.prefill(names[i], prompts[i, :start].tolist(), 0)
+        else:
+            for p in range(start):
+                h.forward_batch(names, [[int(prompts[i, p])] for i in range(B)], [p] * B, want_logits=False, want_argmax=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        prefill = {"mode": "chunked" if args.chunked_prefill else "token-by-token", "tokens": int(B * start),
+                   "tokens_per_s": B * start / dt, "seconds": dt}
     stream = torch.cuda.ExternalStream(ctx.stream(), device=torch.device("cuda", local_rank))
     pos = start
     last = [int(prompts[i, min(start, prompts.shape[1] - 1)]) for i in range(B)]
@@ -301,7 +315,10 @@ def main():
     ctx.profile(False)
     peak, peak_kind = measured_peaks()
     g = prof["gemv_q4k"]
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<Q4_K> (fused dequant-GEMV)", "achieved": None, "peak": peak,
+    kname = "gemv_kernel<Q4_K> (fused dequant-GEMV)" if B < 9 else "gemm_kernel<Q4_K> (one-pass batched dequant-GEMM)"
+    if prof.get("decode_step", {}).get("launches"):  # JUNO_STEP_KERNEL=1: the whole step is one kernel
+        g, kname = prof["decode_step"], "decode_step_kernel (persistent step kernel; weights only)"
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": None, "peak": peak,
                 "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind}
     if g["launches"]:
         ach = g["algo_bytes"] / (g["ms"] / 1e3) / 1e9
@@ -320,6 +337,8 @@ def main():
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, arch), "clocks": clocks, "e2e": e2e,
             "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]), "roofline": roofline,
             "step_roofline": step_roof, "kernels_profiled": kernels}
+    if prefill:
+        line["prefill"] = prefill
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             v, cores, sample = cpu_decode_rate(arch, tensors, 15.0)

@@ -195,6 +195,14 @@ int juno_model_seq_create(juno_model *m, juno_seq **out);
  * argmax_out ([n], first maximum = SampleStep.java:51-58) may each be NULL. */
 int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *token_ids,
                  const int32_t *positions, float *logits_host, int32_t *argmax_out);
+/* Prompt prefill in chunks: feeds token_ids[0..n_tokens) of ONE sequence at positions start_pos.. and fills its KV
+ * pages, up to min(max_batch, 64) positions per pass through the batched dequant-GEMM kernels (causal attention
+ * inside a chunk).  Replaces the token-by-token prefill loop of GenerationLoop.java:306-317 (same positions, same
+ * cache contents up to the FP16 rounding of the batched path).  logits_host ([vocab]) and argmax_out (one id) are
+ * optional and refer to the LAST position fed.  Tensor parallel models: logits only with an unsharded vocabulary. */
+int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t n_tokens, int32_t start_pos,
+                 float *logits_host, int32_t *argmax_out);
+
 /* `steps` greedy steps kept on the device: step 0 feeds first_tokens at positions, step s>0
  * feeds the token picked at step s-1 at positions+s.  out_ids is [steps][n]. */
 int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t *first_tokens,

@@ -76,6 +76,7 @@ SIGNATURES = {
     "juno_model_seq_create": (C.c_int, [P, PP]),
     "juno_forward": (C.c_int, [P, I32, PP, P, P, P, P]),
     "juno_decode_greedy": (C.c_int, [P, I32, PP, P, P, I32, P]),
+    "juno_prefill": (C.c_int, [P, P, P, I32, I32, P, P]),
     "juno_model_last_hidden": (C.c_int, [P, I32, P]),
 }
 

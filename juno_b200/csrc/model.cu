@@ -381,7 +381,7 @@ int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) 
     m->mix_formats = !(nm && *nm == '1');
     {
         // The persistent step kernel (all products and the attention of a step in one cooperative launch) is
-        // correct but measured slower than one kernel per product on the 8B batch-1 workload (3.2-3.7 ms against
+        // correct but measured slower than one kernel per product on the 8B batch-1 workload (3.2-3.9 ms against
         // 2.46 ms per step): its per-tile instruction overhead outweighs what it saves in launches.  Opt-in.
         const char *ns = getenv("JUNO_STEP_KERNEL");
         m->use_step = (ns && *ns == '1') && w == 1 && m->debug_skip == 0;
@@ -520,10 +520,8 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->img_h, std::max(stage_image_bytes(c, H, B), gemm_image_bytes(H, Bg))));
     JUNO_TRY(dev_alloc((void **)&m->img_att, std::max(stage_image_bytes(c, m->heads_loc * hd, B), gemm_image_bytes(m->heads_loc * hd, Bg))));
     JUNO_TRY(dev_alloc((void **)&m->img_i, std::max(stage_image_bytes(c, m->inter_loc, B), gemm_image_bytes(m->inter_loc, Bg))));
-    if (B >= gemm_min_batch()) {
-        JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
-        JUNO_TRY(dev_alloc((void **)&m->xsc, (size_t)3 * B * 4));
-    }
+    JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
+    JUNO_TRY(dev_alloc((void **)&m->xsc, (size_t)3 * B * 4));
     JUNO_TRY(dev_alloc((void **)&m->logits_loc, (size_t)B * m->vocab_loc * 4));
     if (m->vocab_sharded) {
         JUNO_TRY(dev_alloc((void **)&m->logits_gather, (size_t)B * f.vocab * 4));
@@ -643,7 +641,7 @@ static void set_input_scale(juno_model *m, GemvArgs &a, bool scaled_by_consumer,
 // over its weights for all n sequences (launch_gemm), with separate staging kernels in between (they need the
 // whole row for its power-of-two factor).  x[0] holds the embeddings on entry; the residual stream ends in x[cur].
 static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, const int32_t *d_len, int n_splits, int &cur,
-                                  cudaStream_t st) {
+                                  cudaStream_t st, const int32_t *d_prefill_pos = nullptr, bool want_logits = true) {
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
@@ -695,10 +693,17 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
         at.part_o = m->attn_scratch;
         at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
         at.algo_bytes = m->step_kv_bytes;
-        at.rope_cs = m->rope_cs;
-        at.knew = m->qkv + Hl;
-        at.vnew = m->qkv + Hl + KVl;
-        at.ldkv = m->qkv_ld;
+        if (d_prefill_pos) {
+            // chunked prefill: the n rows are consecutive positions of ONE sequence; their k, v are rotated and
+            // appended first, so that every row finds the rows before it in the cache (causal by construction)
+            JUNO_TRY(launch_rope_append(c, m->pool, l, n, m->heads_loc, m->qkv, m->qkv_ld, m->qkv + Hl, m->qkv + Hl + KVl, m->qkv_ld,
+                                        d_slot, d_prefill_pos, m->rope_cs, st));
+        } else {
+            at.rope_cs = m->rope_cs;
+            at.knew = m->qkv + Hl;
+            at.vnew = m->qkv + Hl + KVl;
+            at.ldkv = m->qkv_ld;
+        }
         JUNO_TRY(launch_attn(c, at, st));
         JUNO_TRY(stage(STAGE_PLAIN, m->att, Hl, nullptr, nullptr, nullptr, Hl, m->img_att, sc_att));
         // x2 = x + Wo att (summed over ranks first when tensor parallel), staged rmsNorm(x2, ffn_norm)
@@ -722,6 +727,7 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
         JUNO_TRY(stage(STAGE_RMSNORM, m->x[cur], H, m->proj, m->x[cur ^ 1], next_norm, H, m->img_h, sc_h));
         cur ^= 1;
     }
+    if (!want_logits) return JUNO_OK;
     juno_qmat *lm[1] = {m->output};
     float *lo[1] = {m->logits_loc};
     return product(lm, lo, 1, EPI_STORE, m->vocab_loc, m->img_h, sc_h);
@@ -1034,6 +1040,80 @@ int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t 
     JUNO_TRY(step_check(m));
     for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + 1);
     m->last_n = n;
+    return JUNO_OK;
+}
+
+int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t n_tokens, int32_t start_pos,
+                 float *logits_host, int32_t *argmax_out) {
+    JUNO_TRY(model_check(m));
+    juno_ctx *c = m->ctx;
+    std::lock_guard<std::recursive_mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    JUNO_REQUIRE(m->finalized, "model is not finalized");
+    JUNO_REQUIRE(seq && seq->magic == kMagicSeq && seq->pool == m->pool, "sequence is closed or belongs to another model");
+    JUNO_REQUIRE(token_ids && n_tokens >= 1 && start_pos >= 0, "bad prefill arguments (n_tokens=%d, start_pos=%d)", n_tokens, start_pos);
+    JUNO_REQUIRE(start_pos + n_tokens <= m->cfg.max_ctx, "position %d is beyond max_ctx %d", start_pos + n_tokens - 1, m->cfg.max_ctx);
+    JUNO_REQUIRE(m->pool->dtype == 0 || m->pool->dtype == 1, "unsupported KV type");
+    const juno_model_cfg &f = m->cfg;
+    const int B = f.max_batch, chunk_max = std::min(B, kGemmMaxBatch), V = f.vocab;
+    cudaStream_t st = c->stream;
+    for (int done = 0; done < n_tokens;) {
+        const int n = std::min(chunk_max, n_tokens - done), pos0 = start_pos + done;
+        const bool last = done + n == n_tokens;
+        JUNO_CUDA_TRY(cudaStreamSynchronize(st));  // the pinned step buffer is reused
+        JUNO_TRY(seq_reserve(seq, pos0 + n, st));
+        for (int i = 0; i < n; i++) {
+            m->h_step[i] = token_ids[done + i];
+            m->h_step[B + i] = pos0 + i;
+            m->h_step[2 * B + i] = seq->slot;
+            m->h_step[3 * B + i] = pos0 + i + 1;
+        }
+        JUNO_CUDA_TRY(cudaMemcpyAsync(m->d_step, m->h_step, (size_t)4 * B * 4, cudaMemcpyHostToDevice, st));
+        c->h2d_bytes += 4 * n * 4;
+        m->step_kv_bytes = 0;
+        for (int i = 0; i < n; i++) m->step_kv_bytes += (double)(pos0 + i + 1) * m->kv_loc * m->hd * 2 * m->pool->elem_bytes;
+        const int n_splits = attn_pick_splits(c, n, m->kv_loc, bucket_len(pos0 + n));
+        const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
+        {
+            juno_qmat *e = m->tok_embd;
+            dim3 grid((f.hidden + 255) / 256, n);
+            int64_t rb = e->tiled ? 0 : e->cols / raw_block_elems(e->type) * raw_block_bytes(e->type);
+            embed_kernel<<<grid, 256, 0, st>>>(e->type, e->tiled, e->dev, e->nb, rb, f.hidden, V, d_tok, m->x[0]);
+            JUNO_CUDA_TRY(cudaGetLastError());
+            c->kernel_launches++;
+        }
+        JUNO_TRY(launch_rope_table(c, d_pos, n, m->hd, f.rope_theta, m->rope_cs, st));
+        int cur = 0;
+        JUNO_TRY(enqueue_layers_batched(m, n, d_slot, d_len, n_splits, cur, st, d_pos, last && (logits_host || argmax_out)));
+        m->last_x = cur;
+        m->last_n = n;
+        c->forward_calls++;
+        if (last && (logits_host || argmax_out)) {
+            // row n-1 is the last prompt position
+            const float *row = m->logits_loc + (size_t)(n - 1) * m->vocab_loc;
+            JUNO_REQUIRE(!m->vocab_sharded, "prefill logits are not implemented for a sharded vocabulary");
+            if (argmax_out) {
+                LogitsView lv;
+                lv.n = 1;
+                lv.vocab = V;
+                lv.base = row;
+                lv.vloc = V;
+                argmax_partial_kernel<<<dim3(kArgmaxBlocks, 1), 256, 0, st>>>(lv, m->d_pval, m->d_pidx);
+                argmax_final_kernel<<<1, 64, 0, st>>>(m->d_pval, m->d_pidx, 1, m->d_argmax);
+                JUNO_CUDA_TRY(cudaGetLastError());
+                c->kernel_launches += 2;
+                JUNO_CUDA_TRY(cudaMemcpyAsync(argmax_out, m->d_argmax, 4, cudaMemcpyDeviceToHost, st));
+                c->d2h_bytes += 4;
+            }
+            if (logits_host) {
+                JUNO_CUDA_TRY(cudaMemcpyAsync(logits_host, row, (size_t)V * 4, cudaMemcpyDeviceToHost, st));
+                c->d2h_bytes += (int64_t)V * 4;
+            }
+        }
+        done += n;
+    }
+    JUNO_CUDA_TRY(cudaStreamSynchronize(st));
+    seq->len = std::max(seq->len, start_pos + n_tokens);
     return JUNO_OK;
 }
 

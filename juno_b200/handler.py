@@ -147,6 +147,15 @@ class B200TransformerHandler:
             return logits, ids
         return logits if want_logits else ids
 
+    def prefill(self, request_id: str, token_ids, start_pos: int = 0, want_logits: bool = False):
+        """Chunked prompt prefill (juno_prefill): positions start_pos.. of one request in passes of up to
+        min(max_batch, 64) positions.  Returns the logits of the last position fed, or None."""
+        toks = np.ascontiguousarray(np.asarray(token_ids, dtype=np.int32))
+        logits = np.empty(self.arch.vocab, dtype=np.float32) if want_logits else None
+        check(self._L.juno_prefill(self.handle, self._seq(request_id), _ptr(toks), len(toks), int(start_pos),
+                                   _ptr(logits) if want_logits else None, None), "juno_prefill")
+        return logits
+
     def decode_greedy(self, request_ids, first_tokens, positions, steps: int) -> np.ndarray:
         """`steps` greedy tokens per request with the loop kept on the device; returns [steps, n] ids."""
         n = len(request_ids)
@@ -193,11 +202,15 @@ class B200InferencePipeline:
         return self.handler.forward_batch(request_ids, tokens, positions)
 
 
-def generate_greedy(pipeline: B200InferencePipeline, request_id: str, prompt, steps: int) -> list:
+def generate_greedy(pipeline: B200InferencePipeline, request_id: str, prompt, steps: int, chunked_prefill: bool = False) -> list:
     """Decode driver of coordinator/.../GenerationLoop.java:306-334: prefill positions 0..P-2 token by token
-    (logits discarded), then greedy steps from position P-1."""
+    (logits discarded), then greedy steps from position P-1.  chunked_prefill feeds the same positions through
+    juno_prefill instead (batched kernels, FP16 operands)."""
     h = pipeline.handler
     P = len(prompt)
-    for p in range(P - 1):
-        h.forward_batch([request_id], [[prompt[p]]], [p], want_logits=False, want_argmax=True)
+    if chunked_prefill and P > 1:
+        h.prefill(request_id, prompt[:-1], 0)
+    else:
+        for p in range(P - 1):
+            h.forward_batch([request_id], [[prompt[p]]], [p], want_logits=False, want_argmax=True)
     return h.decode_greedy([request_id], [prompt[-1]], [P - 1], steps)[:, 0].tolist()

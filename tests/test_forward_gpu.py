@@ -176,3 +176,35 @@ def test_forward_batched_path_matches_oracle(ctx, oracle, n_seq):
     errs = np.sort(np.array(errs))
     assert float(np.median(errs)) < 3e-3 and errs[int(0.85 * len(errs))] < 3e-2, (float(np.median(errs)), errs[-4:])
     h.release_gpu_resources()
+
+
+@pytest.mark.parametrize("max_batch,n_prompt", [(32, 100), (64, 64), (8, 21)])
+def test_chunked_prefill_matches_token_by_token(ctx, oracle, max_batch, n_prompt):
+    """juno_prefill (chunks of min(max_batch, 64) positions through the batched kernels, causal inside a chunk) leaves
+    the sequence where the reference's token-by-token prefill leaves it: the logits of the last prompt position and
+    of the following token-by-token decode steps match the oracle (FP16 operands on the prefill path: 5e-3 on a
+    two-layer model), greedy choice included."""
+    arch = TINY
+    om, h = build_pair(oracle, arch, seed=31, kv_dtype="f16", max_ctx=160, max_batch=max_batch, max_seqs=2, ctx=ctx)
+    rng = np.random.default_rng(7)
+    prompt = rng.integers(0, arch.vocab, n_prompt).tolist()
+    seq = om.new_seq()
+    for p, t in enumerate(prompt):
+        ref = om.forward(seq, t, p)
+    got = h.prefill("p0", prompt, 0, want_logits=True)
+    assert rel_err(got, ref) < 5e-3, rel_err(got, ref)
+    assert int(np.argmax(got)) == oracle.greedy(ref)
+    tok, pos = oracle.greedy(ref), n_prompt
+    for _ in range(6):  # continue token by token on top of the prefilled cache
+        ref = om.forward(seq, tok, pos)
+        got = h.forward_batch(["p0"], [[tok]], [pos])[0]
+        assert rel_err(got, ref) < 5e-3
+        tok, pos = oracle.greedy(ref), pos + 1
+    # a second request, prefilled in two calls (continuation from a non-zero start position)
+    h.prefill("p1", prompt[:10], 0)
+    got2 = h.prefill("p1", prompt[10:], 10, want_logits=True)
+    seq2 = om.new_seq()
+    for p, t in enumerate(prompt):
+        ref2 = om.forward(seq2, t, p)
+    assert rel_err(got2, ref2) < 5e-3
+    h.release_gpu_resources()
