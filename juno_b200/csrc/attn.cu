@@ -283,42 +283,54 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
     merge_splits_group<HD, G>(p, seq, h0, tid, mg_f, mg_L);
 }
 
-// Merges the context splits of one (sequence, head): blockDim = HD threads, one output dimension each.
-// The split weights are computed once in parallel (one split per thread) instead of once per output element.
+// Merges the context splits of one (sequence, head): blockDim = kCombineParts * HD threads.  The split weights are
+// computed once in parallel (one split per thread of the first HD threads); then thread (part, d) adds the splits
+// s = part, part + kCombineParts, ... of output dimension d with all its loads in flight at once, and the parts are
+// added in fixed order.
+constexpr int kCombineParts = 4;
 template <int HD>
-__global__ void attn_combine_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kCombineParts * HD) attn_combine_kernel(const AttnParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x, d = tid % HD, part = tid / HD, lane = tid & 31, warp = tid >> 5;
     const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
     const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h) * p.n_splits * 2;
-    __shared__ float f[64], red[HD / 32], red2[HD / 32];
+    __shared__ float f[64], red[HD / 32], red2[HD / 32], acc_s[kCombineParts][HD];
     float ms = -INFINITY, ls = 0.f;
-    if (d < p.n_splits) {  // n_splits <= 64 <= HD
-        ms = pml[2 * d];
-        ls = pml[2 * d + 1];
+    if (tid < p.n_splits) {  // n_splits <= 64 <= HD
+        ms = pml[2 * tid];
+        ls = pml[2 * tid + 1];
     }
     float M = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if (lane == 0) red[warp] = M;
+    if (lane == 0 && warp < HD / 32) red[warp] = M;
     __syncthreads();
     M = red[0];
 #pragma unroll
     for (int w = 1; w < HD / 32; w++) M = fmaxf(M, red[w]);
     const float fs = (ls > 0.f) ? exp2f(ms - M) : 0.f;  // maxima are kept in the log2 domain
-    if (d < 64) f[d] = fs;
+    if (tid < 64) f[tid] = fs;
     float L = ls * fs;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    if (lane == 0) red2[warp] = L;
+    if (lane == 0 && warp < HD / 32) red2[warp] = L;
     __syncthreads();
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64 / kCombineParts; i++) {
+        const int s = part + i * kCombineParts;
+        if (s < p.n_splits) acc = fmaf(po[(size_t)s * HD + d], f[s], acc);
+    }
+    acc_s[part][d] = acc;
+    __syncthreads();
+    if (part != 0) return;
     L = 0.f;
 #pragma unroll
     for (int w = 0; w < HD / 32; w++) L += red2[w];
-    float acc = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < p.n_splits; s++) acc = fmaf(po[(size_t)s * HD + d], f[s], acc);
+    acc = acc_s[0][d];
+#pragma unroll
+    for (int q = 1; q < kCombineParts; q++) acc += acc_s[q][d];
     const float outv = (L > 0.f) ? acc / L : 0.f;
     p.out[(size_t)(seq * p.n_heads + h) * HD + d] = outv;
     if (p.stage.img) {
@@ -476,9 +488,9 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     }
     dim3 cgrid(a.n_heads, a.n);
     if (hd == 128)
-        launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, st, p);
+        launch_pdl(attn_combine_kernel<128>, cgrid, dim3(kCombineParts * 128), 0, st, p);
     else
-        launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, st, p);
+        launch_pdl(attn_combine_kernel<64>, cgrid, dim3(kCombineParts * 64), 0, st, p);
     JUNO_CUDA_TRY(cudaGetLastError());
     ctx->kernel_launches += 2;
     return JUNO_OK;
