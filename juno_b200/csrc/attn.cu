@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <type_traits>
 
 #include "attn.cuh"
 #include "stage.cuh"
@@ -283,6 +284,264 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
     merge_splits_group<HD, G>(p, seq, h0, tid, mg_f, mg_L);
 }
 
+// ───────────────────────────── tensor-core variant (FP16 pages) ───────────────────────────
+// Same work split as attn_split_kernel (one CTA per kv head, context split and sequence; partials in the same
+// layout), but the scores and the weighted sums run on mma.sync.m16n8k16: a warp takes whole 16-position pages,
+// copies the page's K and V rows (16 x HD halfs each, contiguous in the pool) into its own shared-memory tiles with
+// cp.async (next page in flight while the current one is computed), and per page does
+//   S = Q K^T   : A = q as two FP16 limbs (hi + lo, so the scores keep FP32-level accuracy), B = K via ldmatrix
+//   online softmax on the FP32 fragment (row max / sum across the four lanes that share a row)
+//   O += P V    : A = P (the score fragment re-used as an A fragment, FP16), B = V via ldmatrix.trans
+// Rows of the 16-row MMA tile are the G query heads of the group (G <= 8; rows 8..15 stay zero).
+constexpr int kMmaWarps = 4;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnParams p) {
+    constexpr int LDT = HD + 8;             // tile row stride in halfs (the pad keeps ldmatrix rows on distinct banks)
+    constexpr int TILE = 16 * LDT;          // halfs per K or V tile
+    constexpr int KS = HD / 16, DN = HD / 8;
+    static_assert(G <= 8, "the query heads of a group occupy rows 0..7 of the MMA tile");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *sm_q = reinterpret_cast<__half *>(smem_raw);                 // [2 limbs][8 rows][LDT]
+    __half *sm_kv = sm_q + 2 * 8 * LDT;                                   // [warp][stage 2][K | V][TILE]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r8 = lane >> 2, c = lane & 3;
+    const int len = p.seq_lens[seq];
+    const int chunk = (((len + p.n_splits - 1) / p.n_splits) + 15) & ~15;
+    const int t0 = split * chunk, t1 = min(len, t0 + chunk);
+    const int h0 = kvh * G;
+    float *po = p.part_o + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * HD;   // head stride n_splits*HD
+    float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
+    if (t0 >= t1) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
+        if (tid < G) {
+            pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
+            pml[(size_t)tid * p.n_splits * 2 + 1] = 0.f;
+        }
+        for (int idx = tid; idx < G * HD; idx += kMmaWarps * 32) po[(size_t)(idx / HD) * p.n_splits * HD + (idx % HD)] = 0.f;
+        return;
+    }
+    // q of the group: rotate (rope :1657-1671), scale into the log2 domain, split into two FP16 limbs
+    const float scale = (float)(1.0 / sqrt((double)HD)) * 1.4426950408889634f;
+    for (int idx = tid; idx < 8 * (HD / 2); idx += kMmaWarps * 32) {
+        const int g = idx / (HD / 2), i = idx - g * (HD / 2);
+        float y0 = 0.f, y1 = 0.f;
+        if (g < G) {
+            const float *qp = p.q + (size_t)seq * p.ldq + (size_t)(h0 + g) * HD + 2 * i;
+            float x0 = qp[0], x1 = qp[1];
+            if (p.rope_cs) {
+                const float2 cs = p.rope_cs[seq * (HD / 2) + i];
+                const float a = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+                const float b = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+                x0 = a;
+                x1 = b;
+            }
+            y0 = x0 * scale;
+            y1 = x1 * scale;
+        }
+        const __half h0h = __float2half_rn(y0), h1h = __float2half_rn(y1);
+        sm_q[g * LDT + 2 * i] = h0h;
+        sm_q[g * LDT + 2 * i + 1] = h1h;
+        sm_q[8 * LDT + g * LDT + 2 * i] = __float2half_rn(y0 - __half2float(h0h));
+        sm_q[8 * LDT + g * LDT + 2 * i + 1] = __float2half_rn(y1 - __half2float(h1h));
+    }
+    __syncthreads();
+    // A fragments of q (rows 0..7 only): a0 = (row r8, k 2c..2c+1), a2 = (row r8, k 2c+8..2c+9) of every 16-column step
+    uint32_t qh[KS][2], ql[KS][2];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        qh[ks][0] = *reinterpret_cast<const uint32_t *>(sm_q + r8 * LDT + ks * 16 + 2 * c);
+        qh[ks][1] = *reinterpret_cast<const uint32_t *>(sm_q + r8 * LDT + ks * 16 + 2 * c + 8);
+        ql[ks][0] = *reinterpret_cast<const uint32_t *>(sm_q + 8 * LDT + r8 * LDT + ks * 16 + 2 * c);
+        ql[ks][1] = *reinterpret_cast<const uint32_t *>(sm_q + 8 * LDT + r8 * LDT + ks * 16 + 2 * c + 8);
+    }
+    const int32_t *table = p.table + (size_t)p.slots[seq] * p.max_pages_per_seq;
+    const __half *kbase = static_cast<const __half *>(p.k), *vbase = static_cast<const __half *>(p.v);
+    const size_t page_stride = (size_t)p.n_kv_heads * kPageTokens * HD;
+    const size_t layer_off = (size_t)p.layer * p.n_pages * page_stride + (size_t)kvh * kPageTokens * HD;
+    __half *my_kv = sm_kv + (size_t)warp * 4 * TILE;
+    const uint32_t my_kv_s = (uint32_t)__cvta_generic_to_shared(my_kv);
+    const int pg0 = t0 >> 4, pg1 = (t1 + 15) >> 4;
+    auto issue = [&](int pg, int stage) {  // this warp's copy of page pg into its stage
+        const size_t off = layer_off + (size_t)table[pg] * page_stride;
+        const uint32_t kd = my_kv_s + (uint32_t)(stage * 2 * TILE) * 2u, vd = kd + TILE * 2u;
+#pragma unroll
+        for (int i = 0; i < HD / 16; i++) {  // 16 rows x HD/8 chunks of 16 bytes = 32 lanes x HD/16
+            const int ch = i * 32 + lane, row = ch / (HD / 8), col8 = ch - row * (HD / 8);
+            cp_async_16(kd + (uint32_t)(row * LDT + col8 * 8) * 2u, kbase + off + (size_t)row * HD + col8 * 8);
+            cp_async_16(vd + (uint32_t)(row * LDT + col8 * 8) * 2u, vbase + off + (size_t)row * HD + col8 * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[DN][2], m_run = -INFINITY, l_run = 0.f;  // row r8: output columns dn*8 + 2c, +1; running max; this lane's share of the sum
+#pragma unroll
+    for (int dn = 0; dn < DN; dn++) o[dn][0] = o[dn][1] = 0.f;
+    int pg = pg0 + warp, stage = 0;
+    if (pg < pg1) issue(pg, 0);
+    for (; pg < pg1; pg += kMmaWarps, stage ^= 1) {
+        const bool more = pg + kMmaWarps < pg1;
+        if (more) issue(pg + kMmaWarps, stage ^ 1);
+        if (more)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        __half *kt = my_kv + (size_t)stage * 2 * TILE, *vt = kt + TILE;
+        const int pos0 = pg << 4;
+        if (p.rope_cs && len - 1 >= pos0 && len - 1 < pos0 + 16) {
+            // the position being decoded lives in this page: rotate k, round k and v to FP16, use them and append them
+            const int row = (len - 1) & 15;
+            const size_t off = layer_off + (size_t)table[pg] * page_stride + (size_t)row * HD;
+            __half *kd = static_cast<__half *>(p.kw) + off, *vd = static_cast<__half *>(p.vw) + off;
+            const float *kx = p.knew + (size_t)seq * p.ldkv + kvh * HD, *vx = p.vnew + (size_t)seq * p.ldkv + kvh * HD;
+            for (int i = lane; i < HD / 2; i += 32) {
+                const float2 cs = p.rope_cs[seq * (HD / 2) + i];
+                const float x0 = kx[2 * i], x1 = kx[2 * i + 1];
+                const __half k0 = __float2half_rn(__fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y)));
+                const __half k1 = __float2half_rn(__fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x)));
+                const __half v0 = __float2half_rn(vx[2 * i]), v1 = __float2half_rn(vx[2 * i + 1]);
+                kt[row * LDT + 2 * i] = k0;
+                kt[row * LDT + 2 * i + 1] = k1;
+                vt[row * LDT + 2 * i] = v0;
+                vt[row * LDT + 2 * i + 1] = v1;
+                kd[2 * i] = k0;
+                kd[2 * i + 1] = k1;
+                vd[2 * i] = v0;
+                vd[2 * i + 1] = v1;
+            }
+            __syncwarp();
+        }
+        // rows of V beyond the attended range must not inject NaN/inf through 0 * x: zero them
+        if (pos0 + 16 > t1) {
+            const int first_bad = t1 - pos0;  // 1..15
+            for (int i = lane; i < (16 - first_bad) * (HD / 2); i += 32) {
+                const int row = first_bad + i / (HD / 2), cc = i - (i / (HD / 2)) * (HD / 2);
+                *reinterpret_cast<uint32_t *>(vt + row * LDT + 2 * cc) = 0u;
+            }
+            __syncwarp();
+        }
+        const uint32_t kts = (uint32_t)__cvta_generic_to_shared(kt), vts = (uint32_t)__cvta_generic_to_shared(vt);
+        // scores of the 16 positions: two n-tiles of 8
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int mi = lane >> 3, rr = (lane & 7) + 8 * (mi >> 1), cc = 8 * (mi & 1);
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                uint32_t b[4];  // (pos 0-7, k lo), (pos 0-7, k hi), (pos 8-15, k lo), (pos 8-15, k hi)
+                ldmatrix_x4(b, kts + (uint32_t)(rr * LDT + ks * 16 + cc) * 2u);
+                mma_f16(s0, qh[ks][0], 0u, qh[ks][1], 0u, b[0], b[1]);
+                mma_f16(s1, qh[ks][0], 0u, qh[ks][1], 0u, b[2], b[3]);
+                mma_f16(s0, ql[ks][0], 0u, ql[ks][1], 0u, b[0], b[1]);
+                mma_f16(s1, ql[ks][0], 0u, ql[ks][1], 0u, b[2], b[3]);
+            }
+        }
+        // this lane holds row r8, positions pos0 + 2c, +1 (s0) and pos0 + 8 + 2c, +1 (s1)
+        float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
+        if (pos0 + 16 > t1) {
+            if (pos0 + 2 * c >= t1) sc[0] = -INFINITY;
+            if (pos0 + 2 * c + 1 >= t1) sc[1] = -INFINITY;
+            if (pos0 + 8 + 2 * c >= t1) sc[2] = -INFINITY;
+            if (pos0 + 8 + 2 * c + 1 >= t1) sc[3] = -INFINITY;
+        }
+        float mloc = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
+        mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
+        const float mn = fmaxf(m_run, mloc);  // finite: position pos0 is inside the range
+        const float corr = exp2f(m_run - mn);
+        float pe[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) pe[i] = exp2f(sc[i] - mn);
+        l_run = fmaf(l_run, corr, (pe[0] + pe[1]) + (pe[2] + pe[3]));
+        m_run = mn;
+#pragma unroll
+        for (int dn = 0; dn < DN; dn++) {
+            o[dn][0] *= corr;
+            o[dn][1] *= corr;
+        }
+        const uint32_t pa0 = pack_h2(pe[0], pe[1]), pa2 = pack_h2(pe[2], pe[3]);
+        {
+            const int mi = lane >> 3, rr = (lane & 7) + 8 * (mi & 1), cc = 8 * (mi >> 1);
+#pragma unroll
+            for (int dn = 0; dn < DN; dn += 2) {
+                uint32_t b[4];  // (pos 0-7, dims dn), (pos 8-15, dims dn), (pos 0-7, dims dn+1), (pos 8-15, dims dn+1), transposed
+                ldmatrix_x4_trans(b, vts + (uint32_t)(rr * LDT + dn * 8 + cc) * 2u);
+                float acc0[4] = {o[dn][0], o[dn][1], 0.f, 0.f}, acc1[4] = {o[dn + 1][0], o[dn + 1][1], 0.f, 0.f};
+                mma_f16(acc0, pa0, 0u, pa2, 0u, b[0], b[1]);
+                mma_f16(acc1, pa0, 0u, pa2, 0u, b[2], b[3]);
+                o[dn][0] = acc0[0];
+                o[dn][1] = acc0[1];
+                o[dn + 1][0] = acc1[0];
+                o[dn + 1][1] = acc1[1];
+            }
+        }
+        __syncwarp();  // everybody is done with this stage before it is refilled two pages later
+    }
+    // this lane's share of the row sum -> row sum
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    // merge the four warps through shared memory (the K/V tiles are dead)
+    __syncthreads();
+    float *mg_o = reinterpret_cast<float *>(sm_kv);       // [warp][G][HD]
+    float *mg_m = mg_o + kMmaWarps * G * HD;               // [warp][G]
+    float *mg_l = mg_m + kMmaWarps * G;                    // [warp][G]
+    if (r8 < G) {
+#pragma unroll
+        for (int dn = 0; dn < DN; dn++)
+            *reinterpret_cast<float2 *>(mg_o + ((size_t)warp * G + r8) * HD + dn * 8 + 2 * c) = make_float2(o[dn][0], o[dn][1]);
+        if (c == 0) {
+            mg_m[warp * G + r8] = m_run;
+            mg_l[warp * G + r8] = l_run;
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += kMmaWarps * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) M = fmaxf(M, mg_m[w * G + g]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) {
+            const float lw = mg_l[w * G + g];
+            if (lw > 0.f) {
+                const float f = exp2f(mg_m[w * G + g] - M);
+                L = fmaf(lw, f, L);
+                acc = fmaf(mg_o[((size_t)w * G + g) * HD + d], f, acc);
+            }
+        }
+        po[(size_t)g * p.n_splits * HD + d] = acc;
+        if (d == 0) {
+            pml[(size_t)g * p.n_splits * 2 + 0] = M;  // log2 domain
+            pml[(size_t)g * p.n_splits * 2 + 1] = L;
+        }
+    }
+}
+
 // Merges the context splits of one (sequence, head): blockDim = kCombineParts * HD threads.  The split weights are
 // computed once in parallel (one split per thread of the first HD threads); then thread (part, d) adds the splits
 // s = part, part + kCombineParts, ... of output dimension d with all its loads in flight at once, and the parts are
@@ -418,9 +677,36 @@ int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
     return std::min(s, 64);
 }
 
+static bool attn_use_mma() {
+    static const bool on = [] {
+        const char *e = getenv("JUNO_ATTN_SCALAR");  // JUNO_ATTN_SCALAR=1: the FMA/shuffle kernel also for FP16 pages
+        return !(e && *e == '1');
+    }();
+    return on;
+}
+
+template <int HD, int G>
+static size_t attn_mma_smem() {
+    return ((size_t)2 * 8 * (HD + 8) + (size_t)kMmaWarps * 4 * 16 * (HD + 8)) * sizeof(__half);
+}
+
 template <typename T, int HD, int G>
 static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
     dim3 grid(p.n_kv_heads, p.n_splits, n);
+    if constexpr (std::is_same<T, __half>::value) {
+        if (attn_use_mma() && !p.merge_counters) {
+            const size_t smem = attn_mma_smem<HD, G>();
+            static bool configured[64] = {false};  // per device
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (!configured[dev & 63]) {
+                cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                configured[dev & 63] = true;
+            }
+            launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(kMmaWarps * 32), smem, st, p);
+            return;
+        }
+    }
     launch_pdl(attn_split_kernel<T, HD, G>, grid, dim3(kAttnWarps * 32), 0, st, p);
 }
 
