@@ -305,7 +305,7 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
     }
     // one pass over the weights per group of up to kGemmMaxBatch rows
     if (!c->gemv_scratch.xscale) {
-        cudaError_t e = cudaMalloc((void **)&c->gemv_scratch.xscale, kGemmMaxBatch * sizeof(float));
+        cudaError_t e = cudaMalloc((void **)&c->gemv_scratch.xscale, (kGemmMaxBatch + 4) * sizeof(float));  // + an error word for the tcgen05 kernel
         if (e != cudaSuccess) {
             cudaGetLastError();
             set_error("cudaMalloc of %zu bytes failed: %s", kGemmMaxBatch * sizeof(float), cudaGetErrorString(e));
@@ -314,6 +314,18 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
     }
     for (int b0 = 0; b0 < batch; b0 += kGemmMaxBatch) {
         const int bc = std::min(kGemmMaxBatch, batch - b0);
+        if (gemm_tc_enabled() && gemm_tc_shape_ok(c, (int)m->row_tiles, bc)) {  // tcgen05/TMEM kernel (opt-in)
+            void *pt = c->gemv_scratch.ximg;
+            JUNO_TRY(ensure_device(&pt, &c->gemv_scratch.ximg_bytes, gemm_tc_image_bytes((int)m->cols, bc) + 16));
+            c->gemv_scratch.ximg = (uint8_t *)pt;
+            unsigned *err = reinterpret_cast<unsigned *>(c->gemv_scratch.xscale + kGemmMaxBatch);
+            JUNO_CUDA_TRY(cudaMemsetAsync(err, 0, 4, st));
+            JUNO_TRY(launch_stage_tc(c, x + (size_t)b0 * m->cols, (int)m->cols, (int)m->cols, bc, c->gemv_scratch.ximg,
+                                     c->gemv_scratch.xscale, st));
+            JUNO_TRY(launch_gemm_tc(c, m->dev, m->type, (int)m->rows, (int)m->row_tiles, (int)m->cols, bc, c->gemv_scratch.ximg,
+                                    c->gemv_scratch.xscale, y + (size_t)b0 * m->rows, (int)m->rows, EPI_STORE, err, st));
+            continue;
+        }
         sa.x = x + (size_t)b0 * m->cols;
         sa.batch = bc;
         JUNO_TRY(launch_stage_f16(c, sa, c->gemv_scratch.xscale, st));

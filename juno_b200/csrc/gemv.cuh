@@ -101,6 +101,16 @@ size_t gemm_image_bytes(int K, int batch);
 int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t stream);
 int launch_gemm(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 
+// tcgen05/TMEM version of the batched path (gemm_tc.cu), opt-in with JUNO_GEMM_TCGEN05=1, for matrices with at least
+// sm_count/2 blocks of 128 rows.  It takes its own (chunk-major) FP16 image.
+bool gemm_tc_enabled();
+bool gemm_tc_shape_ok(const juno_ctx *ctx, int row_tiles, int batch);
+int gemm_tc_padded_batch(int batch);
+size_t gemm_tc_image_bytes(int K, int batch);
+int launch_stage_tc(juno_ctx *ctx, const float *x, int ldx, int K, int batch, uint8_t *img, float *xscale, cudaStream_t stream);
+int launch_gemm_tc(juno_ctx *ctx, const uint8_t *w, int type, int rows, int row_tiles, int K, int batch, const uint8_t *ximg,
+                   const float *xscale, float *out, int ld_out, int epi, unsigned *err, cudaStream_t stream);
+
 // Enqueues the product on `stream`.  All pointers are device pointers.
 int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 // Raw-layout / FP32 fallback (one warp per output), used for shapes the tile layout does not cover.
