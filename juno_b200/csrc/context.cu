@@ -311,6 +311,7 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
             set_error("cudaMalloc of %zu bytes failed: %s", kGemmMaxBatch * sizeof(float), cudaGetErrorString(e));
             return JUNO_ERR_OOM;
         }
+        JUNO_CUDA_TRY(cudaMemset(c->gemv_scratch.xscale, 0, (kGemmMaxBatch + 4) * sizeof(float)));
     }
     for (int b0 = 0; b0 < batch; b0 += kGemmMaxBatch) {
         const int bc = std::min(kGemmMaxBatch, batch - b0);
@@ -319,7 +320,6 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
             JUNO_TRY(ensure_device(&pt, &c->gemv_scratch.ximg_bytes, gemm_tc_image_bytes((int)m->cols, bc) + 16));
             c->gemv_scratch.ximg = (uint8_t *)pt;
             unsigned *err = reinterpret_cast<unsigned *>(c->gemv_scratch.xscale + kGemmMaxBatch);
-            JUNO_CUDA_TRY(cudaMemsetAsync(err, 0, 4, st));
             JUNO_TRY(launch_stage_tc(c, x + (size_t)b0 * m->cols, (int)m->cols, (int)m->cols, bc, c->gemv_scratch.ximg,
                                      c->gemv_scratch.xscale, st));
             JUNO_TRY(launch_gemm_tc(c, m->dev, m->type, (int)m->rows, (int)m->row_tiles, (int)m->cols, bc, c->gemv_scratch.ximg,
@@ -367,6 +367,14 @@ int juno_gemv(juno_ctx *c, juno_qmat *m, const float *x_host, int32_t batch, flo
     JUNO_TRY(gemv_on_stream(c, m, c->stage_x, batch, c->stage_y, c->stream));
     JUNO_CUDA_TRY(cudaMemcpyAsync(y_host, c->stage_y, yb, cudaMemcpyDeviceToHost, c->stream));
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (c->gemv_scratch.xscale && batch >= gemm_min_batch()) {  // did a wait inside the tcgen05 kernel give up?
+        unsigned code = 0;
+        JUNO_CUDA_TRY(cudaMemcpy(&code, c->gemv_scratch.xscale + kGemmMaxBatch, 4, cudaMemcpyDeviceToHost));
+        if (code) {
+            set_error("batched tensor-core product gave up waiting (code %u, block %u)", code & 0xffu, code >> 8);
+            return JUNO_ERR_CUDA;
+        }
+    }
     c->h2d_bytes += (int64_t)xb;
     c->d2h_bytes += (int64_t)yb;
     return JUNO_OK;

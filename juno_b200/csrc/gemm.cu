@@ -334,6 +334,8 @@ struct StageF16Params {
     int K, batch, NC;
     uint8_t *img;
     float *xscale;
+    uint8_t *img_tc;  // optional second copy, chunk-major [K/8][N][8] for the tcgen05 kernel (gemm_tc.cu)
+    int N_tc;
 };
 
 __global__ void __launch_bounds__(256) stage_f16_kernel(const StageF16Params p) {
@@ -341,10 +343,17 @@ __global__ void __launch_bounds__(256) stage_f16_kernel(const StageF16Params p) 
     unsigned short *xb = reinterpret_cast<unsigned short *>(p.img);
     const int K = p.K, NC = p.NC;
     __shared__ float red[8], redm[8];
+    unsigned short *xt = reinterpret_cast<unsigned short *>(p.img_tc);
+    auto tc_dst = [&](int i4) {  // where columns i4..i4+3 go in the chunk-major image (see gemm_tc.cu)
+        const int s16 = i4 >> 4, c = (i4 >> 2) & 3, slab = s16 >> 4, t = s16 & 15;
+        const int chunk = slab * 32 + ((t >> 2) * 2 + ((t >> 1) & 1)) * 4 + c;
+        return ((size_t)chunk * p.N_tc + b) * 8 + (size_t)(t & 1) * 4;
+    };
     if (b >= p.batch) {
         for (int i4 = tid * 4; i4 < K; i4 += 256 * 4) {
             const int s16 = i4 >> 4, c = (i4 >> 2) & 3;
-            *reinterpret_cast<uint2 *>(xb + ((size_t)(s16 * NC + b) * 4 + c) * 4) = make_uint2(0u, 0u);
+            if (b < NC) *reinterpret_cast<uint2 *>(xb + ((size_t)(s16 * NC + b) * 4 + c) * 4) = make_uint2(0u, 0u);
+            if (xt && b < p.N_tc) *reinterpret_cast<uint2 *>(xt + tc_dst(i4)) = make_uint2(0u, 0u);
         }
         return;
     }
@@ -419,6 +428,7 @@ __global__ void __launch_bounds__(256) stage_f16_kernel(const StageF16Params p) 
         w.x = (uint32_t)h[0] | ((uint32_t)h[2] << 16);
         w.y = (uint32_t)h[1] | ((uint32_t)h[3] << 16);
         *reinterpret_cast<uint2 *>(xb + ((size_t)(s16 * NC + b) * 4 + c) * 4) = w;
+        if (xt) *reinterpret_cast<uint2 *>(xt + tc_dst(i4)) = w;  // same (x0, x2, x1, x3) packing
     }
 }
 
@@ -435,7 +445,7 @@ int gemm_min_batch() {
 int gemm_padded_batch(int batch) { return (batch + 7) / 8 * 8; }
 size_t gemm_image_bytes(int K, int batch) { return (size_t)K * gemm_padded_batch(batch) * 2; }
 
-int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t st) {
+int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t st, uint8_t *img_tc) {
     JUNO_REQUIRE(a.K > 0 && a.K % 256 == 0 && a.batch >= 1 && a.batch <= kGemmMaxBatch && a.x && a.img && xscale,
                  "stage (fp16): bad arguments (K=%d, batch=%d)", a.K, a.batch);
     JUNO_REQUIRE(a.ldx % 4 == 0, "stage: row stride %d must be a multiple of 4", a.ldx);
@@ -452,8 +462,10 @@ int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStrea
     p.NC = gemm_padded_batch(a.batch);
     p.img = a.img;
     p.xscale = xscale;
+    p.img_tc = img_tc;
+    p.N_tc = gemm_tc_padded_batch(a.batch);
     ProfScope prof(ctx, st, PROF_OTHER, 0);
-    stage_f16_kernel<<<p.NC, 256, 0, st>>>(p);
+    stage_f16_kernel<<<img_tc ? std::max(p.NC, p.N_tc) : p.NC, 256, 0, st>>>(p);
     JUNO_CUDA_TRY(cudaGetLastError());
     ctx->kernel_launches++;
     return JUNO_OK;
@@ -504,6 +516,12 @@ int launch_gemm(juno_ctx *ctx, const GemvArgs &a, cudaStream_t st) {
     for (int s = 0; s < a.nseg; s++) {
         const int t = a.seg[s].type ? a.seg[s].type : a.type;
         JUNO_REQUIRE(t == 12 || t == 14 || t == 8, "gemm: type %d has no tiled kernel", t);
+        if (a.ximg_tc && a.tc_err && a.epi != EPI_RESID_NORM && gemm_tc_enabled() && gemm_tc_shape_ok(ctx, a.seg[s].row_tiles, a.batch)) {
+            JUNO_REQUIRE(a.seg[s].out, "gemm: segment %d has no output", s);
+            JUNO_TRY(launch_gemm_tc(ctx, a.seg[s].w, t, a.seg[s].rows, a.seg[s].row_tiles, a.K, a.batch, a.ximg_tc, a.xscale, a.seg[s].out,
+                                    a.ld_out, a.epi, a.tc_err, st));
+            continue;
+        }
         GemmParams p;
         memset(&p, 0, sizeof(p));
         p.w = a.seg[s].w;

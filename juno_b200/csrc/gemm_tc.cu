@@ -4,7 +4,9 @@
 //   * sixteen warps dequantise: two warps per row tile turn the quantised 16x256 tile into FP16 values in registers
 //     (the arithmetic of gemm.cu) and store them into the slab's A operand in shared memory, laid out as the
 //     canonical K-major "core matrices" of a shared-memory matrix descriptor without swizzle: 8 rows x 16 bytes
-//     contiguous, row groups 128 bytes apart, the two 16-byte K chunks of an MMA 2048 bytes apart;
+//     contiguous, row groups 128 bytes apart, the two 16-byte K chunks of an MMA 2048 bytes apart.  The order of the
+//     256 columns inside a slab is free as long as both operands use it: here a 16-byte chunk is exactly the eight
+//     values ONE lane holds for one row and one 32-column sub-block quarter, so every store is a 128-bit store;
 //   * one thread copies the slab of the activation (one FP16 column per sequence, already stored chunk-major in the
 //     same K order) with one cp.async.bulk;
 //   * one thread issues sixteen tcgen05.mma (M = 128, N = padded batch, K = 16, FP16 in, FP32 accumulate in TMEM) per
@@ -28,7 +30,10 @@ namespace juno {
 
 constexpr int kTcDequantWarps = 16, kTcThreads = (kTcDequantWarps + 1) * 32, kTcStages = 2;
 constexpr int kTcRows = 128;
-constexpr unsigned kTcASlabBytes = kTcRows * 256 * 2;  // 64 KB
+// A chunk (8 K values of all 128 rows) is 2048 bytes; the 32-byte pad between chunks spreads the four chunks a warp
+// writes at once (one per lane % 4) over all shared-memory banks.
+constexpr unsigned kTcChunkStride = kTcRows * 16 + 32;
+constexpr unsigned kTcASlabBytes = 32 * kTcChunkStride;  // 65 KB
 
 struct TcParams {
     const uint8_t *w;
@@ -132,19 +137,25 @@ __device__ __forceinline__ uint32_t tc_h2_dup(float v) {
 }
 __device__ __forceinline__ void tc_sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
 
-// One fragment quadruple (a0, a1, a2, a3) of 16-column step s16 of the slab -> the A operand in shared memory.
-// a0/a2: row r8, MMA k 2c..2c+1 / 2c+8..2c+9; a1/a3: row r8+8.  Chunk 2*s16 holds k 0..7, chunk 2*s16+1 k 8..15.
-__device__ __forceinline__ void tc_store_frag(uint32_t a_row, int s16, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-    const uint32_t base = a_row + (uint32_t)(2 * s16) * (kTcRows * 16u);
-    tc_sts32(base, a0);
-    tc_sts32(base + 8u * 16u, a1);
-    tc_sts32(base + kTcRows * 16u, a2);
-    tc_sts32(base + kTcRows * 16u + 8u * 16u, a3);
+// K order inside a slab (both operands): chunk index = (quarter * 2 + half) * 4 + c, where quarter = 64-column quarter
+// of the slab, half = first / second 32 columns of the quarter, c = lane % 4; the chunk's eight values are columns
+// 64*quarter + 32*half + {4c, 4c+2, 4c+1, 4c+3, 16+4c, 16+4c+2, 16+4c+1, 16+4c+3} -- what lane c holds for one row as
+// the A fragments of two consecutive 16-column steps.  One 128-bit store per (row, chunk).
+__device__ __forceinline__ void tc_sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// a_row = shared address of row r8 of this tile inside chunk 0; rows r8 and r8+8 of chunk (quarter, half, c).
+__device__ __forceinline__ void tc_store_chunk(uint32_t a_row, int quarter, int half, int c, const uint32_t (&lo)[4],
+                                               const uint32_t (&hi)[4]) {
+    const uint32_t base = a_row + (uint32_t)((quarter * 2 + half) * 4 + c) * kTcChunkStride;
+    tc_sts128(base, lo[0], lo[1], lo[2], lo[3]);
+    tc_sts128(base + 8u * 16u, hi[0], hi[1], hi[2], hi[3]);
 }
 
 // Dequantise quarters [q0, q1) of a tile (64 columns each) into the A operand.  a_row = shared address of
 // (row r8 of this tile, byte 4*c) inside chunk 0.
 __device__ __forceinline__ void tc_dequant(const TileRegs<12> &R, int q0, int q1, uint32_t a_row, int lane) {
+    const int c = lane & 3;
     const float d_r = f16bits_to_f32(R.dm0), m_r = f16bits_to_f32(R.dm0 >> 16);
     const float d_q = f16bits_to_f32(R.dm1), m_q = f16bits_to_f32(R.dm1 >> 16);
     // (scale, -min) of sub-blocks 2c, 2c+1 for rows r8 / r8+8, packed as FP16 pairs
@@ -183,14 +194,18 @@ __device__ __forceinline__ void tc_dequant(const TileRegs<12> &R, int q0, int q1
             ha[i] = tc_h2_fma(tc_h2_sub(ha[i], K), s_hi, m_hi);
             hb[i] = tc_h2_fma(tc_h2_sub(hb[i], K), s_hi, m_hi);
         }
-        tc_store_frag(a_row, 4 * g + 0, la[0], la[2], lb[0], lb[2]);
-        tc_store_frag(a_row, 4 * g + 1, la[1], la[3], lb[1], lb[3]);
-        tc_store_frag(a_row, 4 * g + 2, ha[0], ha[2], hb[0], hb[2]);
-        tc_store_frag(a_row, 4 * g + 3, ha[1], ha[3], hb[1], hb[3]);
+        // words x, y (index 0, 1) are row r8, words z, w (2, 3) row r8+8; low nibbles = first 32 columns of the quarter
+        {
+            const uint32_t r_lo[4] = {la[0], lb[0], la[1], lb[1]}, q_lo[4] = {la[2], lb[2], la[3], lb[3]};
+            const uint32_t r_hi[4] = {ha[0], hb[0], ha[1], hb[1]}, q_hi[4] = {ha[2], hb[2], ha[3], hb[3]};
+            tc_store_chunk(a_row, g, 0, c, r_lo, q_lo);
+            tc_store_chunk(a_row, g, 1, c, r_hi, q_hi);
+        }
     }
 }
 
 __device__ __forceinline__ void tc_dequant(const TileRegs<14> &R, int q0, int q1, uint32_t a_row, int lane) {
+    const int c = lane & 3;
     const float d_r = f16bits_to_f32(R.d01), d_q = f16bits_to_f32(R.d01 >> 16);
     uint32_t s_r[4], s_q[4];
 #pragma unroll
@@ -216,19 +231,26 @@ __device__ __forceinline__ void tc_dequant(const TileRegs<14> &R, int q0, int q1
         V_q[2] = and_or(WB_q, NIB, (H_q << 2) & HI);
         V_q[3] = and_or(WB_q >> 4, NIB, (H_q << 4) & HI);
         const int src = (lane & ~3) | m;
+        uint32_t ar[4][2], aq[4][2];  // [16-column step k of the quarter][fragment k 2c.. | 2c+8..] for rows r8 / r8+8
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const uint32_t sr = __shfl_sync(0xffffffffu, s_r[k], src), sq = __shfl_sync(0xffffffffu, s_q[k], src);
-            const uint32_t a0 = tc_h2_mul(tc_h2_sub(__byte_perm(V_r[k], 0x64646464u, 0x4140), 0x64206420u), sr);
-            const uint32_t a2 = tc_h2_mul(tc_h2_sub(__byte_perm(V_r[k], 0x64646464u, 0x4342), 0x64206420u), sr);
-            const uint32_t a1 = tc_h2_mul(tc_h2_sub(__byte_perm(V_q[k], 0x64646464u, 0x4140), 0x64206420u), sq);
-            const uint32_t a3 = tc_h2_mul(tc_h2_sub(__byte_perm(V_q[k], 0x64646464u, 0x4342), 0x64206420u), sq);
-            tc_store_frag(a_row, 4 * m + k, a0, a1, a2, a3);
+            ar[k][0] = tc_h2_mul(tc_h2_sub(__byte_perm(V_r[k], 0x64646464u, 0x4140), 0x64206420u), sr);
+            ar[k][1] = tc_h2_mul(tc_h2_sub(__byte_perm(V_r[k], 0x64646464u, 0x4342), 0x64206420u), sr);
+            aq[k][0] = tc_h2_mul(tc_h2_sub(__byte_perm(V_q[k], 0x64646464u, 0x4140), 0x64206420u), sq);
+            aq[k][1] = tc_h2_mul(tc_h2_sub(__byte_perm(V_q[k], 0x64646464u, 0x4342), 0x64206420u), sq);
+        }
+        {
+            const uint32_t r0[4] = {ar[0][0], ar[0][1], ar[1][0], ar[1][1]}, q0v[4] = {aq[0][0], aq[0][1], aq[1][0], aq[1][1]};
+            const uint32_t r1[4] = {ar[2][0], ar[2][1], ar[3][0], ar[3][1]}, q1v[4] = {aq[2][0], aq[2][1], aq[3][0], aq[3][1]};
+            tc_store_chunk(a_row, m, 0, c, r0, q0v);
+            tc_store_chunk(a_row, m, 1, c, r1, q1v);
         }
     }
 }
 
-__device__ __forceinline__ void tc_dequant(const TileRegs<8> &R, int q0, int q1, uint32_t a_row, int /*lane*/) {
+__device__ __forceinline__ void tc_dequant(const TileRegs<8> &R, int q0, int q1, uint32_t a_row, int lane) {
+    const int c = lane & 3;
     const uint32_t dr[4] = {R.d0.x, R.d0.y, R.d0.z, R.d0.w}, dq[4] = {R.d1.x, R.d1.y, R.d1.z, R.d1.w};
     uint32_t SGN = 0x80808080u;
     asm volatile("" : "+r"(SGN));
@@ -245,9 +267,61 @@ __device__ __forceinline__ void tc_dequant(const TileRegs<8> &R, int q0, int q1,
             a[i][0] = tc_h2_mul(tc_h2_sub(__byte_perm(w4[i], 0x64646464u, 0x4240), 0x64806480u), d);
             a[i][1] = tc_h2_mul(tc_h2_sub(__byte_perm(w4[i], 0x64646464u, 0x4341), 0x64806480u), d);
         }
-        tc_store_frag(a_row, 2 * j, a[0][0], a[2][0], a[0][1], a[2][1]);
-        tc_store_frag(a_row, 2 * j + 1, a[1][0], a[3][0], a[1][1], a[3][1]);
+        // block j = 32 columns = half (j & 1) of quarter j >> 1; words x, y: row r8; z, w: row r8+8
+        {
+            const uint32_t rr[4] = {a[0][0], a[0][1], a[1][0], a[1][1]}, qq[4] = {a[2][0], a[2][1], a[3][0], a[3][1]};
+            tc_store_chunk(a_row, j >> 1, j & 1, c, rr, qq);
+        }
     }
+}
+
+// The half of a tile one warp works on (quarters 2h, 2h+1): only those registers of TileRegs are loaded.
+__device__ __forceinline__ void tc_load_half(TileRegs<12> &r, const uint8_t *tile, int lane, int h) {
+    const uint32_t *t1 = reinterpret_cast<const uint32_t *>(tile);
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile + kQ4KQsOff);
+    const int r8 = lane >> 2, c = lane & 3;
+    r.dm0 = __ldcs(t1 + r8);
+    r.dm1 = __ldcs(t1 + r8 + 8);
+    r.sm0 = __ldcs(t1 + 16 + r8 * 4 + c);
+    r.sm1 = __ldcs(t1 + 16 + (r8 + 8) * 4 + c);
+    if (h == 0) {  // static register indices: a runtime index would push the tile into local memory
+        r.q[0] = __ldcs(t4 + 0 * 32 + lane);
+        r.q[1] = __ldcs(t4 + 1 * 32 + lane);
+    } else {
+        r.q[2] = __ldcs(t4 + 2 * 32 + lane);
+        r.q[3] = __ldcs(t4 + 3 * 32 + lane);
+    }
+}
+__device__ __forceinline__ void tc_load_half(TileRegs<14> &r, const uint8_t *tile, int lane, int h) {
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
+    const int r8 = lane >> 2, c = lane & 3;
+    if (h == 0) {
+        r.ql[0] = __ldcs(t4 + 0 * 32 + lane);
+        r.ql[1] = __ldcs(t4 + 1 * 32 + lane);
+        r.qh[0] = __ldcs(t4 + 128 + lane);
+    } else {
+        r.ql[2] = __ldcs(t4 + 2 * 32 + lane);
+        r.ql[3] = __ldcs(t4 + 3 * 32 + lane);
+        r.qh[1] = __ldcs(t4 + 128 + 32 + lane);
+    }
+    const uint32_t *sc = reinterpret_cast<const uint32_t *>(tile + 3072);
+    r.sc0 = __ldcs(sc + r8 * 4 + c);
+    r.sc1 = __ldcs(sc + (r8 + 8) * 4 + c);
+    const unsigned short *d = reinterpret_cast<const unsigned short *>(tile + 3328);
+    r.d01 = (uint32_t)__ldcs(d + r8) | ((uint32_t)__ldcs(d + r8 + 8) << 16);
+}
+__device__ __forceinline__ void tc_load_half(TileRegs<8> &r, const uint8_t *tile, int lane, int h) {
+    const uint4 *t4 = reinterpret_cast<const uint4 *>(tile);
+    const int r8 = lane >> 2;
+    if (h == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) r.q[j] = __ldcs(t4 + j * 32 + lane);
+    } else {
+#pragma unroll
+        for (int j = 4; j < 8; j++) r.q[j] = __ldcs(t4 + j * 32 + lane);
+    }
+    r.d0 = __ldcs(t4 + 256 + r8);
+    r.d1 = __ldcs(t4 + 256 + r8 + 8);
 }
 
 template <int TYPE>
@@ -261,6 +335,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
     const uint32_t bars = tc_smem_u32(tail);  // full[2], free[2], acc_ready, acc_free
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail + 64);
     volatile unsigned *err_s = reinterpret_cast<volatile unsigned *>(tail + 72);
+    float *xs_s = reinterpret_cast<float *>(tail + 128);  // the activation's per-row factors, read once
+    if (tid < kGemmMaxBatch) xs_s[tid] = (tid < p.batch && p.xscale) ? p.xscale[tid] : 1.f;
     const uint32_t full0 = bars, free0 = bars + 16, acc_ready = bars + 32, acc_free = bars + 40;
     const int tmem_cols = p.N <= 32 ? 32 : 64;
     if (tid == 0) {
@@ -295,10 +371,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
             const int R = task * 8 + rt_local;
             const bool have = R < p.total_rt;
             const uint8_t *wrow = p.w + (size_t)(have ? R : 0) * p.nb * tile_bytes(TYPE);
-            TileRegs<TYPE> bufA, bufB;
-            if (have) load_tile<TYPE>(bufA, wrow, lane);
-            const int r8 = lane >> 2, c = lane & 3;
-            const uint32_t row_off = (uint32_t)(rt_local * 16 + r8) * 16u + (uint32_t)c * 4u;
+            TileRegs<TYPE> buf0, buf1, buf2;  // this warp's half of the tiles sb, sb+1, sb+2 (two tiles in flight)
+            const int h = warp & 1;
+            const size_t tb = (size_t)tile_bytes(TYPE);
+            if (have) tc_load_half(buf0, wrow, lane, h);
+            if (have && p.nb > 1) tc_load_half(buf1, wrow + tb, lane, h);
+            const int r8 = lane >> 2;
+            const uint32_t row_off = (uint32_t)(rt_local * 16 + r8) * 16u;
             unsigned my_it = it;
             for (int sb = 0; sb < p.nb; sb++, my_it++) {
                 const unsigned stage = my_it % kTcStages, use = my_it / kTcStages;
@@ -309,15 +388,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
                     tc_bulk_g2s(b_s + stage * b_slab_bytes, p.ximg + (size_t)sb * b_slab_bytes, b_slab_bytes, full0 + 8 * stage);
                 }
                 const uint32_t a_row = a_s + stage * kTcASlabBytes + row_off;
-                if (sb & 1) {
-                    if (have && sb + 1 < p.nb) load_tile<TYPE>(bufA, wrow + (size_t)(sb + 1) * tile_bytes(TYPE), lane);
-                    if (have) tc_dequant(bufB, q0, q1, a_row, lane);
+                const bool pre = have && sb + 2 < p.nb;
+                const uint8_t *nxt = wrow + (size_t)(sb + 2) * tb;
+                const int which = sb % 3;
+                if (which == 0) {
+                    if (pre) tc_load_half(buf2, nxt, lane, h);
+                    if (have) tc_dequant(buf0, q0, q1, a_row, lane);
+                } else if (which == 1) {
+                    if (pre) tc_load_half(buf0, nxt, lane, h);
+                    if (have) tc_dequant(buf1, q0, q1, a_row, lane);
                 } else {
-                    if (have && sb + 1 < p.nb) load_tile<TYPE>(bufB, wrow + (size_t)(sb + 1) * tile_bytes(TYPE), lane);
-                    if (have) tc_dequant(bufA, q0, q1, a_row, lane);
+                    if (pre) tc_load_half(buf1, nxt, lane, h);
+                    if (have) tc_dequant(buf2, q0, q1, a_row, lane);
                 }
                 if (!have) {  // rows past the end of the matrix: zeros
-                    for (int s16 = q0 * 4; s16 < q1 * 4; s16++) tc_store_frag(a_row, s16, 0u, 0u, 0u, 0u);
+                    const uint32_t z[4] = {0u, 0u, 0u, 0u};
+                    for (int q = q0; q < q1; q++) {
+                        tc_store_chunk(a_row, q, 0, lane & 3, z, z);
+                        tc_store_chunk(a_row, q, 1, lane & 3, z, z);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> visible to the tensor core
                 __syncwarp();
@@ -335,7 +424,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
                 if (ok) {
 #pragma unroll 4
                     for (int s16 = 0; s16 < 16; s16++) {
-                        const uint64_t ad = tc_smem_desc(a_s + stage * kTcASlabBytes + (uint32_t)(2 * s16) * (kTcRows * 16u), kTcRows * 16u, 128u);
+                        const uint64_t ad = tc_smem_desc(a_s + stage * kTcASlabBytes + (uint32_t)(2 * s16) * kTcChunkStride, kTcChunkStride, 128u);
                         const uint64_t bd = tc_smem_desc(b_s + stage * b_slab_bytes + (uint32_t)(2 * s16) * ((uint32_t)p.N * 16u), (uint32_t)p.N * 16u, 128u);
                         tc_mma_f16(tmem_base, ad, bd, idesc, (sb > 0 || s16 > 0) ? 1u : 0u);
                     }
@@ -358,8 +447,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
                 for (int j = 0; j < 16; j++) {
                     const int b = c0 + j;
                     float y = __uint_as_float(v[j]);
-                    const float sc = (b < p.batch && p.xscale) ? p.xscale[b] : 1.f;
-                    y *= sc;
+                    y *= xs_s[b];
                     if (p.epi == EPI_SILU_PAIR) {
                         const float up = __shfl_down_sync(0xffffffffu, y, 8);  // rows 8..15 of a tile are the up rows
                         const int orow = (task * 8 + (row_in_cta >> 4)) * 8 + (row_in_cta & 7);
@@ -384,9 +472,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcParams p
 }
 
 // ───────────────────────────── chunk-major FP16 staging ────────────────────────────────────
-// Image [K/8][N][8]: the eight halfs of chunk ch of sequence b are MMA k indices 0..7 (even chunk) or 8..15 (odd
-// chunk) of 16-column group ch/2, in the feed order of the weight fragments (layout.cuh): fragment k 2c, 2c+1 are
-// columns 4c, 4c+2 of the group; fragment k 2c+8, 2c+9 are columns 4c+1, 4c+3.
+// Image [K/8][N][8] in the slab K order described above (tc_store_chunk): the four consecutive columns 16*s16 + 4c ..
+// + 3 of a sequence go, as (x0, x2, x1, x3), to half of the chunk (quarter, half, c) with quarter = (s16 % 16) / 4,
+// half = (s16 / 2) % 2, and to its first or second 8 bytes for even / odd s16.
 struct StageTcParams {
     const float *x;
     int ldx;
@@ -400,12 +488,13 @@ __global__ void __launch_bounds__(256) stage_tc_kernel(const StageTcParams p) {
     unsigned short *img = reinterpret_cast<unsigned short *>(p.img);
     const int K = p.K, N = p.N;
     __shared__ float redm[8];
+    auto chunk_of = [&](int i4) {  // destination (in halfs) of columns i4..i4+3
+        const int s16 = i4 >> 4, c = (i4 >> 2) & 3, slab = s16 >> 4, t = s16 & 15;
+        const int chunk = slab * 32 + ((t >> 2) * 2 + ((t >> 1) & 1)) * 4 + c;
+        return ((size_t)chunk * N + b) * 8 + (size_t)(t & 1) * 4;
+    };
     if (b >= p.batch) {
-        for (int i4 = tid * 4; i4 < K; i4 += 256 * 4) {
-            const int s16 = i4 >> 4, c = (i4 >> 2) & 3;
-            *reinterpret_cast<uint32_t *>(img + ((size_t)(2 * s16) * N + b) * 8 + 2 * c) = 0u;
-            *reinterpret_cast<uint32_t *>(img + ((size_t)(2 * s16 + 1) * N + b) * 8 + 2 * c) = 0u;
-        }
+        for (int i4 = tid * 4; i4 < K; i4 += 256 * 4) *reinterpret_cast<uint2 *>(img + chunk_of(i4)) = make_uint2(0u, 0u);
         return;
     }
     const float *xrow = p.x + (size_t)b * p.ldx;
@@ -428,27 +517,34 @@ __global__ void __launch_bounds__(256) stage_tc_kernel(const StageTcParams p) {
     if (tid == 0) p.xscale[b] = up;
     for (int i4 = tid * 4; i4 < K; i4 += 256 * 4) {
         const float4 xv = *reinterpret_cast<const float4 *>(xrow + i4);
-        const int s16 = i4 >> 4, c = (i4 >> 2) & 3;
-        const __half2 lo = __floats2half2_rn(xv.x * down, xv.z * down);  // columns 4c, 4c+2 -> k 2c, 2c+1
-        const __half2 hi = __floats2half2_rn(xv.y * down, xv.w * down);  // columns 4c+1, 4c+3 -> k 2c+8, 2c+9
-        *reinterpret_cast<__half2 *>(img + ((size_t)(2 * s16) * N + b) * 8 + 2 * c) = lo;
-        *reinterpret_cast<__half2 *>(img + ((size_t)(2 * s16 + 1) * N + b) * 8 + 2 * c) = hi;
+        const __half2 lo = __floats2half2_rn(xv.x * down, xv.z * down);  // columns 4c, 4c+2
+        const __half2 hi = __floats2half2_rn(xv.y * down, xv.w * down);  // columns 4c+1, 4c+3
+        uint2 w;
+        w.x = *reinterpret_cast<const uint32_t *>(&lo);
+        w.y = *reinterpret_cast<const uint32_t *>(&hi);
+        *reinterpret_cast<uint2 *>(img + chunk_of(i4)) = w;
     }
 }
 
 // ───────────────────────────── host ───────────────────────────────────────────────────────
 bool gemm_tc_enabled() {
     static const bool on = [] {
-        const char *e = getenv("JUNO_GEMM_TCGEN05");
-        return e && *e == '1';
+        const char *e = getenv("JUNO_GEMM_TCGEN05");  // JUNO_GEMM_TCGEN05=0: keep every batched product on mma.sync
+        return !(e && *e == '0');
     }();
     return on;
 }
 int gemm_tc_padded_batch(int batch) { return (batch + 15) / 16 * 16; }
 size_t gemm_tc_image_bytes(int K, int batch) { return (size_t)K * gemm_tc_padded_batch(batch) * 2; }
-// Shapes this kernel takes: enough 128-row blocks to occupy the GPU, batch 9..64.
+// Shapes this kernel takes: enough 128-row blocks to occupy the GPU, and a batch from which it measured faster than the
+// mma.sync kernel (its time hardly depends on the batch: 185-209 us on 128256 x 4096 Q4_K for 16-64 sequences, against
+// 138-294 us).
 bool gemm_tc_shape_ok(const juno_ctx *ctx, int row_tiles, int batch) {
-    return batch >= 9 && batch <= kGemmMaxBatch && (row_tiles + 7) / 8 >= ctx->sm_count / 2;
+    static const int min_batch = [] {
+        const char *e = getenv("JUNO_GEMM_TC_MIN_BATCH");
+        return (e && *e) ? atoi(e) : 48;
+    }();
+    return batch >= min_batch && batch <= kGemmMaxBatch && (row_tiles + 7) / 8 >= ctx->sm_count / 2;
 }
 
 int launch_stage_tc(juno_ctx *ctx, const float *x, int ldx, int K, int batch, uint8_t *img, float *xscale, cudaStream_t st) {
@@ -471,7 +567,7 @@ int launch_stage_tc(juno_ctx *ctx, const float *x, int ldx, int K, int batch, ui
 
 template <int TYPE>
 static int gemm_tc_launch_type(juno_ctx *ctx, const TcParams &p, cudaStream_t st) {
-    const size_t smem = (size_t)kTcStages * kTcASlabBytes + (size_t)kTcStages * p.N * 512 + 128;
+    const size_t smem = (size_t)kTcStages * kTcASlabBytes + (size_t)kTcStages * p.N * 512 + 128 + kGemmMaxBatch * 4;
     static std::mutex mu;
     static bool configured[16] = {false};
     {

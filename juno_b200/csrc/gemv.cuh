@@ -80,6 +80,10 @@ struct GemvArgs {
     int img_next_K = 0;
     // batched path (launch_gemm): ximg is an FP16 image (launch_stage_f16) and xscale its per-row factors
     const float *xscale = nullptr;
+    // optional: the same activation in the chunk-major layout of the tcgen05 kernel, and the device word that kernel
+    // reports a given-up wait in; segments with enough row tiles then run on it (gemm_tc_shape_ok)
+    const uint8_t *ximg_tc = nullptr;
+    unsigned *tc_err = nullptr;
 };
 // Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
 int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
@@ -98,7 +102,7 @@ constexpr int kGemmMaxBatch = 64;
 int gemm_min_batch();               // smallest batch routed to the batched path (JUNO_GEMM_MIN_BATCH, default 9)
 int gemm_padded_batch(int batch);   // image columns: batch rounded up to a multiple of 8
 size_t gemm_image_bytes(int K, int batch);
-int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t stream);
+int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t stream, uint8_t *img_tc = nullptr);
 int launch_gemm(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 
 // tcgen05/TMEM version of the batched path (gemm_tc.cu), opt-in with JUNO_GEMM_TCGEN05=1, for matrices with at least

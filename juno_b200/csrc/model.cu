@@ -212,6 +212,9 @@ struct juno_model {
     // activations
     float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *ss = nullptr;
     float *hdn = nullptr, *xsc = nullptr;  // batched path: silu(gate)*up rows; per-row factors of the three FP16 images
+    uint8_t *img_h_tc = nullptr;            // batched path: the hidden-size activation again, chunk-major for the tcgen05 kernel
+    unsigned *tc_err = nullptr;             // device word: a wait inside the tcgen05 kernel gave up
+    bool tc_used = false;                   // the batched path ran since the word was last read
     uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
@@ -299,7 +302,7 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->hdn, m->xsc, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->hdn, m->xsc, m->img_h_tc, m->tc_err, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
                     m->attn_scratch, m->attn_counters, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
@@ -522,6 +525,9 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->img_i, std::max(stage_image_bytes(c, m->inter_loc, B), gemm_image_bytes(m->inter_loc, Bg))));
     JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
     JUNO_TRY(dev_alloc((void **)&m->xsc, (size_t)3 * B * 4));
+    JUNO_TRY(dev_alloc((void **)&m->img_h_tc, gemm_tc_image_bytes(H, Bg)));
+    JUNO_TRY(dev_alloc((void **)&m->tc_err, 4));
+    JUNO_CUDA_TRY(cudaMemset(m->tc_err, 0, 4));
     JUNO_TRY(dev_alloc((void **)&m->logits_loc, (size_t)B * m->vocab_loc * 4));
     if (m->vocab_sharded) {
         JUNO_TRY(dev_alloc((void **)&m->logits_gather, (size_t)B * f.vocab * 4));
@@ -647,6 +653,7 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
     const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
     float *sc_h = m->xsc, *sc_att = m->xsc + B, *sc_i = m->xsc + 2 * B;
+    m->tc_used = true;
     auto stage = [&](int mode, const float *x, int ldx, const float *add, float *x_out, const float *normw, int K, uint8_t *img,
                      float *sc) {
         StageArgs a;
@@ -660,7 +667,7 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
         a.K = K;
         a.batch = n;
         a.img = img;
-        return launch_stage_f16(c, a, sc, st);
+        return launch_stage_f16(c, a, sc, st, img == m->img_h ? m->img_h_tc : nullptr);
     };
     auto product = [&](juno_qmat *const *mats, float *const *outs, int count, int epi, int ld_out, const uint8_t *img,
                        const float *sc) {
@@ -670,6 +677,10 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
         a.xscale = sc;
         a.epi = epi;
         a.ld_out = ld_out;
+        if (img == m->img_h) {
+            a.ximg_tc = m->img_h_tc;
+            a.tc_err = m->tc_err;
+        }
         return gemv_group(m, mats, outs, count, a, st);
     };
     JUNO_TRY(stage(STAGE_RMSNORM, m->x[0], H, nullptr, nullptr, m->layers[0].attn_norm, H, m->img_h, sc_h));
@@ -949,6 +960,15 @@ static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
 
 // After a stream synchronise: did the last step kernel give up on a wait?
 static int step_check(juno_model *m) {
+    if (m->tc_err && m->tc_used) {
+        m->tc_used = false;
+        unsigned code = 0;
+        if (cudaMemcpy(&code, m->tc_err, 4, cudaMemcpyDeviceToHost) == cudaSuccess && code) {
+            cudaMemset(m->tc_err, 0, 4);
+            set_error("batched tensor-core product gave up waiting (code %u, block %u)", code & 0xffu, code >> 8);
+            return JUNO_ERR_CUDA;
+        }
+    }
     if (!m->last_plan) return JUNO_OK;
     const unsigned code = step_plan_error(*m->last_plan);
     if (!code) return JUNO_OK;
@@ -1113,6 +1133,7 @@ int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t
         done += n;
     }
     JUNO_CUDA_TRY(cudaStreamSynchronize(st));
+    JUNO_TRY(step_check(m));
     seq->len = std::max(seq->len, start_pos + n_tokens);
     return JUNO_OK;
 }
