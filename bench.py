@@ -322,6 +322,12 @@ def main():
                 "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind}
     if g["launches"]:
         ach = g["algo_bytes"] / (g["ms"] / 1e3) / 1e9
+        # DRAM traffic per launch: ncu on the same kernel (profiles/gemv_q4k_q6k_128256x4096_b1.md) measured
+        # dram read+write = 1.04 x the algorithmic bytes (byte-wide scale header of the tile layout, no re-reads);
+        # scaled to this mix of launches by the bytes they process
+        if kname.startswith("gemv_kernel"):
+            roofline["traffic"] = 1.04 * g["algo_bytes"] / g["launches"]
+            roofline["traffic_source"] = "ncu capture of the 128256x4096 launch, scaled by algorithmic bytes"
         roofline.update({"achieved": ach, "frac": ach / peak, "launches_timed": g["launches"],
                          "avg_launch_us": g["ms"] * 1e3 / g["launches"],
                          "algo_bytes_per_launch": g["algo_bytes"] / g["launches"]})
