@@ -120,6 +120,43 @@ __device__ __forceinline__ const uint8_t *tile_addr(const GemvParams &p, int R, 
     return p.w[s] + ((size_t)(R - p.rt_begin[s]) * p.nb + sb) * (size_t)tile_bytes(type);
 }
 
+// Hint: bring [a, a+bytes) into the L2 (16-byte aligned, bytes a multiple of 16).  No completion, no dependency.
+__device__ __forceinline__ void l2_prefetch_range(const uint8_t *a, unsigned bytes) {
+    for (unsigned o = 0; o < bytes; o += 32768u) {
+        const unsigned n = min(32768u, bytes - o);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a + o), "r"(n) : "memory");
+    }
+}
+
+template <int TYPE>
+__device__ __forceinline__ void gemv_prefetch_own(const GemvParams &p, int tid) {
+    // own weights: the row tiles of CTA tasks blockIdx.x, blockIdx.x + grid, ... below pf_rt, one row tile per thread
+    for (int i = tid;; i += kThreads) {
+        const int r = i / p.groups, g = i - r * p.groups;
+        const int ct = blockIdx.x + r * gridDim.x;
+        if (ct >= p.n_ctasks || ct * p.groups >= p.pf_rt) break;
+        const int R = ct * p.groups + g;
+        if (R < p.pf_rt) {
+            int ty;
+            const uint8_t *a = tile_addr<TYPE>(p, R, 0, ty);
+            l2_prefetch_range(a, (unsigned)(p.nb * tile_bytes(ty)));
+        }
+    }
+}
+
+// The products that follow: each CTA one slice per range, issued by the first lane of warps 1..3.
+__device__ __forceinline__ void gemv_prefetch_next(const GemvParams &p, int tid) {
+    if ((tid & 31) == 0 && tid >= 32 && tid < 128) {
+        const int r = (tid >> 5) - 1;
+        const unsigned bytes = p.pfx_bytes[r];
+        if (bytes) {
+            const unsigned per = (((bytes + gridDim.x - 1) / gridDim.x) + 15u) & ~15u;
+            const unsigned long long off = (unsigned long long)blockIdx.x * per;
+            if (off < bytes) l2_prefetch_range(p.pfx[r] + off, min(per, (unsigned)(bytes - off)));
+        }
+    }
+}
+
 template <int TYPE, int NB>
 __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     constexpr int NC = 3 * NB, NT = (NC + 7) / 8, LD = 8 * NT;
@@ -142,6 +179,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     int ct = blockIdx.x;
     if (tid == 0) next_task[0] = gridDim.x + (int)atomicAdd(p.counters, 1u);
 
+    if (p.pf_rt > 0) gemv_prefetch_own<TYPE>(p, tid);
+    if (p.pfx_bytes[0] && !p.pf_late) gemv_prefetch_next(p, tid);
     // Issue the first tile's loads before touching x: the weights do not depend on the producer of x.
     TileRegs<TYPE> bufA, bufB;
     int R = ct * p.groups + grp;
@@ -332,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
         have = nhave;
         it++;
     }
+    if (p.pfx_bytes[0] && p.pf_late) gemv_prefetch_next(p, tid);  // HBM goes idle as the CTAs run out of tasks
     // the last CTA to leave zeroes the counters for the next launch that uses this pair
     if (tid == 0) {
         const unsigned done = atomicAdd(p.counters + 1, 1u);
@@ -473,6 +513,15 @@ static int gemv_check_args(const GemvArgs &a) {
     return JUNO_OK;
 }
 
+size_t gemv_l2_prefetch_bytes() {
+    static const size_t v = [] {
+        const char *e = getenv("JUNO_L2_PREFETCH_MB");
+        const long mb = e ? atol(e) : 0;  // measured: no gain at 8-16 MB, 2-6 % slower at 48-96 MB (the step is not latency bound on HBM)
+        return (size_t)std::max(0L, std::min(mb, 96L)) << 20;
+    }();
+    return v;
+}
+
 int gemv_fill_params(juno_ctx *ctx, const GemvArgs &a, int b0, int bc, int chunk, int kin, int tpt, int groups, int n_ctasks,
                      GemvParams *out) {
     JUNO_TRY(gemv_check_args(a));
@@ -512,6 +561,23 @@ int gemv_fill_params(juno_ctx *ctx, const GemvArgs &a, int b0, int bc, int chunk
     p.normw_next = a.normw_next;
     p.ss_out = a.ss_out ? a.ss_out + (size_t)b0 * a.ss_out_ld : nullptr;
     p.ss_out_ld = a.ss_out_ld;
+    if (b0 == 0) {
+        const size_t budget = gemv_l2_prefetch_bytes();
+        int max_tb = 0;
+        for (int s = 0; s < a.nseg; s++) max_tb = std::max(max_tb, tile_bytes(p.seg_type[s]));
+        static const int mode = [] {
+            const char *e = getenv("JUNO_L2_PREFETCH_MODE");  // 1 own weights, 2 next at entry, 4 next at exit
+            return e ? atoi(e) : 7;
+        }();
+        if (budget && max_tb && (mode & 1)) p.pf_rt = (int)std::min<size_t>((size_t)p.total_rt, budget / ((size_t)p.nb * max_tb));
+        for (int r = 0, k = 0; r < 3 && budget; r++) {
+            if (!a.pf_next[r] || !a.pf_next_bytes[r] || !(mode & (a.pf_next_late ? 4 : 2))) continue;
+            p.pfx[k] = a.pf_next[r];
+            p.pfx_bytes[k] = (unsigned)std::min<size_t>(a.pf_next_bytes[r] & ~(size_t)15, budget);
+            k++;
+        }
+        p.pf_late = a.pf_next_late;
+    }
     if (a.img_next) {
         // the next product chunks the batch by ITS K; rows b0.. of this launch map to rows b0.. of that image
         p.img_next = stage_image_desc(ctx, a.img_next, a.img_next_K, a.batch);

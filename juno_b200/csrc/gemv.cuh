@@ -84,7 +84,14 @@ struct GemvArgs {
     // reports a given-up wait in; segments with enough row tiles then run on it (gemm_tc_shape_ok)
     const uint8_t *ximg_tc = nullptr;
     unsigned *tc_err = nullptr;
+    // launch_gemv only: weights of the products that follow this one in the stream; the kernel asks the L2 for them
+    // at entry (a hint: no data dependency, no completion)
+    const uint8_t *pf_next[3] = {nullptr, nullptr, nullptr};
+    size_t pf_next_bytes[3] = {0, 0, 0};
+    int pf_next_late = 0;  // ask when the CTAs run out of tasks instead (a long product followed by another long one)
 };
+// Bytes of weights a GEMV launch asks the L2 for ahead of its own loads (JUNO_L2_PREFETCH_MB, default 0 = off).
+size_t gemv_l2_prefetch_bytes();
 // Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
 int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
 

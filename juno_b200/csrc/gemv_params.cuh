@@ -31,6 +31,13 @@ struct GemvParams {
     float *ss_out;
     int ss_out_ld;
     StageImage img_next;  // also used by EPI_SILU_PAIR / EPI_STORE to emit the output as a staged activation
+    // L2 prefetch hints issued by every CTA, at kernel entry before it waits for the producer of x: row tiles
+    // [0, pf_rt) of this product (the CTA tasks that are handed out first), and up to three byte ranges of the
+    // products that follow in the stream (each CTA takes a 1/grid slice).
+    int pf_rt;
+    int pf_late;  // the ranges of the following products are requested when the CTA runs out of tasks, not at entry
+    const uint8_t *pfx[3];
+    unsigned pfx_bytes[3];
 };
 
 __device__ __forceinline__ int seg_of(const GemvParams &p, int R) {

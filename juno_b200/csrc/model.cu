@@ -601,12 +601,21 @@ static int stage_rms(juno_model *m, int n, const float *x, const float *add, flo
 // A row-parallel projection (Wo or Wdown) followed by "residual add, RMSNorm with the next norm weights, stage".
 // Single GPU: all fused into the GEMV epilogue (the 1/rms factor is applied by the consumer from per-task sums of
 // squares).  Tensor parallel: the partial products are all-reduced first, then one staging kernel does the rest.
+static void prefetch_after(GemvArgs &a, juno_qmat *const *next, int n_next, bool late) {
+    for (int i = 0; i < n_next && i < 3; i++) {
+        a.pf_next[i] = next[i] ? next[i]->dev : nullptr;
+        a.pf_next_bytes[i] = (next[i] && next[i]->tiled) ? next[i]->bytes : 0;
+    }
+    a.pf_next_late = late ? 1 : 0;
+}
+
 static int proj_resid_norm(juno_model *m, int n, juno_qmat *w, const uint8_t *ximg, int &cur, const float *normw_next,
-                           float *ss_out, bool *consumer_scales, cudaStream_t st) {
+                           float *ss_out, bool *consumer_scales, juno_qmat *const *next, int n_next, cudaStream_t st) {
     const int H = m->cfg.hidden;
     GemvArgs a;
     a.batch = n;
     a.ximg = ximg;
+    prefetch_after(a, next, n_next, false);
     juno_qmat *mats[1] = {w};
     if (m->world == 1) {
         a.epi = EPI_RESID_NORM;
@@ -819,6 +828,7 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
             set_input_scale(m, a, scaled, ss_d, parts_d);
             juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
             float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
+            prefetch_after(a, &L.w[JUNO_T_ATTN_OUT], 1, true);  // HBM is nearly idle during the attention
             if (!(m->debug_skip & 1u)) JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, a, st));
         }
         AttnArgs at;
@@ -846,7 +856,8 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         if (!(m->debug_skip & 2u)) JUNO_TRY(launch_attn(c, at, st));
         // x2 = x + Wo·att ; staged rmsNorm(x2, ffn_norm)
         if (!(m->debug_skip & 4u))
-            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled, st));
+            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled,
+                                     &L.w[JUNO_T_FFN_GATE], 1, st));
         // hdn = silu(Wgate·xn2) * (Wup·xn2), emitted as Wdown's staged input
         {
             GemvArgs a;
@@ -859,12 +870,21 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
             set_input_scale(m, a, scaled, ss_o, parts_o);
             juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
             float *gu_o[1] = {nullptr};
+            prefetch_after(a, &L.w[JUNO_T_FFN_DOWN], 1, true);
             if (!(m->debug_skip & 8u)) JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, a, st));
         }
         // x = x2 + Wdown·hdn ; staged rmsNorm(x, next norm)
         const float *next_norm = (l + 1 < f.n_layers) ? m->layers[l + 1].attn_norm : m->output_norm;
+        juno_qmat *after_down[3] = {m->output, nullptr, nullptr};
+        int n_after = 1;
+        if (l + 1 < f.n_layers) {
+            JunoLayer &N = m->layers[l + 1];
+            after_down[0] = N.w[JUNO_T_ATTN_Q], after_down[1] = N.w[JUNO_T_ATTN_K], after_down[2] = N.w[JUNO_T_ATTN_V];
+            n_after = 3;
+        }
         if (!(m->debug_skip & 16u))
-            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, st));
+            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, after_down,
+                                     n_after, st));
     }
     // logits = Wout · rmsNorm(x, output_norm)
     if (!replay) {
