@@ -671,7 +671,9 @@ size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits) {
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
     const int target = ctx->sm_count * 4;  // CTAs of 128 threads wanted in flight
     int by_occupancy = (target + n * n_kv_heads - 1) / std::max(1, n * n_kv_heads);
-    int by_length = std::max(1, (max_len + 63) / 64);  // at least 64 positions per split
+    // at least 128 positions per split (two pages per warp): in the batch-1 step at context 2048, 16-32 splits
+    // measured 2.27 ms/step against 2.36 ms with 64 (fewer partials to merge, same occupancy where it matters)
+    int by_length = std::max(1, (max_len + 127) / 128);
     int s = std::max(1, std::min(by_occupancy, by_length));
     if (const char *e = getenv("JUNO_ATTN_SPLITS")) s = std::max(1, std::min(s, atoi(e)));
     return std::min(s, 64);
