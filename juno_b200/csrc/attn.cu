@@ -4,6 +4,7 @@
 // LlamaTransformerHandler.java:670-733,1657-1730.  One CTA handles one (sequence, kv head, context
 // split): K and V pages are streamed once and shared by the G query heads of the group; each split
 // keeps an online-softmax state (m, l, o) and a second small kernel merges the splits.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -35,6 +36,9 @@ struct AttnParams {
     // when set ([n][n_kv_heads], zero between launches): the last split CTA of a (sequence, kv head) to finish
     // merges the splits itself and no separate merge kernel is launched
     unsigned *merge_counters;
+    // the context splits of a (sequence, kv head) form one thread-block cluster (cluster dimension y = n_splits): the
+    // splits are merged through distributed shared memory inside attn_mma_kernel and no merge kernel is launched
+    int cluster_merge;
 };
 
 template <typename T>
@@ -329,7 +333,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
     __half *sm_q = reinterpret_cast<__half *>(smem_raw);                 // [2 limbs][8 rows][LDT]
     __half *sm_kv = sm_q + 2 * 8 * LDT;                                   // [warp][stage 2][K | V][TILE]
     pdl_launch_dependents();
-    pdl_wait();
+    // Sequence lengths, page table and the cached positions were written by earlier steps (or, inside a prefill pass, by
+    // kernels that are not launched programmatically): only q and the k, v of the position being decoded come from
+    // the kernel before this one.  So the first K/V page of every warp is requested before the wait.
     const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r8 = lane >> 2, c = lane & 3;
     const int len = p.seq_lens[seq];
@@ -338,7 +344,29 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
     const int h0 = kvh * G;
     float *po = p.part_o + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * HD;   // head stride n_splits*HD
     float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
-    if (t0 >= t1) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
+    const int32_t *table = p.table + (size_t)p.slots[seq] * p.max_pages_per_seq;
+    const __half *kbase = static_cast<const __half *>(p.k), *vbase = static_cast<const __half *>(p.v);
+    const size_t page_stride = (size_t)p.n_kv_heads * kPageTokens * HD;
+    const size_t layer_off = (size_t)p.layer * p.n_pages * page_stride + (size_t)kvh * kPageTokens * HD;
+    __half *my_kv = sm_kv + (size_t)warp * 4 * TILE;
+    const uint32_t my_kv_s = (uint32_t)__cvta_generic_to_shared(my_kv);
+    const int pg0 = t0 >> 4, pg1 = (t1 + 15) >> 4;
+    auto issue = [&](int pg, int stage) {  // this warp's copy of page pg into its stage
+        const size_t off = layer_off + (size_t)table[pg] * page_stride;
+        const uint32_t kd = my_kv_s + (uint32_t)(stage * 2 * TILE) * 2u, vd = kd + TILE * 2u;
+#pragma unroll
+        for (int i = 0; i < HD / 16; i++) {  // 16 rows x HD/8 chunks of 16 bytes = 32 lanes x HD/16
+            const int ch = i * 32 + lane, row = ch / (HD / 8), col8 = ch - row * (HD / 8);
+            cp_async_16(kd + (uint32_t)(row * LDT + col8 * 8) * 2u, kbase + off + (size_t)row * HD + col8 * 8);
+            cp_async_16(vd + (uint32_t)(row * LDT + col8 * 8) * 2u, vbase + off + (size_t)row * HD + col8 * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int pg = pg0 + warp, stage = 0;
+    if (pg < pg1) issue(pg, 0);
+    pdl_wait();
+    // An empty split leaves at once, except as a member of a cluster: there it takes part in the merge with sum 0.
+    if (t0 >= t1 && !p.cluster_merge) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
         if (tid < G) {
             pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
             pml[(size_t)tid * p.n_splits * 2 + 1] = 0.f;
@@ -380,29 +408,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
         ql[ks][0] = *reinterpret_cast<const uint32_t *>(sm_q + 8 * LDT + r8 * LDT + ks * 16 + 2 * c);
         ql[ks][1] = *reinterpret_cast<const uint32_t *>(sm_q + 8 * LDT + r8 * LDT + ks * 16 + 2 * c + 8);
     }
-    const int32_t *table = p.table + (size_t)p.slots[seq] * p.max_pages_per_seq;
-    const __half *kbase = static_cast<const __half *>(p.k), *vbase = static_cast<const __half *>(p.v);
-    const size_t page_stride = (size_t)p.n_kv_heads * kPageTokens * HD;
-    const size_t layer_off = (size_t)p.layer * p.n_pages * page_stride + (size_t)kvh * kPageTokens * HD;
-    __half *my_kv = sm_kv + (size_t)warp * 4 * TILE;
-    const uint32_t my_kv_s = (uint32_t)__cvta_generic_to_shared(my_kv);
-    const int pg0 = t0 >> 4, pg1 = (t1 + 15) >> 4;
-    auto issue = [&](int pg, int stage) {  // this warp's copy of page pg into its stage
-        const size_t off = layer_off + (size_t)table[pg] * page_stride;
-        const uint32_t kd = my_kv_s + (uint32_t)(stage * 2 * TILE) * 2u, vd = kd + TILE * 2u;
-#pragma unroll
-        for (int i = 0; i < HD / 16; i++) {  // 16 rows x HD/8 chunks of 16 bytes = 32 lanes x HD/16
-            const int ch = i * 32 + lane, row = ch / (HD / 8), col8 = ch - row * (HD / 8);
-            cp_async_16(kd + (uint32_t)(row * LDT + col8 * 8) * 2u, kbase + off + (size_t)row * HD + col8 * 8);
-            cp_async_16(vd + (uint32_t)(row * LDT + col8 * 8) * 2u, vbase + off + (size_t)row * HD + col8 * 8);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
     float o[DN][2], m_run = -INFINITY, l_run = 0.f;  // row r8: output columns dn*8 + 2c, +1; running max; this lane's share of the sum
 #pragma unroll
     for (int dn = 0; dn < DN; dn++) o[dn][0] = o[dn][1] = 0.f;
-    int pg = pg0 + warp, stage = 0;
-    if (pg < pg1) issue(pg, 0);
     for (; pg < pg1; pg += kMmaWarps, stage ^= 1) {
         const bool more = pg + kMmaWarps < pg1;
         if (more) issue(pg + kMmaWarps, stage ^ 1);
@@ -509,6 +517,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
     float *mg_o = reinterpret_cast<float *>(sm_kv);       // [warp][G][HD]
     float *mg_m = mg_o + kMmaWarps * G * HD;               // [warp][G]
     float *mg_l = mg_m + kMmaWarps * G;                    // [warp][G]
+    float *cl_o = mg_l + kMmaWarps * G;                    // [G][HD]   this CTA's merged split, read by the cluster
+    float *cl_m = cl_o + G * HD, *cl_l = cl_m + G;
     if (r8 < G) {
 #pragma unroll
         for (int dn = 0; dn < DN; dn++)
@@ -534,12 +544,47 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
                 acc = fmaf(mg_o[((size_t)w * G + g) * HD + d], f, acc);
             }
         }
-        po[(size_t)g * p.n_splits * HD + d] = acc;
-        if (d == 0) {
-            pml[(size_t)g * p.n_splits * 2 + 0] = M;  // log2 domain
-            pml[(size_t)g * p.n_splits * 2 + 1] = L;
+        if (p.cluster_merge) {
+            cl_o[g * HD + d] = acc;
+            if (d == 0) {
+                cl_m[g] = M;
+                cl_l[g] = L;
+            }
+        } else {
+            po[(size_t)g * p.n_splits * HD + d] = acc;
+            if (d == 0) {
+                pml[(size_t)g * p.n_splits * 2 + 0] = M;  // log2 domain
+                pml[(size_t)g * p.n_splits * 2 + 1] = L;
+            }
         }
     }
+    if (!p.cluster_merge) return;
+    // Merge of the splits inside the cluster: every CTA keeps its (max, sum, output) in its own shared memory; CTA r
+    // then finishes the slice [r, r+1) * G*HD/S of the outputs, reading the S partial results over distributed shared
+    // memory in split order (fixed order: bitwise repeatable).  An empty split carries sum 0 and is skipped.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    {
+        const int S = (int)cluster.num_blocks(), r = (int)cluster.block_rank();
+        const int per = (G * HD) / S;
+        for (int idx = r * per + tid; idx < (r + 1) * per; idx += kMmaWarps * 32) {
+            const int g = idx / HD, d = idx - g * HD;
+            float M = -INFINITY;
+            for (int sp = 0; sp < S; sp++) M = fmaxf(M, *cluster.map_shared_rank(cl_m + g, sp));
+            float L = 0.f, acc = 0.f;
+            for (int sp = 0; sp < S; sp++) {
+                const float lw = *cluster.map_shared_rank(cl_l + g, sp);
+                if (lw > 0.f) {
+                    const float f = exp2f(*cluster.map_shared_rank(cl_m + g, sp) - M);
+                    L = fmaf(lw, f, L);
+                    acc = fmaf(*cluster.map_shared_rank(cl_o + g * HD + d, sp), f, acc);
+                }
+            }
+            p.out[(size_t)(seq * p.n_heads + h0 + g) * HD + d] = (L > 0.f) ? acc / L : 0.f;
+        }
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
 }
 
 // Merges the context splits of one (sequence, head): blockDim = kCombineParts * HD threads.  The split weights are
@@ -668,6 +713,16 @@ size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits) {
     return (size_t)n * n_heads * n_splits * (hd + 2);
 }
 
+// Largest split count the cluster-merged kernel takes: a power of two, at most 16 CTAs per cluster.
+static int attn_cluster_max() {
+    static const int v = [] {
+        const char *e = getenv("JUNO_ATTN_CLUSTER");  // 0: always merge with the separate kernel
+        const int m = e ? atoi(e) : 16;
+        return std::max(0, std::min(m, 16));
+    }();
+    return v;
+}
+
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
     const int target = ctx->sm_count * 4;  // CTAs of 128 threads wanted in flight
     int by_occupancy = (target + n * n_kv_heads - 1) / std::max(1, n * n_kv_heads);
@@ -676,7 +731,17 @@ int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {
     int by_length = std::max(1, (max_len + 127) / 128);
     int s = std::max(1, std::min(by_occupancy, by_length));
     if (const char *e = getenv("JUNO_ATTN_SPLITS")) s = std::max(1, std::min(s, atoi(e)));
-    return std::min(s, 64);
+    s = std::min(s, 64);
+    // Up to twice the cluster limit the count is rounded down to a power of two within it, so that the splits of a
+    // (sequence, kv head) can be one thread-block cluster and merge on chip; longer contexts keep their many splits
+    // and the separate merge kernel.
+    const int cmax = attn_cluster_max();
+    if (cmax > 0 && s <= 2 * cmax) {
+        int p2 = 1;
+        while (2 * p2 <= std::min(s, cmax)) p2 *= 2;
+        s = p2;
+    }
+    return s;
 }
 
 static bool attn_use_mma() {
@@ -692,6 +757,41 @@ static size_t attn_mma_smem() {
     return ((size_t)2 * 8 * (HD + 8) + (size_t)kMmaWarps * 4 * 16 * (HD + 8)) * sizeof(__half);
 }
 
+// Whether a cluster of `splits` CTAs of the tensor-core kernel can be co-scheduled on this device (asked once per size).
+template <int HD, int G>
+static bool attn_cluster_fits(int splits) {
+    static int fits[64][5] = {{0}};  // per device, per log2(splits): 0 unknown, 1 yes, 2 no
+    int dev = 0, lg = 0;
+    cudaGetDevice(&dev);
+    while ((1 << lg) < splits) lg++;
+    int &f = fits[dev & 63][lg];
+    if (f == 0) {
+        const size_t smem = attn_mma_smem<HD, G>();
+        cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, splits, 1);
+        cfg.blockDim = dim3(kMmaWarps * 32);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = (unsigned)splits;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_mma_kernel<HD, G>, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();
+        f = (e == cudaSuccess && n > 0) ? 1 : 2;
+    }
+    return f == 1;
+}
+static bool attn_cluster_fits_any(int hd, int G, int splits) {
+    if (hd == 128) return G == 1 ? attn_cluster_fits<128, 1>(splits) : G == 2 ? attn_cluster_fits<128, 2>(splits) : G == 4 ? attn_cluster_fits<128, 4>(splits) : G == 8 ? attn_cluster_fits<128, 8>(splits) : false;
+    return G == 1 ? attn_cluster_fits<64, 1>(splits) : G == 2 ? attn_cluster_fits<64, 2>(splits) : G == 4 ? attn_cluster_fits<64, 4>(splits) : G == 8 ? attn_cluster_fits<64, 8>(splits) : false;
+}
+
 template <typename T, int HD, int G>
 static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
     dim3 grid(p.n_kv_heads, p.n_splits, n);
@@ -704,6 +804,29 @@ static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
             if (!configured[dev & 63]) {
                 cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 configured[dev & 63] = true;
+            }
+            if (p.cluster_merge) {
+                static bool np_set[64] = {false};
+                if (!np_set[dev & 63]) {
+                    cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                    np_set[dev & 63] = true;
+                }
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = grid;
+                cfg.blockDim = dim3(kMmaWarps * 32);
+                cfg.dynamicSmemBytes = smem;
+                cfg.stream = st;
+                cudaLaunchAttribute attr[2];
+                attr[0].id = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 1;
+                attr[0].val.clusterDim.y = (unsigned)p.n_splits;
+                attr[0].val.clusterDim.z = 1;
+                attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[1].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = pdl_enabled() ? 2 : 1;
+                cudaLaunchKernelEx(&cfg, attn_mma_kernel<HD, G>, p);
+                return;
             }
             launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(kMmaWarps * 32), smem, st, p);
             return;
@@ -762,6 +885,11 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     p.stage.bc = a.stage_bc;
     p.stage.b0 = 0;
     p.stage.chunk_stride = a.stage_chunk_stride;
+    // FP16 pages, a power-of-two split count that fits one cluster and divides the group's outputs: merge in-cluster
+    p.cluster_merge = 0;
+    if (pool->dtype == 0 && attn_use_mma() && !a.merge_counters && !a.stage_img && a.n_splits <= attn_cluster_max() &&
+        (a.n_splits & (a.n_splits - 1)) == 0 && (G * hd) % a.n_splits == 0 && attn_cluster_fits_any(hd, G, a.n_splits))
+        p.cluster_merge = 1;
     ProfScope prof(ctx, st, PROF_ATTN, a.algo_bytes);
     int rc;
     if (pool->dtype == 0)
@@ -770,7 +898,7 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
         rc = hd == 128 ? attn_launch_g<float, 128>(p, a.n, G, st) : attn_launch_g<float, 64>(p, a.n, G, st);
     JUNO_TRY(rc);
     JUNO_CUDA_TRY(cudaGetLastError());
-    if (a.merge_counters) {
+    if (a.merge_counters || p.cluster_merge) {
         ctx->kernel_launches += 1;
         return JUNO_OK;
     }

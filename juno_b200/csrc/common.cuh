@@ -57,6 +57,7 @@ constexpr int kGemvCounterSlots = 256;
 struct GemvScratch {
     unsigned *counters = nullptr;  // [kGemvCounterSlots][2]
     unsigned next_slot = 0;
+    unsigned *qerr = nullptr;      // one word after the counters: a weight-tile wait of the integer GEMV gave up
     uint8_t *ximg = nullptr;       // staged activation for the host-level entry points
     size_t ximg_bytes = 0;
     float *xscale = nullptr;       // per-row factors of an FP16 staged activation (batched path), 64 floats

@@ -6,6 +6,7 @@
 #include <algorithm>
 
 #include "gemv.cuh"
+#include "qgemv.cuh"
 
 namespace juno {
 
@@ -127,8 +128,9 @@ int juno_ctx_create(int32_t device, juno_ctx **out) {
         delete c;
         return JUNO_ERR_CUDA;
     }
-    if (e == cudaSuccess) e = cudaMalloc((void **)&c->gemv_scratch.counters, kGemvCounterSlots * 2 * sizeof(unsigned));
-    if (e == cudaSuccess) e = cudaMemset(c->gemv_scratch.counters, 0, kGemvCounterSlots * 2 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&c->gemv_scratch.counters, (kGemvCounterSlots * 2 + 4) * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(c->gemv_scratch.counters, 0, (kGemvCounterSlots * 2 + 4) * sizeof(unsigned));
+    if (e == cudaSuccess) c->gemv_scratch.qerr = c->gemv_scratch.counters + kGemvCounterSlots * 2;
     if (e != cudaSuccess) {
         set_error("context set-up failed: rc=%d (%s)", (int)e, cudaGetErrorString(e));
         delete c;
@@ -277,6 +279,21 @@ int juno_qmat_shape(juno_qmat *m, int64_t *rows, int64_t *cols, int32_t *type) {
 static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, float *y, cudaStream_t st) {
     if (!m->tiled) return launch_gemv_raw(c, m, x, batch, y, st);
     const bool batched = batch >= gemm_min_batch();
+    if (!batched && qgemv_enabled()) {
+        QGemvArgs q;
+        q.nseg = 1;
+        q.seg[0].w = m->dev;
+        q.seg[0].out = y;
+        q.seg[0].rows = (int)m->rows;
+        q.seg[0].row_tiles = (int)m->row_tiles;
+        q.seg[0].type = m->type;
+        q.K = (int)m->cols;
+        q.batch = batch;
+        q.ld_out = (int)m->rows;
+        q.x = x;
+        q.ldx = (int)m->cols;
+        return launch_qgemv(c, q, st);
+    }
     const size_t need = batched ? gemm_image_bytes((int)m->cols, std::min(batch, kGemmMaxBatch)) : stage_image_bytes(c, (int)m->cols, batch);
     void *pi = c->gemv_scratch.ximg;
     JUNO_TRY(ensure_device(&pi, &c->gemv_scratch.ximg_bytes, need));

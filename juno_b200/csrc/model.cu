@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
+#include "qgemv.cuh"
 
 namespace juno {
 
@@ -210,7 +211,7 @@ struct juno_model {
     juno_kvpool *pool = nullptr;
     juno::NcclComm comm = nullptr;
     // activations
-    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *ss = nullptr;
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *proj2 = nullptr, *ss = nullptr;
     float *hdn = nullptr, *xsc = nullptr;  // batched path: silu(gate)*up rows; per-row factors of the three FP16 images
     uint8_t *img_h_tc = nullptr;            // batched path: the hidden-size activation again, chunk-major for the tcgen05 kernel
     unsigned *tc_err = nullptr;             // device word: a wait inside the tcgen05 kernel gave up
@@ -302,7 +303,7 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->ss, m->hdn, m->xsc, m->img_h_tc, m->tc_err, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->proj2, m->ss, m->hdn, m->xsc, m->img_h_tc, m->tc_err, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
                     m->attn_scratch, m->attn_counters, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
@@ -518,6 +519,7 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->qkv, (size_t)B * m->qkv_ld * 4));
     JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
+    JUNO_TRY(dev_alloc((void **)&m->proj2, (size_t)B * H * 4));
     JUNO_TRY(dev_alloc((void **)&m->ss, (size_t)2 * B * kSsLd * 4));
     const int Bg = std::min(B, kGemmMaxBatch);
     JUNO_TRY(dev_alloc((void **)&m->img_h, std::max(stage_image_bytes(c, H, B), gemm_image_bytes(H, Bg))));
@@ -753,6 +755,139 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
     return product(lm, lo, 1, EPI_STORE, m->vocab_loc, m->img_h, sc_h);
 }
 
+// ───────────────────────────── decode step on the integer-MMA GEMV (1..8 sequences) ───────
+// Matrices that share an input share a launch: one block format, or Q4_K mixed with Q6_K.
+static int q_group(juno_model *m, juno_qmat *const *mats, float *const *outs, int count, const QGemvArgs &proto, cudaStream_t st) {
+    int i = 0;
+    while (i < count) {
+        int j = i + 1;
+        while (j < count && j - i < 3) {
+            const int ta = mats[i]->type, tb = mats[j]->type;
+            const bool k_quant = m->mix_formats && (ta == 12 || ta == 14) && (tb == 12 || tb == 14);
+            if (tb != ta && !k_quant) break;
+            j++;
+        }
+        QGemvArgs a = proto;
+        a.nseg = j - i;
+        for (int s = 0; s < a.nseg; s++) {
+            a.seg[s].w = mats[i + s]->dev;
+            a.seg[s].out = outs[i + s];
+            a.seg[s].rows = a.epi == QEPI_SILU_PAIR ? (int)mats[i + s]->rows / 2 : (int)mats[i + s]->rows;
+            a.seg[s].row_tiles = (int)mats[i + s]->row_tiles;
+            a.seg[s].type = mats[i + s]->type;
+        }
+        a.K = (int)mats[i]->cols;
+        JUNO_TRY(launch_qgemv(m->ctx, a, st));
+        i = j;
+    }
+    return JUNO_OK;
+}
+
+// Layers and output projection for n <= 8 sequences.  x[0] holds the embeddings on entry.  Activations travel between
+// the kernels as plain FP32 rows; the residual additions (x + Wo att, x + Wdown hdn) and the RMSNorms are done by the
+// CONSUMING product while it builds its operand, which also writes the new residual row once (x_store).  Under tensor
+// parallelism the row-parallel products are all-reduced before their consumer reads them.
+static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const int32_t *d_len, int n_splits, int &cur, cudaStream_t st) {
+    juno_ctx *c = m->ctx;
+    const juno_model_cfg &f = m->cfg;
+    const int H = f.hidden, hd = m->hd;
+    const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
+    cur = 0;
+    const float *pend = nullptr;  // row-parallel product not yet added to the residual stream
+    auto from_residual = [&](QGemvArgs &a, const float *normw) {
+        a.batch = n;
+        a.x = m->x[cur];
+        a.ldx = H;
+        a.normw = normw;
+        a.eps = f.rms_eps;
+        if (pend) {
+            a.add[0] = pend;
+            a.n_add = 1;
+            a.x_store = m->x[cur ^ 1];
+        }
+    };
+    auto all_reduce = [&](float *buf) -> int {
+        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(buf, buf, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+        return JUNO_OK;
+    };
+    for (int l = 0; l < f.n_layers; l++) {
+        JunoLayer &L = m->layers[l];
+        {   // q, k, v = W rmsNorm(x)
+            QGemvArgs a;
+            from_residual(a, L.attn_norm);
+            a.ld_out = m->qkv_ld;
+            juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
+            float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
+            JUNO_TRY(q_group(m, qkv_m, qkv_o, 3, a, st));
+            if (pend) cur ^= 1;
+            pend = nullptr;
+        }
+        AttnArgs at;
+        at.pool = m->pool;
+        at.layer = l;
+        at.n = n;
+        at.n_heads = m->heads_loc;
+        at.q = m->qkv;
+        at.ldq = m->qkv_ld;
+        at.out = m->att;
+        at.slots = d_slot;
+        at.seq_lens = d_len;
+        at.n_splits = n_splits;
+        at.part_o = m->attn_scratch;
+        at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
+        at.algo_bytes = m->step_kv_bytes;
+        at.rope_cs = m->rope_cs;  // q, k are rotated and k, v appended inside the attention kernel
+        at.knew = m->qkv + Hl;
+        at.vnew = m->qkv + Hl + KVl;
+        at.ldkv = m->qkv_ld;
+        JUNO_TRY(launch_attn(c, at, st));
+        {   // proj = Wo att (this rank's heads)
+            QGemvArgs a;
+            a.batch = n;
+            a.x = m->att;
+            a.ldx = Hl;
+            a.ld_out = H;
+            juno_qmat *wo[1] = {L.w[JUNO_T_ATTN_OUT]};
+            float *po[1] = {m->proj};
+            JUNO_TRY(q_group(m, wo, po, 1, a, st));
+            JUNO_TRY(all_reduce(m->proj));
+            pend = m->proj;
+        }
+        {   // hdn = silu(Wgate xn2) * (Wup xn2), xn2 = rmsNorm(x + proj)
+            QGemvArgs a;
+            from_residual(a, L.ffn_norm);
+            a.epi = QEPI_SILU_PAIR;
+            a.ld_out = Il;
+            juno_qmat *gu[1] = {L.w[JUNO_T_FFN_GATE]};
+            float *go[1] = {m->hdn};
+            JUNO_TRY(q_group(m, gu, go, 1, a, st));
+            cur ^= 1;
+            pend = nullptr;
+        }
+        {   // proj2 = Wdown hdn (this rank's FFN rows)
+            QGemvArgs a;
+            a.batch = n;
+            a.x = m->hdn;
+            a.ldx = Il;
+            a.ld_out = H;
+            juno_qmat *wd[1] = {L.w[JUNO_T_FFN_DOWN]};
+            float *po[1] = {m->proj2};
+            JUNO_TRY(q_group(m, wd, po, 1, a, st));
+            JUNO_TRY(all_reduce(m->proj2));
+            pend = m->proj2;
+        }
+    }
+    // logits = Wout rmsNorm(x + proj2)
+    QGemvArgs a;
+    from_residual(a, m->output_norm);
+    a.ld_out = m->vocab_loc;
+    juno_qmat *lm[1] = {m->output};
+    float *lo[1] = {m->logits_loc};
+    JUNO_TRY(q_group(m, lm, lo, 1, a, st));
+    if (pend) cur ^= 1;
+    return JUNO_OK;
+}
+
 // Whether this model and batch size run through the persistent step kernel.
 static bool step_model_ok(juno_model *m, int n) {
     if (m->world != 1) return false;
@@ -796,7 +931,8 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
         juno_ctx *c;
         ~RecGuard() { c->step_rec = nullptr; }
     } rec_guard{c};
-    const bool replay = (plan && plan->d_phases) || (m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0);
+    const bool replay = (plan && plan->d_phases) || (m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0) ||
+                        (!plan && qgemv_enabled() && n <= 8 && m->debug_skip == 0);
     float *ss_o = m->ss, *ss_d = m->ss + (size_t)B * kSsLd;  // sums of squares written by Wo / Wdown epilogues
     const int parts_o = gemv_n_ctasks(c, Hl, n, H / 16), parts_d = gemv_n_ctasks(c, Il, n, H / 16);
     JUNO_REQUIRE(parts_o <= kSsLd && parts_d <= kSsLd, "hidden size %d needs more than %d partial sums", H, kSsLd);
@@ -813,7 +949,9 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
     JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
     int cur = 0;          // x[cur] holds the residual stream
     const bool batched = m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0;
+    const bool qpath = !batched && !plan && qgemv_enabled() && n <= 8 && m->debug_skip == 0;
     if (batched) JUNO_TRY(enqueue_layers_batched(m, n, d_slot, d_len, n_splits, cur, st));
+    else if (qpath) JUNO_TRY(enqueue_layers_q(m, n, d_slot, d_len, n_splits, cur, st));
     else JUNO_TRY(stage_rms(m, n, m->x[0], nullptr, nullptr, m->layers[0].attn_norm, st));
 
     bool scaled = false;  // img_h holds normw*x and the consumer still has to apply 1/rms

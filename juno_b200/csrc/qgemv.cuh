@@ -1,0 +1,51 @@
+// Fused dequant-GEMV on integer tensor-core MMAs (decode batches of 1..8 sequences): device-level interface.
+//
+// The activation arrives as plain FP32 rows.  Every CTA builds its own operand from it: optional residual
+// adds (x + partial products, summed in a fixed order), optional RMSNorm weights, then a block-floating-point
+// split of every 256-column slice into three signed 8-bit limbs (q = round(v / 2^e), q = l0 + 256 l1 + 65536 l2),
+// so that the products against the 4/6/8-bit weights are exact integers (qgemv.cu).
+#pragma once
+#include "common.cuh"
+
+namespace juno {
+
+enum QEpilogue {
+    QEPI_STORE = 0,      // out[b][row] = y
+    QEPI_SILU_PAIR = 1,  // tile rows 0-7 are gate rows, 8-15 the matching up rows: out[b][8*tile+row] = silu(gate)*up
+};
+
+constexpr int kQMaxAdd = 8;
+
+struct QSeg {
+    const uint8_t *w = nullptr;  // tiled weights (layout.cuh)
+    float *out = nullptr;        // [batch][ld_out]
+    int rows = 0;                // valid output rows (after pairing, for QEPI_SILU_PAIR)
+    int row_tiles = 0;
+    int type = 0;                // 12 / 14 / 8
+};
+
+struct QGemvArgs {
+    QSeg seg[3];
+    int nseg = 1;
+    int K = 0;
+    int batch = 1;
+    int ld_out = 0;
+    int epi = QEPI_STORE;
+    // input rows: v = x (+ (add[0] + add[1] + ...)), each [batch][ldx]
+    const float *x = nullptr;
+    int ldx = 0;
+    const float *add[kQMaxAdd] = {nullptr};
+    int n_add = 0;
+    float *x_store = nullptr;       // optional: the summed input rows are written here (by one CTA)
+    const float *normw = nullptr;   // optional RMSNorm (LlamaTransformerHandler.rmsNorm :818-828): operand = normw*v,
+    float eps = 0.f;                //   outputs multiplied by 1/sqrt(mean(v^2) + eps)
+};
+
+// The integer-MMA kernel is the default for 1..8 sequences; JUNO_QGEMV=0 keeps the bf16-limb kernel (gemv.cu).
+bool qgemv_enabled();
+// Most sequences one launch can take for this K and block format mix (shared memory), at most 8.
+int qgemv_batch_chunk(const juno_ctx *ctx, int K, int type_mix, int batch);
+// Enqueues the product (several launches when the batch exceeds one chunk).  All pointers are device pointers.
+int launch_qgemv(juno_ctx *ctx, const QGemvArgs &a, cudaStream_t stream);
+
+}  // namespace juno

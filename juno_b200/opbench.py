@@ -23,7 +23,7 @@ BPW = {synth.Q4_K: 144 / 256, synth.Q6_K: 210 / 256, synth.Q8_0: 34 / 32}
 L2_BYTES = 126e6
 
 
-def gemv_case(ctx, mv, t, rows, cols, batch, iters, warmup, seed=1):
+def gemv_case(ctx, mv, t, rows, cols, batch, iters, warmup, seed=1, chain=0):
     import torch
     rng = np.random.default_rng(seed)
     wbytes = rows * cols * BPW[t]
@@ -42,6 +42,31 @@ def gemv_case(ctx, mv, t, rows, cols, batch, iters, warmup, seed=1):
 
     for i in range(warmup):
         launch(i)
+    name = [k for k, v in TYPES.items() if v == t][0]
+    algo = wbytes + batch * cols * 4 + batch * rows * 4
+    if chain:
+        # `chain` launches back to back inside one CUDA graph: the per-launch time a product costs inside a decode step
+        # (launch latency overlapped by programmatic dependent launch), not the time of an isolated launch
+        g = torch.cuda.CUDAGraph()
+        ctx.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(chain):
+                launch(i)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ms = []
+        for _ in range(iters):
+            with torch.cuda.stream(stream):
+                g.replay()
+                a.record(stream)
+                g.replay()
+                b.record(stream)
+            ctx.synchronize()
+            ms.append(a.elapsed_time(b) / chain)
+        for m in mats:
+            m.close()
+        us = float(np.median(ms) * 1e3)
+        return {"op": "gemv", "mode": f"graph chain of {chain}", "type": name, "rows": rows, "cols": cols, "batch": batch,
+                "us_per_launch": us, "algo_bytes": algo, "gbs": float(algo / (us / 1e6) / 1e9), "weight_copies": copies}
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
     for i, (a, b) in enumerate(evs):
         a.record(stream)
@@ -49,10 +74,8 @@ def gemv_case(ctx, mv, t, rows, cols, batch, iters, warmup, seed=1):
         b.record(stream)
     ctx.synchronize()
     ms = np.array([a.elapsed_time(b) for a, b in evs])
-    algo = wbytes + batch * cols * 4 + batch * rows * 4
     for m in mats:
         m.close()
-    name = [k for k, v in TYPES.items() if v == t][0]
     return {"op": "gemv", "type": name, "rows": rows, "cols": cols, "batch": batch, "us_median": float(np.median(ms) * 1e3),
             "us_min": float(ms.min() * 1e3), "algo_bytes": algo, "gbs": float(algo / (np.median(ms) / 1e3) / 1e9),
             "weight_copies": copies, "iters": iters}
@@ -100,6 +123,7 @@ def main():
     ap.add_argument("--ctx", default="512,2048,8192,32768")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--chain", type=int, default=0, help="gemv: time this many launches back to back inside one CUDA graph")
     a = ap.parse_args()
     ctx = GpuContext.shared(0)
     if a.op == "gemv":
@@ -108,7 +132,7 @@ def main():
             for shp in a.shapes.split(","):
                 rows, cols = map(int, shp.split("x"))
                 for b in map(int, (a.batches or "1,4,16,64").split(",")):
-                    print(json.dumps(gemv_case(ctx, mv, TYPES[tn], rows, cols, b, a.iters, a.warmup)), flush=True)
+                    print(json.dumps(gemv_case(ctx, mv, TYPES[tn], rows, cols, b, a.iters, a.warmup, chain=a.chain)), flush=True)
     else:
         for c in map(int, a.ctx.split(",")):
             for b in map(int, (a.batches or "1,8,64").split(",")):

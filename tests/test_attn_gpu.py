@@ -58,3 +58,19 @@ def test_attention_sweep_point(ctx, oracle):
 
 def test_attention_long_context_split(ctx, oracle):
     _run(ctx, oracle, 32, 8, 128, [8192], "f16")
+
+
+@pytest.mark.parametrize("lens", [[2049], [300, 2049, 17], [1025, 1040]])
+def test_attention_cluster_merge_with_empty_split(ctx, oracle, lens):
+    """Lengths just above a multiple of the split size: the splits are rounded up to whole pages, so the last
+    split of a sequence holds no position at all.  With FP16 pages the splits of a (sequence, kv head) form one
+    thread-block cluster and are merged on chip: the empty one must still take part."""
+    _run(ctx, oracle, 32, 8, 128, lens, "f16")
+
+
+def test_attention_sweep_long_and_wide(ctx, oracle):
+    """Two more points of the attention sweep: context 32768 at batch 1, and batch 64 at context 2048 with lengths
+    uniform in [ctx/2, ctx]."""
+    _run(ctx, oracle, 32, 8, 128, [32768], "f16")
+    rng = np.random.default_rng(3)
+    _run(ctx, oracle, 32, 8, 128, rng.integers(1024, 2049, 64).tolist(), "f16")
