@@ -133,7 +133,8 @@ int juno_attn_decode(juno_ctx *ctx, juno_kvpool *p, int32_t layer, int32_t n, ju
  * are used when the array is the constraint.  The first call on a device resolves the array's device address
  * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls share the array: it keeps
  * the previous call's contents (every entry a call reads is rewritten by that call first), and two calls that
- * overlap on the GPU race - this function serialises on the context and returns after the stream has drained.
+ * overlap on the GPU race - this function holds one lock per device (so two contexts of a GPU are serialised as
+ * well) and returns after the stream has drained.
  * No counterpart in the reference. */
 int juno_attn_decode_static(juno_ctx *ctx, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs,
                             int32_t n_heads, const float *q_dev, float *out_dev);
@@ -174,6 +175,14 @@ typedef struct juno_model_cfg {
 #define JUNO_T_FFN_GATE 9
 #define JUNO_T_FFN_UP 10
 #define JUNO_T_FFN_DOWN 11
+
+/* Host-only (no GPU needed): the slice of a FULL tensor of `kind` that rank tp_rank of tp_world keeps - the rule
+ * juno_model_set_tensor applies itself (TensorShardContext.java:74-100: headsPerNode = numHeads / world, sliceDim =
+ * hidden / world).  out6 = {rows, cols, row0, nrows, col0, ncols} of the full tensor and of the kept sub-matrix:
+ * column-parallel attn_q/k/v, ffn_gate/up and output keep whole rows, row-parallel attn_output / ffn_down keep whole
+ * 256-column super-blocks of every row.  A host can use it to ship only what a rank needs. */
+int juno_tp_slice(int32_t hidden, int32_t n_heads, int32_t n_kv_heads, int32_t inter, int32_t vocab, int32_t kind,
+                  int32_t tp_rank, int32_t tp_world, int64_t *out6);
 
 /* Fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and ships the bytes to the other ranks). */
 int juno_nccl_unique_id(uint8_t *out128);
@@ -225,8 +234,8 @@ int juno_ctx_counters(juno_ctx *ctx, juno_counters *out, int32_t reset);
  * While enabled every launch is bracketed by CUDA events on the context stream and forward passes run
  * without CUDA graphs; juno_ctx_profile_read synchronises and returns, per category, launches, summed
  * milliseconds and the algorithmic bytes the launches had to move.  Categories: 0 Q4_K GEMV, 1 Q6_K GEMV,
- * 2 Q8_0 GEMV, 3 attention (split + merge), 4 RoPE + KV append, 5 other, 6 the persistent decode-step kernel
- * (all products and attention of a step in one launch). */
+ * 2 Q8_0 GEMV, 3 attention (split + merge), 4 RoPE + KV append, 5 other, 6 batched products that ran on the
+ * tcgen05/TMEM kernel (also counted under their block format). */
 #define JUNO_PROF_COUNT 7
 typedef struct juno_profile_entry {
     int64_t launches;

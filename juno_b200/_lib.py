@@ -33,7 +33,7 @@ class ProfileEntry(C.Structure):
     _fields_ = [("launches", C.c_int64), ("ms", C.c_double), ("algo_bytes", C.c_double)]
 
 
-PROF_NAMES = ["gemv_q4k", "gemv_q6k", "gemv_q8_0", "attention", "rope_append", "other", "decode_step"]
+PROF_NAMES = ["gemv_q4k", "gemv_q6k", "gemv_q8_0", "attention", "rope_append", "other", "gemm_tcgen05"]
 
 P = C.c_void_p
 PP = C.POINTER(C.c_void_p)
@@ -68,6 +68,7 @@ SIGNATURES = {
     "juno_seq_append_kv": (C.c_int, [P, I32, I32, I32, P, P]),
     "juno_attn_decode": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),
     "juno_attn_decode_static": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),
+    "juno_tp_slice": (C.c_int, [I32, I32, I32, I32, I32, I32, I32, I32, C.POINTER(I64)]),
     "juno_nccl_unique_id": (C.c_int, [P]),
     "juno_model_create": (C.c_int, [P, C.POINTER(ModelCfg), PP]),
     "juno_model_set_tensor": (C.c_int, [P, I32, I32, P, I32, I64, I64]),

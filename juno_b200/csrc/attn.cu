@@ -12,8 +12,6 @@
 #include <type_traits>
 
 #include "attn.cuh"
-#include "stage.cuh"
-#include "step.cuh"
 
 namespace juno {
 
@@ -26,16 +24,12 @@ struct AttnParams {
     int ldq;
     const int32_t *slots, *seq_lens;
     float *part_o, *part_ml, *out;
-    StageImage stage;  // img == nullptr: not requested
     // fused RoPE + KV append (rope_cs != nullptr): q is rotated on load, and the CTA whose split holds the newest
     // position rotates k, rounds k and v to the cache type, uses them and writes them to their page
     const float2 *rope_cs;
     const float *knew, *vnew;
     int ldkv;
     void *kw, *vw;
-    // when set ([n][n_kv_heads], zero between launches): the last split CTA of a (sequence, kv head) to finish
-    // merges the splits itself and no separate merge kernel is launched
-    unsigned *merge_counters;
     // the context splits of a (sequence, kv head) form one thread-block cluster (cluster dimension y = n_splits): the
     // splits are merged through distributed shared memory inside attn_mma_kernel and no merge kernel is launched
     int cluster_merge;
@@ -79,53 +73,6 @@ __device__ __forceinline__ void load8<float>(const float *p, float (&o)[8]) {
 constexpr int kAttnWarps = 4;
 constexpr int kAttnUnroll = 4;  // positions in flight per token slot
 
-// Merge of the context splits of the G heads of one kv head by a block of 128 threads, all heads at once:
-// the split weights of head g are computed by warp g % 4 (one or two splits per lane), then every thread
-// accumulates G*HD/128 outputs.  One block barrier inside.
-template <int HD, int G>
-__device__ __forceinline__ void merge_splits_group(const AttnParams &p, int seq, int h0, int tid, float (*f)[64], float *Ls) {
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int g = warp; g < G; g += 4) {
-        const float *pml = p.part_ml + (size_t)(seq * p.n_heads + h0 + g) * p.n_splits * 2;
-        float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-        if (lane < p.n_splits) {
-            m0 = __ldcg(pml + 2 * lane);
-            l0 = __ldcg(pml + 2 * lane + 1);
-        }
-        if (lane + 32 < p.n_splits) {  // n_splits <= 64
-            m1 = __ldcg(pml + 2 * (lane + 32));
-            l1 = __ldcg(pml + 2 * (lane + 32) + 1);
-        }
-        float M = fmaxf(m0, m1);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        const float f0 = (l0 > 0.f) ? exp2f(m0 - M) : 0.f, f1 = (l1 > 0.f) ? exp2f(m1 - M) : 0.f;  // log2 domain
-        f[g][lane] = f0;
-        f[g][lane + 32] = f1;
-        float L = fmaf(l0, f0, l1 * f1);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-        if (lane == 0) Ls[g] = L;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < G * HD; idx += 128) {
-        const int g = idx / HD, d = idx - g * HD, h = h0 + g;
-        const float *po = p.part_o + (size_t)(seq * p.n_heads + h) * p.n_splits * HD;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < p.n_splits; s++) acc = fmaf(__ldcg(po + (size_t)s * HD + d), f[g][s], acc);
-        const float L = Ls[g];
-        const float outv = (L > 0.f) ? acc / L : 0.f;
-        p.out[(size_t)(seq * p.n_heads + h) * HD + d] = outv;
-        if (p.stage.img) {
-            unsigned short *xb;
-            int NC, col0;
-            p.stage.locate(seq, xb, NC, col0);
-            stage_store1(xb, NC, col0, h * HD + d, outv);
-        }
-    }
-}
-
 // One CTA = (kv head, context split, sequence).  HD/8 lanes share one cached position (eight head dimensions
 // each, one 128-bit load for K and one for V), so a warp works on 32/(HD/8) positions at a time and every lane
 // keeps an online-softmax state for the G query heads of the group; the states are merged through shared memory.
@@ -144,8 +91,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
     float *pml = p.part_ml + ((size_t)(seq * p.n_heads + h0) * p.n_splits + split) * 2;  // head stride n_splits*2
     __shared__ float sm_m[SLOTS][G], sm_l[SLOTS][G];
     __shared__ float sm_o[SLOTS][G][HD];
-    __shared__ float mg_f[G][64], mg_L[G];
-    __shared__ int is_last;
     if (t0 >= t1) {  // empty split: weight 0, and finite zeros so that 0 * partial stays 0 in the merge
         if (tid < G) {
             pml[(size_t)tid * p.n_splits * 2 + 0] = -INFINITY;
@@ -272,20 +217,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnP
         }
     }
     }  // non-empty split
-    if (!p.merge_counters) return;
-    // the last split of this (sequence, kv head) to get here merges all of them (no waiting: whoever is last does it)
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        unsigned *ctr = p.merge_counters + seq * p.n_kv_heads + kvh;
-        const unsigned old = atomicAdd(ctr, 1u);
-        is_last = (old == (unsigned)p.n_splits - 1u);
-        if (is_last) *ctr = 0u;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    merge_splits_group<HD, G>(p, seq, h0, tid, mg_f, mg_L);
 }
 
 // ───────────────────────────── tensor-core variant (FP16 pages) ───────────────────────────
@@ -491,7 +422,17 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
             o[dn][0] *= corr;
             o[dn][1] *= corr;
         }
+        // the weights as two FP16 limbs (hi + lo), like q: the weighted sum keeps FP32-level accuracy
         const uint32_t pa0 = pack_h2(pe[0], pe[1]), pa2 = pack_h2(pe[2], pe[3]);
+        float pl[4];
+        {
+            const __half2 h01 = *reinterpret_cast<const __half2 *>(&pa0), h23 = *reinterpret_cast<const __half2 *>(&pa2);
+            pl[0] = pe[0] - __low2float(h01);
+            pl[1] = pe[1] - __high2float(h01);
+            pl[2] = pe[2] - __low2float(h23);
+            pl[3] = pe[3] - __high2float(h23);
+        }
+        const uint32_t pb0 = pack_h2(pl[0], pl[1]), pb2 = pack_h2(pl[2], pl[3]);
         {
             const int mi = lane >> 3, rr = (lane & 7) + 8 * (mi & 1), cc = 8 * (mi >> 1);
 #pragma unroll
@@ -501,6 +442,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
                 float acc0[4] = {o[dn][0], o[dn][1], 0.f, 0.f}, acc1[4] = {o[dn + 1][0], o[dn + 1][1], 0.f, 0.f};
                 mma_f16(acc0, pa0, 0u, pa2, 0u, b[0], b[1]);
                 mma_f16(acc1, pa0, 0u, pa2, 0u, b[2], b[3]);
+                mma_f16(acc0, pb0, 0u, pb2, 0u, b[0], b[1]);
+                mma_f16(acc1, pb0, 0u, pb2, 0u, b[2], b[3]);
                 o[dn][0] = acc0[0];
                 o[dn][1] = acc0[1];
                 o[dn + 1][0] = acc1[0];
@@ -637,12 +580,6 @@ __global__ void __launch_bounds__(kCombineParts * HD) attn_combine_kernel(const 
     for (int q = 1; q < kCombineParts; q++) acc += acc_s[q][d];
     const float outv = (L > 0.f) ? acc / L : 0.f;
     p.out[(size_t)(seq * p.n_heads + h) * HD + d] = outv;
-    if (p.stage.img) {
-        unsigned short *xb;
-        int NC, col0;
-        p.stage.locate(seq, xb, NC, col0);
-        stage_store1(xb, NC, col0, h * HD + d, outv);
-    }
 }
 
 // cos/sin of pos * theta^(-2i/hd) in binary64, cast to float, as LlamaTransformerHandler.rope (:1662-1666).
@@ -796,7 +733,7 @@ template <typename T, int HD, int G>
 static void attn_launch_inst(const AttnParams &p, int n, cudaStream_t st) {
     dim3 grid(p.n_kv_heads, p.n_splits, n);
     if constexpr (std::is_same<T, __half>::value) {
-        if (attn_use_mma() && !p.merge_counters) {
+        if (attn_use_mma()) {
             const size_t smem = attn_mma_smem<HD, G>();
             static bool configured[64] = {false};  // per device
             int dev = 0;
@@ -849,7 +786,6 @@ static int attn_launch_g(const AttnParams &p, int n, int G, cudaStream_t st) {
 }
 
 int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
-    if (ctx->step_rec) return step_record_attn(ctx, a);
     const juno_kvpool *pool = a.pool;
     JUNO_REQUIRE(a.n_heads % pool->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", a.n_heads,
                  pool->n_kv_heads);
@@ -872,22 +808,15 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
     p.part_o = a.part_o;
     p.part_ml = a.part_ml;
     p.out = a.out;
-    p.merge_counters = a.merge_counters;
     p.rope_cs = a.rope_cs;
     p.knew = a.knew;
     p.vnew = a.vnew;
     p.ldkv = a.ldkv;
     p.kw = pool->k;
     p.vw = pool->v;
-    p.stage.img = a.stage_img;
-    p.stage.K = a.n_heads * hd;
-    p.stage.batch = a.n;
-    p.stage.bc = a.stage_bc;
-    p.stage.b0 = 0;
-    p.stage.chunk_stride = a.stage_chunk_stride;
     // FP16 pages, a power-of-two split count that fits one cluster and divides the group's outputs: merge in-cluster
     p.cluster_merge = 0;
-    if (pool->dtype == 0 && attn_use_mma() && !a.merge_counters && !a.stage_img && a.n_splits <= attn_cluster_max() &&
+    if (pool->dtype == 0 && attn_use_mma() && a.n_splits <= attn_cluster_max() &&
         (a.n_splits & (a.n_splits - 1)) == 0 && (G * hd) % a.n_splits == 0 && attn_cluster_fits_any(hd, G, a.n_splits))
         p.cluster_merge = 1;
     ProfScope prof(ctx, st, PROF_ATTN, a.algo_bytes);
@@ -898,7 +827,7 @@ int launch_attn(juno_ctx *ctx, const AttnArgs &a, cudaStream_t st) {
         rc = hd == 128 ? attn_launch_g<float, 128>(p, a.n, G, st) : attn_launch_g<float, 64>(p, a.n, G, st);
     JUNO_TRY(rc);
     JUNO_CUDA_TRY(cudaGetLastError());
-    if (a.merge_counters || p.cluster_merge) {
+    if (p.cluster_merge) {
         ctx->kernel_launches += 1;
         return JUNO_OK;
     }
@@ -1243,7 +1172,7 @@ int juno_attn_decode(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno
 constexpr size_t kStaticAttnScratchBytes = 8u << 20;
 constexpr int kStaticAttnMaxSeqs = 256;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
-static std::mutex g_static_attn_mu;
+static std::mutex g_static_attn_mu[64];                // one per device ordinal: held for a whole call, because the array is per device
 static void *g_static_attn_ptr[64] = {nullptr};  // device address of the array, per device ordinal
 
 int juno_attn_decode_static(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t n, juno_seq *const *seqs, int32_t n_heads,
@@ -1261,13 +1190,14 @@ int juno_attn_decode_static(juno_ctx *c, juno_kvpool *p, int32_t layer, int32_t 
     JUNO_REQUIRE(n_heads > 0 && n_heads % p->n_kv_heads == 0, "n_heads %d is not a multiple of n_kv_heads %d", n_heads,
                  p->n_kv_heads);
     JUNO_REQUIRE(c->device >= 0 && c->device < 64, "device ordinal %d not supported here", c->device);
+    // Two contexts of one device share the array: the per-device lock is held until this call's kernels have drained.
+    std::lock_guard<std::mutex> dev_lock(g_static_attn_mu[c->device]);
     std::lock_guard<std::recursive_mutex> lk(c->mu);
     DeviceGuard g(c->device);
     // One-time set-up per device, with that device current: in host code the array's name is only a handle, the
     // address a kernel can use comes from cudaGetSymbolAddress.
     void *base = nullptr;
     {
-        std::lock_guard<std::mutex> lk2(g_static_attn_mu);
         if (!g_static_attn_ptr[c->device]) {
             void *ptr = nullptr;
             cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);

@@ -52,13 +52,6 @@ struct AttnArgs {
     const float2 *rope_cs = nullptr;
     const float *knew = nullptr, *vnew = nullptr;
     int ldkv = 0;
-    // optional: [n][n_kv_heads] words, zero between launches; the last split CTA per (sequence, kv head) then merges
-    // the splits itself and the separate merge kernel is not launched
-    unsigned *merge_counters = nullptr;
-    // optional: also emit the output as a staged GEMV activation (K = n_heads*hd columns per sequence)
-    uint8_t *stage_img = nullptr;
-    int stage_bc = 1;
-    size_t stage_chunk_stride = 0;
 };
 size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits);
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len);

@@ -51,32 +51,25 @@ constexpr uint32_t kMagicSeq = 0x4A534551;    // "JSEQ"
 constexpr uint32_t kMagicPool = 0x4A4B5650;   // "JKVP"
 constexpr uint32_t kMagicDead = 0xDEADDEAD;
 
-// Device-side work counters of the GEMV kernels (dynamic task distribution): a ring of {next, done} pairs so
-// that consecutive launches never share a pair; each kernel leaves its pair at zero.
-constexpr int kGemvCounterSlots = 256;
+// Scratch of the host-level MatVec entry points and the word kernels report a given-up wait in.
 struct GemvScratch {
-    unsigned *counters = nullptr;  // [kGemvCounterSlots][2]
-    unsigned next_slot = 0;
-    unsigned *qerr = nullptr;      // one word after the counters: a weight-tile wait of the integer GEMV gave up
-    uint8_t *ximg = nullptr;       // staged activation for the host-level entry points
+    unsigned *qerr = nullptr;       // device address of qerr_host
+    unsigned *qerr_host = nullptr;  // mapped host memory: code | warp << 8 | block << 16, 0 = no failure
+    uint8_t *ximg = nullptr;        // FP16 staged activation (batched path)
     size_t ximg_bytes = 0;
-    float *xscale = nullptr;       // per-row factors of an FP16 staged activation (batched path), 64 floats
+    float *xscale = nullptr;        // per-row factors of an FP16 staged activation, 64 floats
 };
 
 }  // namespace juno
 
 namespace juno {
-enum ProfCat { PROF_GEMV_Q4K = 0, PROF_GEMV_Q6K, PROF_GEMV_Q80, PROF_ATTN, PROF_ROPE_APPEND, PROF_OTHER, PROF_STEP, PROF_COUNT };
+enum ProfCat { PROF_GEMV_Q4K = 0, PROF_GEMV_Q6K, PROF_GEMV_Q80, PROF_ATTN, PROF_ROPE_APPEND, PROF_OTHER, PROF_GEMM_TC, PROF_COUNT };
 struct ProfSpan {
     int cat;
     double bytes;
     cudaEvent_t e0, e1;
 };
 }  // namespace juno
-
-namespace juno {
-struct StepRecorder;
-}
 
 struct juno_ctx {
     uint32_t magic;
@@ -86,8 +79,6 @@ struct juno_ctx {
     cudaStream_t stream;
     std::recursive_mutex mu;
     juno::GemvScratch gemv_scratch;
-    // while set, launch_gemv / launch_attn describe their work to the recorder instead of launching (step.cuh)
-    juno::StepRecorder *step_rec = nullptr;
     // staging buffers for the host-in/host-out entry points
     float *stage_x = nullptr, *stage_y = nullptr;
     size_t stage_x_bytes = 0, stage_y_bytes = 0;

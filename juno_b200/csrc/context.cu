@@ -128,9 +128,12 @@ int juno_ctx_create(int32_t device, juno_ctx **out) {
         delete c;
         return JUNO_ERR_CUDA;
     }
-    if (e == cudaSuccess) e = cudaMalloc((void **)&c->gemv_scratch.counters, (kGemvCounterSlots * 2 + 4) * sizeof(unsigned));
-    if (e == cudaSuccess) e = cudaMemset(c->gemv_scratch.counters, 0, (kGemvCounterSlots * 2 + 4) * sizeof(unsigned));
-    if (e == cudaSuccess) c->gemv_scratch.qerr = c->gemv_scratch.counters + kGemvCounterSlots * 2;
+    // one word in mapped host memory: a kernel that gave up a wait leaves its code there, the host reads it for free
+    if (e == cudaSuccess) e = cudaHostAlloc((void **)&c->gemv_scratch.qerr_host, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        memset(c->gemv_scratch.qerr_host, 0, 64);
+        e = cudaHostGetDevicePointer((void **)&c->gemv_scratch.qerr, c->gemv_scratch.qerr_host, 0);
+    }
     if (e != cudaSuccess) {
         set_error("context set-up failed: rc=%d (%s)", (int)e, cudaGetErrorString(e));
         delete c;
@@ -147,7 +150,7 @@ int juno_ctx_destroy(juno_ctx *c) {
     cudaStreamSynchronize(c->stream);
     if (c->gemv_scratch.ximg) cudaFree(c->gemv_scratch.ximg);
     if (c->gemv_scratch.xscale) cudaFree(c->gemv_scratch.xscale);
-    if (c->gemv_scratch.counters) cudaFree(c->gemv_scratch.counters);
+    if (c->gemv_scratch.qerr_host) cudaFreeHost(c->gemv_scratch.qerr_host);
     if (c->stage_x) cudaFree(c->stage_x);
     if (c->stage_y) cudaFree(c->stage_y);
     if (c->pinned) cudaFreeHost(c->pinned);
@@ -279,7 +282,7 @@ int juno_qmat_shape(juno_qmat *m, int64_t *rows, int64_t *cols, int32_t *type) {
 static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, float *y, cudaStream_t st) {
     if (!m->tiled) return launch_gemv_raw(c, m, x, batch, y, st);
     const bool batched = batch >= gemm_min_batch();
-    if (!batched && qgemv_enabled()) {
+    if (!batched) {
         QGemvArgs q;
         q.nseg = 1;
         q.seg[0].w = m->dev;
@@ -294,7 +297,7 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
         q.ldx = (int)m->cols;
         return launch_qgemv(c, q, st);
     }
-    const size_t need = batched ? gemm_image_bytes((int)m->cols, std::min(batch, kGemmMaxBatch)) : stage_image_bytes(c, (int)m->cols, batch);
+    const size_t need = gemm_image_bytes((int)m->cols, std::min(batch, kGemmMaxBatch));
     void *pi = c->gemv_scratch.ximg;
     JUNO_TRY(ensure_device(&pi, &c->gemv_scratch.ximg_bytes, need));
     c->gemv_scratch.ximg = (uint8_t *)pi;
@@ -312,14 +315,6 @@ static int gemv_on_stream(juno_ctx *c, juno_qmat *m, const float *x, int batch, 
     sa.ldx = (int)m->cols;
     sa.K = (int)m->cols;
     sa.img = c->gemv_scratch.ximg;
-    if (!batched) {
-        sa.x = x;
-        sa.batch = batch;
-        JUNO_TRY(launch_stage(c, sa, st));
-        a.seg[0].out = y;
-        a.batch = batch;
-        return launch_gemv(c, a, st);
-    }
     // one pass over the weights per group of up to kGemmMaxBatch rows
     if (!c->gemv_scratch.xscale) {
         cudaError_t e = cudaMalloc((void **)&c->gemv_scratch.xscale, (kGemmMaxBatch + 4) * sizeof(float));  // + an error word for the tcgen05 kernel

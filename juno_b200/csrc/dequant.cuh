@@ -2,14 +2,22 @@
 // Formulas and rounding order of LlamaTransformerHandler.dequantizeQ4K/Q6K/Q8_0 (:1017-1050,
 // :1095-1135, :895-913): every product and difference is rounded separately (no FMA).
 #pragma once
+#if defined(__CUDACC__)
 #include <cuda_fp16.h>
+#endif
 #include <string.h>
 
 #include "layout.cuh"
 
+#if defined(__CUDACC__)
+#define JDQ __host__ __device__ inline
+#else
+#define JDQ inline
+#endif
+
 namespace juno {
 
-__host__ __device__ inline float dq_f16(const uint8_t *p) {
+JDQ float dq_f16(const uint8_t *p) {
     uint32_t bits = (uint32_t)p[0] | ((uint32_t)p[1] << 8);
 #if defined(__CUDA_ARCH__)
     return __half2float(__ushort_as_half((unsigned short)bits));
@@ -47,7 +55,7 @@ __host__ __device__ inline float dq_f16(const uint8_t *p) {
 #define JSUB(a, b) ((a) - (b))
 #endif
 
-__host__ __device__ inline float tile_elem_value(int type, const uint8_t *tile, int row16, int e) {
+JDQ float tile_elem_value(int type, const uint8_t *tile, int row16, int e) {
     if (type == 12) {
         const uint8_t *dm = tile + row16 * 4;
         float d = dq_f16(dm), dmin = dq_f16(dm + 2);
@@ -76,6 +84,7 @@ __host__ __device__ inline float tile_elem_value(int type, const uint8_t *tile, 
     }
 }
 
+#if defined(__CUDACC__)
 __device__ inline float raw_elem_value(int type, const uint8_t *rowp, int64_t c) {
     if (type == 0) return reinterpret_cast<const float *>(rowp)[c];
     if (type == 8) {
@@ -97,5 +106,6 @@ __device__ inline float raw_elem_value(int type, const uint8_t *rowp, int64_t c)
     return __fmul_rn(ds, (float)(q6k_raw_u6(b, e) - 32));
 }
 
+#endif
 
 }  // namespace juno

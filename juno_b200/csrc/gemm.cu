@@ -15,7 +15,6 @@
 #include <cstring>
 
 #include "gemv.cuh"
-#include "gemv_params.cuh"
 #include "layout.cuh"
 #include "tile_math.cuh"
 

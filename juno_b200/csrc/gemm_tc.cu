@@ -22,7 +22,6 @@
 #include <cstring>
 
 #include "gemv.cuh"
-#include "gemv_params.cuh"
 #include "layout.cuh"
 #include "tile_math.cuh"
 
@@ -612,6 +611,7 @@ int launch_gemm_tc(juno_ctx *ctx, const uint8_t *w, int type, int rows, int row_
     const double bpw = type == 12 ? 144.0 / 256 : type == 14 ? 210.0 / 256 : 34.0 / 32;
     const double algo = (double)rows * K * bpw * (epi == EPI_SILU_PAIR ? 2 : 1) + (double)batch * K * 4 + (double)batch * rows * 4;
     ProfScope prof(ctx, st, type == 12 ? PROF_GEMV_Q4K : type == 14 ? PROF_GEMV_Q6K : PROF_GEMV_Q80, algo);
+    ProfScope prof_tc(ctx, st, PROF_GEMM_TC, algo);
     return type == 12 ? gemm_tc_launch_type<12>(ctx, p, st) : type == 14 ? gemm_tc_launch_type<14>(ctx, p, st) : gemm_tc_launch_type<8>(ctx, p, st);
 }
 

@@ -1,5 +1,5 @@
-// Device-level interface of the fused dequant-GEMV: used by the MatVec entry points
-// and by the forward pass.
+// Resident quantised matrices and the device-level interface of the batched (9..64 sequences) dequant-GEMM:
+// used by the MatVec entry points and by the forward pass.  The 1..8 sequence GEMV is declared in qgemv.cuh.
 #pragma once
 #include "common.cuh"
 
@@ -22,9 +22,7 @@ enum StageMode {
     STAGE_RMSNORM = 1,  // r = x[i] (+ x_add[i]); optional store of r to x_out; v = (normw[i]*r)*scale  (rmsNorm :818-828)
 };
 
-// The activation as the GEMV kernels consume it: three bf16 limbs per value in MMA feed order plus the
-// per-32-column sums (layout.cuh), for batch chunks of at most `bc` rows.  Written once per product by
-// launch_stage (or by a producer kernel) and copied into shared memory by every GEMV CTA.
+// Input of a staging kernel of the batched path (launch_stage_f16).
 struct StageArgs {
     int mode = STAGE_PLAIN;
     const float *x = nullptr;  // [batch][ldx]
@@ -33,17 +31,13 @@ struct StageArgs {
     float *x_out = nullptr;
     float eps = 0.f;
     int K = 0, batch = 1;
-    uint8_t *img = nullptr;    // at least stage_image_bytes(K, batch)
+    uint8_t *img = nullptr;    // at least gemm_image_bytes(K, batch)
 };
-int gemv_batch_chunk(const juno_ctx *ctx, int K, int batch);   // rows per chunk (1..8)
-size_t stage_chunk_bytes(int K, int rows_in_chunk);
-size_t stage_image_bytes(const juno_ctx *ctx, int K, int batch);
-int launch_stage(juno_ctx *ctx, const StageArgs &a, cudaStream_t stream);
 
 enum GemvEpilogue {
     EPI_STORE = 0,       // out[b][row] = y
     EPI_SILU_PAIR = 1,   // tile rows 0-7 are gate rows, 8-15 the matching up rows: out[b][8*tile+row] = silu(gate)*up
-    EPI_RESID_NORM = 2,  // x_out = resid + y; next image = normw_next * x_out; per-task sums of x_out^2 to ss_out
+    EPI_RESID_NORM = 2,  // x_out = resid + y
 };
 
 struct GemvSeg {
@@ -57,50 +51,23 @@ struct GemvSeg {
 struct GemvArgs {
     GemvSeg seg[3];
     int nseg = 1;
-    int type = 0;     // 12 / 14 / 8, or 0 for a launch that mixes Q4_K and Q6_K segments
+    int type = 0;     // 12 / 14 / 8
     int K = 0;
     int batch = 1;
     int ld_out = 0;   // stride between batch rows of every seg.out
     int epi = EPI_STORE;
-    const uint8_t *ximg = nullptr;  // staged activation (launch_stage) for this K and batch
-    // RMSNorm of the input folded into the output: when the image holds normw*x (not yet scaled), the outputs are
-    // multiplied by 1/sqrt(sum(ss_parts[b][0..n_parts))/scale_n + eps)
-    const float *ss_parts = nullptr;
-    int n_parts = 0, ss_ld = 0, scale_n = 0;
-    float eps = 0.f;
+    const uint8_t *ximg = nullptr;  // FP16 staged activation (launch_stage_f16) for this K and batch
     // EPI_RESID_NORM
     const float *resid = nullptr;
     float *x_out = nullptr;
     int ldx = 0;
-    const float *normw_next = nullptr;
-    float *ss_out = nullptr;
-    int ss_out_ld = 0;
-    // any epilogue: also emit the output as the staged activation of the next product (K = img_next_K)
-    uint8_t *img_next = nullptr;
-    int img_next_K = 0;
     // batched path (launch_gemm): ximg is an FP16 image (launch_stage_f16) and xscale its per-row factors
     const float *xscale = nullptr;
     // optional: the same activation in the chunk-major layout of the tcgen05 kernel, and the device word that kernel
     // reports a given-up wait in; segments with enough row tiles then run on it (gemm_tc_shape_ok)
     const uint8_t *ximg_tc = nullptr;
     unsigned *tc_err = nullptr;
-    // launch_gemv only: weights of the products that follow this one in the stream; the kernel asks the L2 for them
-    // at entry (a hint: no data dependency, no completion)
-    const uint8_t *pf_next[3] = {nullptr, nullptr, nullptr};
-    size_t pf_next_bytes[3] = {0, 0, 0};
-    int pf_next_late = 0;  // ask when the CTAs run out of tasks instead (a long product followed by another long one)
 };
-// Bytes of weights a GEMV launch asks the L2 for ahead of its own loads (JUNO_L2_PREFETCH_MB, default 0 = off).
-size_t gemv_l2_prefetch_bytes();
-// Number of CTA tasks of a product = number of per-task sums of squares an EPI_RESID_NORM launch writes.
-int gemv_n_ctasks(const juno_ctx *ctx, int K, int batch, int total_row_tiles);
-
-struct GemvParams;
-// Kernel-side description of rows [b0, b0+bc) of the batch (chunk index `chunk` of the staged activation) with the
-// given CTA-task geometry.
-int gemv_fill_params(juno_ctx *ctx, const GemvArgs &a, int b0, int bc, int chunk, int kin, int tpt, int groups, int n_ctasks,
-                     GemvParams *out);
-
 // Batched path: one pass over the weights for up to kGemmMaxBatch sequences (FP16 operands on mma.sync, gemm.cu).
 // The activation is staged as ONE FP16 column per sequence, pre-scaled per row by a power of two (xscale holds the
 // factors to multiply the products with).  Epilogues: EPI_STORE, EPI_SILU_PAIR, and EPI_RESID_NORM meaning only
@@ -112,8 +79,9 @@ size_t gemm_image_bytes(int K, int batch);
 int launch_stage_f16(juno_ctx *ctx, const StageArgs &a, float *xscale, cudaStream_t stream, uint8_t *img_tc = nullptr);
 int launch_gemm(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 
-// tcgen05/TMEM version of the batched path (gemm_tc.cu), opt-in with JUNO_GEMM_TCGEN05=1, for matrices with at least
-// sm_count/2 blocks of 128 rows.  It takes its own (chunk-major) FP16 image.
+// tcgen05/TMEM version of the batched path (gemm_tc.cu): batches of at least JUNO_GEMM_TC_MIN_BATCH (48) sequences on
+// matrices with at least sm_count/2 blocks of 128 rows; JUNO_GEMM_TCGEN05=0 switches it off.  It takes its own
+// (chunk-major) FP16 image.
 bool gemm_tc_enabled();
 bool gemm_tc_shape_ok(const juno_ctx *ctx, int row_tiles, int batch);
 int gemm_tc_padded_batch(int batch);
@@ -122,8 +90,6 @@ int launch_stage_tc(juno_ctx *ctx, const float *x, int ldx, int K, int batch, ui
 int launch_gemm_tc(juno_ctx *ctx, const uint8_t *w, int type, int rows, int row_tiles, int K, int batch, const uint8_t *ximg,
                    const float *xscale, float *out, int ld_out, int epi, unsigned *err, cudaStream_t stream);
 
-// Enqueues the product on `stream`.  All pointers are device pointers.
-int launch_gemv(juno_ctx *ctx, const GemvArgs &a, cudaStream_t stream);
 // Raw-layout / FP32 fallback (one warp per output), used for shapes the tile layout does not cover.
 int launch_gemv_raw(juno_ctx *ctx, const juno_qmat *m, const float *x, int batch, float *y, cudaStream_t stream);
 int launch_dequant(juno_ctx *ctx, const juno_qmat *m, int64_t row_start, int64_t n_rows, float *out,

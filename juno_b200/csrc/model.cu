@@ -10,7 +10,6 @@
 #include <vector>
 
 #include "attn.cuh"
-#include "step.cuh"
 #include "common.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
@@ -102,7 +101,6 @@ struct LogitsView {
     }
 };
 
-constexpr int kSsLd = 1024;  // capacity of one row of per-task sums of squares
 constexpr int kArgmaxBlocks = 32;
 // First maximum (lowest index among equal values), as SampleStep.greedy (sampler/.../SampleStep.java:51-58)
 // picks after a monotone softmax.
@@ -211,7 +209,7 @@ struct juno_model {
     juno_kvpool *pool = nullptr;
     juno::NcclComm comm = nullptr;
     // activations
-    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *proj2 = nullptr, *ss = nullptr;
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *proj = nullptr, *proj2 = nullptr;
     float *hdn = nullptr, *xsc = nullptr;  // batched path: silu(gate)*up rows; per-row factors of the three FP16 images
     uint8_t *img_h_tc = nullptr;            // batched path: the hidden-size activation again, chunk-major for the tcgen05 kernel
     unsigned *tc_err = nullptr;             // device word: a wait inside the tcgen05 kernel gave up
@@ -219,7 +217,6 @@ struct juno_model {
     uint8_t *img_h = nullptr, *img_att = nullptr, *img_i = nullptr;  // staged activations (K = hidden, local heads, local FFN)
     float *logits_loc = nullptr, *logits_gather = nullptr, *logits_full = nullptr;
     float *attn_scratch = nullptr;
-    unsigned *attn_counters = nullptr;  // [max_batch][kv heads], self-resetting
     size_t attn_scratch_floats = 0;
     float2 *rope_cs = nullptr;
     int32_t *d_step = nullptr;  // tokens | positions | slots | seq_lens, max_batch each
@@ -230,11 +227,8 @@ struct juno_model {
     int last_n = 0, last_x = 0;
     double step_kv_bytes = 0;  // K+V bytes one layer's attention reads in the current step
     std::map<uint64_t, JunoGraph> graphs;
-    unsigned debug_skip = 0;  // JUNO_DEBUG_SKIP: leave kernels out of the step (results are wrong; for timing attribution only)
-    bool use_graphs = true, mix_formats = true, fused_merge = false;  // JUNO_NO_GRAPH / JUNO_NO_MIXED / JUNO_FUSED_MERGE
-    bool use_step = false;                  // JUNO_STEP_KERNEL=1: the persistent step kernel instead of one kernel per product
-    std::map<int, juno::StepPlan> step_plans;  // by number of sequences
-    juno::StepPlan *last_plan = nullptr;
+    bool use_graphs = true, mix_formats = true;  // JUNO_NO_GRAPH / JUNO_NO_MIXED
+    int batched_from = 9;  // smallest batch on the FP16 one-pass kernels (JUNO_GEMM_MIN_BATCH, read when the model is created)
 };
 
 namespace juno {
@@ -303,16 +297,49 @@ static void model_release(juno_model *m) {
         m->pool->owned_by_model = 0;
         kvpool_destroy(m->pool);
     }
-    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->proj2, m->ss, m->hdn, m->xsc, m->img_h_tc, m->tc_err, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
-                    m->attn_scratch, m->attn_counters, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
+    void *bufs[] = {m->x[0], m->x[1], m->qkv, m->att, m->proj, m->proj2, m->hdn, m->xsc, m->img_h_tc, m->tc_err, m->img_h, m->img_att, m->img_i, m->logits_loc, m->logits_gather, m->logits_full,
+                    m->attn_scratch, m->rope_cs, m->d_step, m->d_argmax, m->d_pidx, m->d_out_ids, m->d_step_counter,
                     m->d_pval, m->output_norm};
     for (void *b : bufs)
         if (b) cudaFree(b);
-    for (auto &kv : m->step_plans) step_plan_free(&kv.second);
-    m->step_plans.clear();
-    m->last_plan = nullptr;
     if (m->h_step) cudaFreeHost(m->h_step);
     m->magic = kMagicDead;
+}
+
+// The slice of a full tensor one tensor-parallel rank keeps (geometry of TensorShardContext.java:74-100 turned into
+// rows and columns): column-parallel attn_q/k/v (by head), ffn_gate/up (by FFN row) and the output projection (by
+// vocabulary row, when the vocabulary divides); row-parallel attn_output and ffn_down (whole 256-column super-blocks).
+static int tp_slice(int hidden, int n_heads, int n_kv_heads, int inter, int vocab, int kind, int rank, int world, int64_t *rows,
+                    int64_t *cols, int64_t *row0, int64_t *nrows, int64_t *col0, int64_t *ncols) {
+    JUNO_REQUIRE(hidden > 0 && n_heads > 0 && n_kv_heads > 0 && inter > 0 && vocab > 0 && hidden % n_heads == 0, "bad model dimensions");
+    JUNO_REQUIRE(world >= 1 && rank >= 0 && rank < world, "tensorRank (%d) must be < tensorWorldSize (%d)", rank, world);
+    const int64_t hd = hidden / n_heads, H = hidden, I = inter, V = vocab;
+    if (world > 1) {
+        JUNO_REQUIRE(n_heads % world == 0 && n_kv_heads % world == 0, "heads (%d query, %d kv) do not divide over %d ranks", n_heads,
+                     n_kv_heads, world);
+        JUNO_REQUIRE(inter % world == 0, "feed_forward_length %d does not divide over %d ranks", inter, world);
+    }
+    const int64_t hl = n_heads / world * hd, kl = n_kv_heads / world * hd, il = I / world;
+    const bool vshard = world > 1 && V % world == 0;
+    int64_t R = 0, C = 0, r0 = 0, nr = 0, c0 = 0, nc = 0;
+    switch (kind) {
+    case JUNO_T_TOKEN_EMBD: R = V; C = H; nr = V; nc = H; break;
+    case JUNO_T_OUTPUT: R = V; C = H; r0 = vshard ? rank * (V / world) : 0; nr = vshard ? V / world : V; nc = H; break;
+    case JUNO_T_ATTN_Q: R = H; C = H; r0 = rank * hl; nr = hl; nc = H; break;
+    case JUNO_T_ATTN_K:
+    case JUNO_T_ATTN_V: R = n_kv_heads * hd; C = H; r0 = rank * kl; nr = kl; nc = H; break;
+    case JUNO_T_ATTN_OUT: R = H; C = H; nr = H; c0 = rank * hl; nc = hl; break;
+    case JUNO_T_FFN_GATE:
+    case JUNO_T_FFN_UP: R = I; C = H; r0 = rank * il; nr = il; nc = H; break;
+    case JUNO_T_FFN_DOWN: R = H; C = I; nr = H; c0 = rank * il; nc = il; break;
+    case JUNO_T_OUTPUT_NORM:
+    case JUNO_T_ATTN_NORM:
+    case JUNO_T_FFN_NORM: R = 1; C = H; nr = 1; nc = H; break;
+    default: set_error("unknown tensor kind %d", kind); return JUNO_ERR_INVALID_ARG;
+    }
+    if (world > 1) JUNO_REQUIRE(c0 % 256 == 0 && nc % 256 == 0, "a column slice must be whole 256-column super-blocks");
+    *rows = R; *cols = C; *row0 = r0; *nrows = nr; *col0 = c0; *ncols = nc;
+    return JUNO_OK;
 }
 
 }  // namespace juno
@@ -328,6 +355,12 @@ int juno_nccl_unique_id(uint8_t *out128) {
     JUNO_NCCL_TRY(g_nccl.GetUniqueId(&id));
     memcpy(out128, id.internal, 128);
     return JUNO_OK;
+}
+
+int juno_tp_slice(int32_t hidden, int32_t n_heads, int32_t n_kv_heads, int32_t inter, int32_t vocab, int32_t kind, int32_t tp_rank,
+                  int32_t tp_world, int64_t *out6) {
+    JUNO_REQUIRE(out6, "out is null");
+    return tp_slice(hidden, n_heads, n_kv_heads, inter, vocab, kind, tp_rank, tp_world, out6, out6 + 1, out6 + 2, out6 + 3, out6 + 4, out6 + 5);
 }
 
 int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) {
@@ -374,23 +407,12 @@ int juno_model_create(juno_ctx *c, const juno_model_cfg *cfg, juno_model **out) 
     m->layers.resize(cfg->n_layers);
     const char *ng = getenv("JUNO_NO_GRAPH");
     m->use_graphs = !(ng && *ng == '1');
-    if (const char *sk = getenv("JUNO_DEBUG_SKIP")) {
-        const char *names[6] = {"qkv", "attn", "wo", "gateup", "down", "logits"};
-        for (int i = 0; i < 6; i++)
-            if (strstr(sk, names[i])) m->debug_skip |= 1u << i;
-    }
-    // merging the splits inside the attention kernel (last CTA per kv head) measured slower than the separate merge
-    // kernel on B200 (fence + atomic in every CTA, serial tail): off unless JUNO_FUSED_MERGE=1
-    const char *nm = getenv("JUNO_NO_MIXED"), *nf = getenv("JUNO_FUSED_MERGE");
+    const char *nm = getenv("JUNO_NO_MIXED");
     m->mix_formats = !(nm && *nm == '1');
     {
-        // The persistent step kernel (all products and the attention of a step in one cooperative launch) is
-        // correct but measured slower than one kernel per product on the 8B batch-1 workload (3.2-3.9 ms against
-        // 2.46 ms per step): its per-tile instruction overhead outweighs what it saves in launches.  Opt-in.
-        const char *ns = getenv("JUNO_STEP_KERNEL");
-        m->use_step = (ns && *ns == '1') && w == 1 && m->debug_skip == 0;
+        const char *gm = getenv("JUNO_GEMM_MIN_BATCH");
+        m->batched_from = std::max(2, (gm && *gm) ? atoi(gm) : 9);
     }
-    m->fused_merge = (nf && *nf == '1');
     if (w > 1) {
         int rc = nccl_load();
         if (rc == JUNO_OK) {
@@ -428,19 +450,10 @@ int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void
     if (kind == JUNO_T_ATTN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].attn_norm);
     if (kind == JUNO_T_FFN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].ffn_norm);
 
-    int64_t want_rows = 0, want_cols = 0, row0 = 0, nrows = 0, sb0 = 0, nsb = 0;
-    switch (kind) {
-    case JUNO_T_TOKEN_EMBD: want_rows = V; want_cols = H; row0 = 0; nrows = V; break;
-    case JUNO_T_OUTPUT: want_rows = V; want_cols = H; row0 = m->vocab_sharded ? (int64_t)r * m->vocab_loc : 0; nrows = m->vocab_loc; break;
-    case JUNO_T_ATTN_Q: want_rows = H; want_cols = H; row0 = (int64_t)r * m->heads_loc * hd; nrows = m->heads_loc * hd; break;
-    case JUNO_T_ATTN_K:
-    case JUNO_T_ATTN_V: want_rows = f.n_kv_heads * hd; want_cols = H; row0 = (int64_t)r * m->kv_loc * hd; nrows = m->kv_loc * hd; break;
-    case JUNO_T_ATTN_OUT: want_rows = H; want_cols = H; nrows = H; sb0 = (int64_t)r * m->heads_loc * hd / 256; nsb = m->heads_loc * hd / 256; break;
-    case JUNO_T_FFN_GATE:
-    case JUNO_T_FFN_UP: want_rows = I; want_cols = H; row0 = (int64_t)r * m->inter_loc; nrows = m->inter_loc; break;
-    case JUNO_T_FFN_DOWN: want_rows = H; want_cols = I; nrows = H; sb0 = (int64_t)r * m->inter_loc / 256; nsb = m->inter_loc / 256; break;
-    default: break;
-    }
+    int64_t want_rows = 0, want_cols = 0, row0 = 0, nrows = 0, col0 = 0, ncols = 0;
+    JUNO_TRY(tp_slice(f.hidden, f.n_heads, f.n_kv_heads, f.inter, f.vocab, kind, m->rank, m->world, &want_rows, &want_cols, &row0, &nrows,
+                      &col0, &ncols));
+    int64_t sb0 = col0 / 256, nsb = ncols / 256;
     JUNO_REQUIRE(rows == want_rows && cols == want_cols, "tensor kind %d has shape %lldx%lld, expected %lldx%lld", kind,
                  (long long)rows, (long long)cols, (long long)want_rows, (long long)want_cols);
     if (kind != JUNO_T_TOKEN_EMBD)
@@ -520,11 +533,10 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->att, (size_t)B * m->heads_loc * hd * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj, (size_t)B * H * 4));
     JUNO_TRY(dev_alloc((void **)&m->proj2, (size_t)B * H * 4));
-    JUNO_TRY(dev_alloc((void **)&m->ss, (size_t)2 * B * kSsLd * 4));
     const int Bg = std::min(B, kGemmMaxBatch);
-    JUNO_TRY(dev_alloc((void **)&m->img_h, std::max(stage_image_bytes(c, H, B), gemm_image_bytes(H, Bg))));
-    JUNO_TRY(dev_alloc((void **)&m->img_att, std::max(stage_image_bytes(c, m->heads_loc * hd, B), gemm_image_bytes(m->heads_loc * hd, Bg))));
-    JUNO_TRY(dev_alloc((void **)&m->img_i, std::max(stage_image_bytes(c, m->inter_loc, B), gemm_image_bytes(m->inter_loc, Bg))));
+    JUNO_TRY(dev_alloc((void **)&m->img_h, gemm_image_bytes(H, Bg)));
+    JUNO_TRY(dev_alloc((void **)&m->img_att, gemm_image_bytes(m->heads_loc * hd, Bg)));
+    JUNO_TRY(dev_alloc((void **)&m->img_i, gemm_image_bytes(m->inter_loc, Bg)));
     JUNO_TRY(dev_alloc((void **)&m->hdn, (size_t)B * m->inter_loc * 4));
     JUNO_TRY(dev_alloc((void **)&m->xsc, (size_t)3 * B * 4));
     JUNO_TRY(dev_alloc((void **)&m->img_h_tc, gemm_tc_image_bytes(H, Bg)));
@@ -537,8 +549,6 @@ extern "C" int juno_model_finalize(juno_model *m) {
     }
     m->attn_scratch_floats = (size_t)(c->sm_count * 4 + B * m->kv_loc) * (m->heads_loc / m->kv_loc) * (hd + 2) + 64;
     JUNO_TRY(dev_alloc((void **)&m->attn_scratch, m->attn_scratch_floats * 4));
-    JUNO_TRY(dev_alloc((void **)&m->attn_counters, (size_t)B * m->heads_loc * 4));
-    JUNO_CUDA_TRY(cudaMemset(m->attn_counters, 0, (size_t)B * m->heads_loc * 4));
     JUNO_TRY(dev_alloc((void **)&m->rope_cs, (size_t)B * (hd / 2) * sizeof(float2)));
     JUNO_TRY(dev_alloc((void **)&m->d_step, (size_t)4 * B * 4));
     JUNO_TRY(dev_alloc((void **)&m->d_argmax, (size_t)B * 4));
@@ -578,80 +588,10 @@ static int gemv_group(juno_model *m, juno_qmat *const *mats, float *const *outs,
         }
         a.type = mixed ? 0 : mats[i]->type;
         a.K = (int)mats[i]->cols;
-        JUNO_TRY(a.xscale ? launch_gemm(m->ctx, a, st) : launch_gemv(m->ctx, a, st));
+        JUNO_TRY(launch_gemm(m->ctx, a, st));
         i = j;
     }
     return JUNO_OK;
-}
-
-static int stage_rms(juno_model *m, int n, const float *x, const float *add, float *x_out, const float *normw,
-                     cudaStream_t st) {
-    StageArgs a;
-    a.mode = STAGE_RMSNORM;
-    a.x = x;
-    a.ldx = m->cfg.hidden;
-    a.x_add = add;
-    a.x_out = x_out;
-    a.normw = normw;
-    a.eps = m->cfg.rms_eps;
-    a.K = m->cfg.hidden;
-    a.batch = n;
-    a.img = m->img_h;
-    return launch_stage(m->ctx, a, st);
-}
-
-// A row-parallel projection (Wo or Wdown) followed by "residual add, RMSNorm with the next norm weights, stage".
-// Single GPU: all fused into the GEMV epilogue (the 1/rms factor is applied by the consumer from per-task sums of
-// squares).  Tensor parallel: the partial products are all-reduced first, then one staging kernel does the rest.
-static void prefetch_after(GemvArgs &a, juno_qmat *const *next, int n_next, bool late) {
-    for (int i = 0; i < n_next && i < 3; i++) {
-        a.pf_next[i] = next[i] ? next[i]->dev : nullptr;
-        a.pf_next_bytes[i] = (next[i] && next[i]->tiled) ? next[i]->bytes : 0;
-    }
-    a.pf_next_late = late ? 1 : 0;
-}
-
-static int proj_resid_norm(juno_model *m, int n, juno_qmat *w, const uint8_t *ximg, int &cur, const float *normw_next,
-                           float *ss_out, bool *consumer_scales, juno_qmat *const *next, int n_next, cudaStream_t st) {
-    const int H = m->cfg.hidden;
-    GemvArgs a;
-    a.batch = n;
-    a.ximg = ximg;
-    prefetch_after(a, next, n_next, false);
-    juno_qmat *mats[1] = {w};
-    if (m->world == 1) {
-        a.epi = EPI_RESID_NORM;
-        a.resid = m->x[cur];
-        a.x_out = m->x[cur ^ 1];
-        a.ldx = H;
-        a.normw_next = normw_next;
-        a.ss_out = ss_out;
-        a.ss_out_ld = kSsLd;
-        a.img_next = m->img_h;
-        a.img_next_K = H;
-        float *outs[1] = {nullptr};
-        JUNO_TRY(gemv_group(m, mats, outs, 1, a, st));
-        *consumer_scales = true;
-    } else {
-        a.epi = EPI_STORE;
-        a.ld_out = H;
-        float *outs[1] = {m->proj};
-        JUNO_TRY(gemv_group(m, mats, outs, 1, a, st));
-        JUNO_NCCL_TRY(g_nccl.AllReduce(m->proj, m->proj, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
-        JUNO_TRY(stage_rms(m, n, m->x[cur], m->proj, m->x[cur ^ 1], normw_next, st));
-        *consumer_scales = false;
-    }
-    cur ^= 1;
-    return JUNO_OK;
-}
-
-static void set_input_scale(juno_model *m, GemvArgs &a, bool scaled_by_consumer, const float *ss, int n_parts) {
-    if (!scaled_by_consumer) return;
-    a.ss_parts = ss;
-    a.n_parts = n_parts;
-    a.ss_ld = kSsLd;
-    a.scale_n = m->cfg.hidden;
-    a.eps = m->cfg.rms_eps;
 }
 
 // Layers and output projection of one step on the batched path (n >= gemm_min_batch()): every product is ONE pass
@@ -888,55 +828,11 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
     return JUNO_OK;
 }
 
-// Whether this model and batch size run through the persistent step kernel.
-static bool step_model_ok(juno_model *m, int n) {
-    if (m->world != 1) return false;
-    int max_K = std::max(m->cfg.hidden, std::max(m->heads_loc * m->hd, m->inter_loc));
-    int max_tile = 0;
-    auto visit = [&](const juno_qmat *q) {
-        if (!q) return true;
-        if (!q->tiled || (q->type != 12 && q->type != 14 && q->type != 8)) return false;
-        max_tile = std::max(max_tile, tile_bytes(q->type));
-        return true;
-    };
-    for (const JunoLayer &L : m->layers)
-        for (int k : {JUNO_T_ATTN_Q, JUNO_T_ATTN_K, JUNO_T_ATTN_V, JUNO_T_ATTN_OUT, JUNO_T_FFN_GATE, JUNO_T_FFN_DOWN})
-            if (!visit(L.w[k])) return false;
-    if (!visit(m->output)) return false;
-    // the staged activations must be single chunks (the step kernel copies one image per product)
-    for (int K : {m->cfg.hidden, m->heads_loc * m->hd, m->inter_loc})
-        if (gemv_batch_chunk(m->ctx, K, n) != n) return false;
-    return step_supported(m->ctx, n, m->hd, m->heads_loc, m->kv_loc, max_K, max_tile);
-}
-
 static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
     const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
-    const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
-    // Persistent step kernel: the products and the attention below are recorded as phases (once per batch size) and
-    // run as one cooperative launch.
-    StepPlan *plan = nullptr;
-    StepRecorder rec;
-    if (m->use_step && step_model_ok(m, n)) {
-        plan = &m->step_plans[n];
-        if (!plan->d_phases) {
-            rec.grid = c->sm_count;
-            rec.n = n;
-            c->step_rec = &rec;
-        }
-    }
-    struct RecGuard {
-        juno_ctx *c;
-        ~RecGuard() { c->step_rec = nullptr; }
-    } rec_guard{c};
-    const bool replay = (plan && plan->d_phases) || (m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0) ||
-                        (!plan && qgemv_enabled() && n <= 8 && m->debug_skip == 0);
-    float *ss_o = m->ss, *ss_d = m->ss + (size_t)B * kSsLd;  // sums of squares written by Wo / Wdown epilogues
-    const int parts_o = gemv_n_ctasks(c, Hl, n, H / 16), parts_d = gemv_n_ctasks(c, Il, n, H / 16);
-    JUNO_REQUIRE(parts_o <= kSsLd && parts_d <= kSsLd, "hidden size %d needs more than %d partial sums", H, kSsLd);
-
     // embedding lookup -> x[0]
     {
         juno_qmat *e = m->tok_embd;
@@ -948,103 +844,13 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
     }
     JUNO_TRY(launch_rope_table(c, d_pos, n, hd, f.rope_theta, m->rope_cs, st));
     int cur = 0;          // x[cur] holds the residual stream
-    const bool batched = m->hdn && n >= gemm_min_batch() && n <= kGemmMaxBatch && m->debug_skip == 0;
-    const bool qpath = !batched && !plan && qgemv_enabled() && n <= 8 && m->debug_skip == 0;
-    if (batched) JUNO_TRY(enqueue_layers_batched(m, n, d_slot, d_len, n_splits, cur, st));
-    else if (qpath) JUNO_TRY(enqueue_layers_q(m, n, d_slot, d_len, n_splits, cur, st));
-    else JUNO_TRY(stage_rms(m, n, m->x[0], nullptr, nullptr, m->layers[0].attn_norm, st));
-
-    bool scaled = false;  // img_h holds normw*x and the consumer still has to apply 1/rms
-    for (int l = 0; l < f.n_layers && !replay; l++) {
-        JunoLayer &L = m->layers[l];
-        // q,k,v = W·rmsNorm(x)
-        {
-            GemvArgs a;
-            a.batch = n;
-            a.ximg = m->img_h;
-            a.ld_out = m->qkv_ld;
-            set_input_scale(m, a, scaled, ss_d, parts_d);
-            juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
-            float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
-            prefetch_after(a, &L.w[JUNO_T_ATTN_OUT], 1, true);  // HBM is nearly idle during the attention
-            if (!(m->debug_skip & 1u)) JUNO_TRY(gemv_group(m, qkv_m, qkv_o, 3, a, st));
-        }
-        AttnArgs at;
-        at.pool = m->pool;
-        at.layer = l;
-        at.n = n;
-        at.n_heads = m->heads_loc;
-        at.q = m->qkv;
-        at.ldq = m->qkv_ld;
-        at.out = m->att;
-        at.slots = d_slot;
-        at.seq_lens = d_len;
-        at.n_splits = n_splits;
-        at.part_o = m->attn_scratch;
-        at.part_ml = m->attn_scratch + (size_t)n * m->heads_loc * n_splits * hd;
-        at.algo_bytes = m->step_kv_bytes;
-        at.rope_cs = m->rope_cs;  // q, k are rotated and k, v appended inside the attention kernel
-        at.knew = m->qkv + Hl;
-        at.vnew = m->qkv + Hl + KVl;
-        at.ldkv = m->qkv_ld;
-        at.merge_counters = (m->fused_merge || c->step_rec) ? m->attn_counters : nullptr;
-        at.stage_img = m->img_att;  // the merge writes Wo's staged input directly
-        at.stage_bc = gemv_batch_chunk(c, Hl, n);
-        at.stage_chunk_stride = stage_chunk_bytes(Hl, at.stage_bc);
-        if (!(m->debug_skip & 2u)) JUNO_TRY(launch_attn(c, at, st));
-        // x2 = x + Wo·att ; staged rmsNorm(x2, ffn_norm)
-        if (!(m->debug_skip & 4u))
-            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_ATTN_OUT], m->img_att, cur, L.ffn_norm, ss_o, &scaled,
-                                     &L.w[JUNO_T_FFN_GATE], 1, st));
-        // hdn = silu(Wgate·xn2) * (Wup·xn2), emitted as Wdown's staged input
-        {
-            GemvArgs a;
-            a.batch = n;
-            a.ximg = m->img_h;
-            a.epi = EPI_SILU_PAIR;
-            a.ld_out = Il;
-            a.img_next = m->img_i;
-            a.img_next_K = Il;
-            set_input_scale(m, a, scaled, ss_o, parts_o);
-            juno_qmat *gu_m[1] = {L.w[JUNO_T_FFN_GATE]};
-            float *gu_o[1] = {nullptr};
-            prefetch_after(a, &L.w[JUNO_T_FFN_DOWN], 1, true);
-            if (!(m->debug_skip & 8u)) JUNO_TRY(gemv_group(m, gu_m, gu_o, 1, a, st));
-        }
-        // x = x2 + Wdown·hdn ; staged rmsNorm(x, next norm)
-        const float *next_norm = (l + 1 < f.n_layers) ? m->layers[l + 1].attn_norm : m->output_norm;
-        juno_qmat *after_down[3] = {m->output, nullptr, nullptr};
-        int n_after = 1;
-        if (l + 1 < f.n_layers) {
-            JunoLayer &N = m->layers[l + 1];
-            after_down[0] = N.w[JUNO_T_ATTN_Q], after_down[1] = N.w[JUNO_T_ATTN_K], after_down[2] = N.w[JUNO_T_ATTN_V];
-            n_after = 3;
-        }
-        if (!(m->debug_skip & 16u))
-            JUNO_TRY(proj_resid_norm(m, n, L.w[JUNO_T_FFN_DOWN], m->img_i, cur, next_norm, ss_d, &scaled, after_down,
-                                     n_after, st));
-    }
-    // logits = Wout · rmsNorm(x, output_norm)
-    if (!replay) {
-        GemvArgs a;
-        a.batch = n;
-        a.ximg = m->img_h;
-        a.ld_out = m->vocab_loc;
-        set_input_scale(m, a, scaled, ss_d, parts_d);
-        juno_qmat *l_m[1] = {m->output};
-        float *l_o[1] = {m->logits_loc};
-        if (!(m->debug_skip & 32u)) JUNO_TRY(gemv_group(m, l_m, l_o, 1, a, st));
-    }
-    if (plan) {
-        if (c->step_rec) {
-            c->step_rec = nullptr;
-            JUNO_TRY(step_plan_build(c, rec, m->pool->dtype == 1, hd, m->heads_loc / m->kv_loc, plan));
-            plan->timeline_period = (plan->n_phases - 1) / std::max(1, f.n_layers);
-        }
-        JUNO_TRY(launch_step(c, *plan, st));
-        m->last_plan = plan;
-        cur = 0;  // every layer flips the residual buffer twice
-    }
+    // 9..64 sequences: one pass over the weights per product on the FP16 tensor-core kernels; otherwise the exact
+    // integer-MMA GEMV (batches above 64 in chunks of up to eight sequences per pass)
+    const bool batched = n >= m->batched_from && n <= kGemmMaxBatch;
+    if (batched)
+        JUNO_TRY(enqueue_layers_batched(m, n, d_slot, d_len, n_splits, cur, st));
+    else
+        JUNO_TRY(enqueue_layers_q(m, n, d_slot, d_len, n_splits, cur, st));
     m->last_x = cur;
     LogitsView lv;
     lv.n = n;
@@ -1127,12 +933,14 @@ static int step_check(juno_model *m) {
             return JUNO_ERR_CUDA;
         }
     }
-    if (!m->last_plan) return JUNO_OK;
-    const unsigned code = step_plan_error(*m->last_plan);
-    if (!code) return JUNO_OK;
-    set_error("decode step kernel gave up waiting (code %u, warp %u of block %u; codes: 1 grid barrier, 2 weight tile, 4 activation, "
-              "5/6 partial sums, 7/8 task hand-over, 9 copy cursor)", code & 0xffu, (code >> 8) & 0xffu, code >> 16);
-    return JUNO_ERR_CUDA;
+    juno_ctx *c = m->ctx;
+    const unsigned code = c->gemv_scratch.qerr_host ? *reinterpret_cast<volatile unsigned *>(c->gemv_scratch.qerr_host) : 0u;
+    if (code) {
+        *reinterpret_cast<volatile unsigned *>(c->gemv_scratch.qerr_host) = 0u;
+        set_error("a GEMV warp gave up waiting for a weight tile (warp %u of block %u)", (code >> 8) & 0xffu, code >> 16);
+        return JUNO_ERR_TIMEOUT;
+    }
+    return JUNO_OK;
 }
 
 static int bucket_len(int len) {
@@ -1156,6 +964,9 @@ static int prepare_step(juno_model *m, int n, juno_seq *const *seqs, const int32
         for (int j = 0; j < i; j++) JUNO_REQUIRE(seqs[j] != s, "sequence listed twice in one step");
         JUNO_REQUIRE(positions[i] >= 0 && positions[i] + extra_positions < m->cfg.max_ctx,
                      "position %d is beyond max_ctx %d", positions[i] + extra_positions, m->cfg.max_ctx);
+        // a position beyond the sequence's length would make attention read cache rows that were never written
+        // (pages come back from the free list as they were left)
+        JUNO_REQUIRE(positions[i] <= s->len, "sequence %d: position %d leaves a gap after its %d cached positions", i, positions[i], s->len);
         JUNO_TRY(seq_reserve(s, positions[i] + 1 + extra_positions, c->stream));
         m->h_step[i] = tokens[i];
         m->h_step[B + i] = positions[i];
@@ -1231,6 +1042,7 @@ int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t
     JUNO_REQUIRE(seq && seq->magic == kMagicSeq && seq->pool == m->pool, "sequence is closed or belongs to another model");
     JUNO_REQUIRE(token_ids && n_tokens >= 1 && start_pos >= 0, "bad prefill arguments (n_tokens=%d, start_pos=%d)", n_tokens, start_pos);
     JUNO_REQUIRE(start_pos + n_tokens <= m->cfg.max_ctx, "position %d is beyond max_ctx %d", start_pos + n_tokens - 1, m->cfg.max_ctx);
+    JUNO_REQUIRE(start_pos <= seq->len, "start position %d leaves a gap after the %d cached positions", start_pos, seq->len);
     JUNO_REQUIRE(m->pool->dtype == 0 || m->pool->dtype == 1, "unsupported KV type");
     const juno_model_cfg &f = m->cfg;
     const int B = f.max_batch, chunk_max = std::min(B, kGemmMaxBatch), V = f.vocab;

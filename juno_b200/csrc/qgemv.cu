@@ -494,7 +494,7 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, unsigned parity,
     const long long t0 = clock64(), limit = failed ? kQWaitLimitAfterFail : kQWaitLimitClk;
     while (!mbar_test(bar, parity, ns)) {
         if (clock64() - t0 > limit) {
-            if (!failed && (threadIdx.x & 31) == 0) atomicCAS(err, 0u, 1u | ((threadIdx.x >> 5) << 8) | (blockIdx.x << 16));
+            if (!failed && (threadIdx.x & 31) == 0) *reinterpret_cast<volatile unsigned *>(err) = 1u | ((threadIdx.x >> 5) << 8) | (blockIdx.x << 16);
             failed = true;
             return;
         }
@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
             // rmsNorm (:818-828): 1f / (float) Math.sqrt(ss / n + eps)
             sc = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(s, (float)p.K), p.eps)));
         }
-        rs_s[tid] = sc;  // read by the warps that finish tasks: ordered by the counters they go through
+        rs_s[tid] = sc;  // read by the warps that finish tasks: ordered by the task barriers
     }
 
     LaneX<NT> L;

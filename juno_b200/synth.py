@@ -113,11 +113,18 @@ def tensor_shape(arch: Arch, kind: int):
             T_OUTPUT_NORM: (1, H), T_ATTN_NORM: (1, H), T_FFN_NORM: (1, H)}[kind]
 
 
-def random_model(arch: Arch, seed: int, type_map=q4_k_m_type):
+def random_model(arch: Arch, seed: int, type_map=q4_k_m_type, norm: str = "ones"):
     """Yields (kind, layer, ggml_type, rows, cols, uint8 blocks) in a fixed order:
-    token_embd, output_norm, output, then per layer attn_norm, ffn_norm, q, k, v, o, gate, up, down."""
+    token_embd, output_norm, output, then per layer attn_norm, ffn_norm, q, k, v, o, gate, up, down.
+    norm="ones": RMSNorm weights of 1.0 (the benchmark configurations); norm="random": 1 + 0.3*N(0,1), drawn per
+    vector from a generator of their own, so that the matrices of a seed are the same either way."""
     rng = np.random.default_rng(seed)
-    ones = np.ones(arch.hidden, dtype=np.float32).view(np.uint8)
+    rng_norm = np.random.default_rng([seed, 0x6E6F726D])
+
+    def norm_vec():
+        if norm == "ones":
+            return np.ones(arch.hidden, dtype=np.float32).view(np.uint8)
+        return (1.0 + 0.3 * rng_norm.standard_normal(arch.hidden)).astype(np.float32).view(np.uint8)
 
     def mat(kind, layer):
         rows, cols = tensor_shape(arch, kind)
@@ -125,10 +132,10 @@ def random_model(arch: Arch, seed: int, type_map=q4_k_m_type):
         return kind, layer, t, rows, cols, random_blocks(rng, t, rows, cols)
 
     yield mat(T_TOKEN_EMBD, 0)
-    yield T_OUTPUT_NORM, 0, F32, 1, arch.hidden, ones
+    yield T_OUTPUT_NORM, 0, F32, 1, arch.hidden, norm_vec()
     yield mat(T_OUTPUT, 0)
     for l in range(arch.n_layers):
-        yield T_ATTN_NORM, l, F32, 1, arch.hidden, ones
-        yield T_FFN_NORM, l, F32, 1, arch.hidden, ones
+        yield T_ATTN_NORM, l, F32, 1, arch.hidden, norm_vec()
+        yield T_FFN_NORM, l, F32, 1, arch.hidden, norm_vec()
         for kind in (T_ATTN_Q, T_ATTN_K, T_ATTN_V, T_ATTN_OUT, T_FFN_GATE, T_FFN_UP, T_FFN_DOWN):
             yield mat(kind, l)

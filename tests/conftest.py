@@ -45,6 +45,24 @@ def oracle():
 
 
 @pytest.fixture(scope="session")
+def layout_host():
+    """Test-only host build (C++ compiler, no CUDA) of the tile-layout index maps the device kernels use."""
+    import ctypes as C
+    import subprocess
+    src = os.path.join(ROOT, "tests", "native", "layout_host.cpp")
+    so = os.path.join(ROOT, "tests", "native", "liblayout_host.so")
+    deps = [src] + [os.path.join(ROOT, "juno_b200", "csrc", f) for f in ("layout.cuh", "dequant.cuh", "repack.cuh")]
+    if not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(d) for d in deps):
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-shared", "-fPIC", "-o", so, src])
+    L = C.CDLL(so)
+    L.layout_tiled_bytes.restype = C.c_int64
+    L.layout_tiled_bytes.argtypes = [C.c_int, C.c_int64, C.c_int64]
+    L.layout_repack.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    L.layout_dequant_tiled.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    return L
+
+
+@pytest.fixture(scope="session")
 def ctx():
     from juno_b200.matvec import GpuContext
     return GpuContext.shared(0)

@@ -1,5 +1,5 @@
-"""CPU checks of the product library: it loads, exports every symbol the header declares, and its
-tile layout round-trips bit-exactly (host mirrors of the device repack / dequantise index maps)."""
+"""CPU checks of the product library: it loads and exports every symbol the header declares (and nothing else with
+the juno_ prefix); the tile layout round-trips bit-exactly through a host build of the device index maps."""
 import ctypes as C
 import os
 import re
@@ -20,6 +20,11 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(L, name), name
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    # no undeclared juno_* export (debug hooks do not belong in the product library)
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    exported = {ln.split()[-1] for ln in out.splitlines() if ln.split() and ln.split()[-1].startswith("juno_")}
+    assert exported == declared, exported ^ declared
 
 
 def test_cfg_struct_matches_header():
@@ -46,19 +51,15 @@ def test_null_and_closed_handles_return_codes():
 
 @pytest.mark.parametrize("t", [synth.Q4_K, synth.Q6_K, synth.Q8_0])
 @pytest.mark.parametrize("rows,cols", [(16, 256), (37, 512), (5, 1024)])
-def test_tile_layout_round_trip_bit_exact(oracle, t, rows, cols):
-    L = C.CDLL(_lib.LIB_PATH)
-    L.juno_dbg_tiled_bytes.restype = C.c_int64
-    L.juno_dbg_tiled_bytes.argtypes = [C.c_int, C.c_int64, C.c_int64]
-    L.juno_dbg_repack_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
-    L.juno_dbg_dequant_tiled_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+def test_tile_layout_round_trip_bit_exact(oracle, layout_host, t, rows, cols):
+    L = layout_host
     raw = synth.random_blocks(np.random.default_rng(t), t, rows, cols)
-    n = L.juno_dbg_tiled_bytes(t, rows, cols)
+    n = L.layout_tiled_bytes(t, rows, cols)
     assert n == ((rows + 15) // 16) * (cols // 256) * {12: 2368, 14: 3360, 8: 4352}[t]
     tiles = np.zeros(n, dtype=np.uint8)
-    assert L.juno_dbg_repack_host(t, raw.ctypes.data, rows, cols, tiles.ctypes.data) == 0
+    assert L.layout_repack(t, raw.ctypes.data, rows, cols, tiles.ctypes.data) == 0
     out = np.empty((rows, cols), dtype=np.float32)
-    assert L.juno_dbg_dequant_tiled_host(t, tiles.ctypes.data, rows, cols, out.ctypes.data) == 0
+    assert L.layout_dequant_tiled(t, tiles.ctypes.data, rows, cols, out.ctypes.data) == 0
     ref = oracle.dequantize(t, raw, rows, cols)
     assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
 

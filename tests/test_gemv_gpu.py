@@ -53,6 +53,64 @@ def test_gemv_large_batch(mv, oracle, t, batch):
     A.close()
 
 
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("rows,cols,batch", [(9616, 4096, 48), (9601, 2048, 64), (14336, 4096, 50)])
+def test_gemm_tcgen05_route_matches_oracle(ctx, mv, oracle, t, rows, cols, batch):
+    """Batches of 48..64 sequences on matrices with at least sm_count/2 blocks of 128 rows take the tcgen05/TMEM
+    kernel: ragged row counts, a batch that is not a multiple of 16, all three block formats, and the launch is
+    seen in the profile category of that kernel."""
+    rng = np.random.default_rng(7)
+    raw = synth.random_blocks(rng, t, rows, cols)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    A = mv.upload_quantized(raw, t, rows, cols)
+    ctx.profile(True)
+    ctx.profile_read()
+    y = mv.sgemv(A, x)
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    assert prof["gemm_tcgen05"]["launches"] >= 1, prof
+    ref = oracle.matvec(t, raw, x, rows, cols)
+    assert rel_err(y, ref) < TOL, rel_err(y, ref)
+    A.close()
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("rows,cols", [(14336, 4096), (4096, 14336), (128256, 4096)])
+def test_gemv_sweep_shapes_batched(mv, oracle, t, rows, cols):
+    """The operator sweep's shapes at batch 16 and 64 (one upload per shape; on the largest shape the oracle
+    checks a sample of the sequences)."""
+    rng = np.random.default_rng(1)
+    raw = synth.random_blocks(rng, t, rows, cols)
+    A = mv.upload_quantized(raw, t, rows, cols)
+    for batch in (16, 64):
+        x = rng.standard_normal((batch, cols)).astype(np.float32)
+        y = mv.sgemv(A, x)
+        pick = list(range(batch)) if rows < 100000 else [0, batch // 2, batch - 1]
+        ref = oracle.matvec(t, raw, x[pick], rows, cols)
+        assert rel_err(y[pick], ref) < TOL, (batch, rel_err(y[pick], ref))
+    A.close()
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_gemv_exact_path_batches_up_to_eight(mv, oracle, t):
+    """1..8 sequences run on the integer tensor-core kernel, whose products are exact: the result differs from the
+    oracle only by FP32 summation order (1e-5), outliers in the activation included."""
+    rows, cols = 1000, 4096
+    rng = np.random.default_rng(9)
+    raw = synth.random_blocks(rng, t, rows, cols)
+    A = mv.upload_quantized(raw, t, rows, cols)
+    for batch in (1, 2, 3, 5, 8):
+        x = rng.standard_normal((batch, cols)).astype(np.float32)
+        x[:, ::7] *= 30.0
+        x[:, 5] = 0.0
+        y = mv.sgemv(A, x)
+        ref = oracle.matvec(t, raw, x, rows, cols)
+        assert rel_err(y, ref) < 1e-5, (batch, rel_err(y, ref))
+    zero = mv.sgemv(A, np.zeros(cols, dtype=np.float32))
+    assert not zero.any()
+    A.close()
+
+
 def test_gemv_sweep_shape_logits(mv, oracle):
     """The largest shape of the operator sweep: 128256 x 4096 Q4_K, batch 1."""
     rows, cols = 128256, 4096

@@ -6,7 +6,8 @@ import socket
 import numpy as np
 import pytest
 
-from juno_b200 import shard, synth
+import shardutil as shard
+from juno_b200 import synth
 
 ARCH = synth.Arch(hidden=512, n_layers=1, n_heads=4, n_kv_heads=2, inter=1024, vocab=512)
 
@@ -90,16 +91,15 @@ def test_two_rank_tensor_parallel_layer_matches_unsharded():
 
 def test_slice_rules():
     a = synth.LLAMA3_8B
-    shard.check(a, 8)
     assert shard.slice_spec(a, synth.T_ATTN_Q, 3, 8) == (3 * 512, 512, 0, 4096)
     assert shard.slice_spec(a, synth.T_ATTN_K, 3, 8) == (3 * 128, 128, 0, 4096)      # one kv head per GPU
     assert shard.slice_spec(a, synth.T_ATTN_OUT, 3, 8) == (0, 4096, 3 * 512, 512)
     assert shard.slice_spec(a, synth.T_FFN_DOWN, 7, 8) == (0, 4096, 7 * 1792, 1792)  # 7 super-blocks per rank
     assert shard.slice_spec(a, synth.T_OUTPUT, 1, 8) == (16032, 16032, 0, 4096)
     with pytest.raises(ValueError):
-        shard.check(synth.TINYLLAMA, 8)  # 4 kv heads do not divide over 8 ranks
+        shard.slice_spec(synth.TINYLLAMA, synth.T_ATTN_K, 0, 8)  # 4 kv heads do not divide over 8 ranks
     with pytest.raises(ValueError):
-        shard.check(synth.Arch(512, 1, 3, 3, 1024, 512), 3)
+        shard.slice_spec(synth.Arch(512, 1, 3, 3, 1024, 512), synth.T_ATTN_Q, 0, 3)
     rng = np.random.default_rng(0)
     blk = synth.random_blocks(rng, synth.Q4_K, 4, 512)
     sl = shard.slice_blocks(blk, synth.Q4_K, 4, 512, 1, 2, 256, 256)

@@ -17,12 +17,15 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3  # the tolerance of the attention parity tests
 
 
-def test_static_scratch_attention_matches_regular_entry_twice(ctx):
+@pytest.mark.parametrize("kv_dtype,lens", [("f16", [700, 129, 16, 2048]), ("f32", [700, 129, 16, 2048]), ("f16", [9000])],
+                         ids=["f16-pages", "f32-pages", "long-context"])
+def test_static_scratch_attention_matches_regular_entry_twice(ctx, kv_dtype, lens):
+    """FP16 pages with few context splits merge on chip and leave the array idle; FP32 pages and a long context (more
+    splits than one thread-block cluster holds) put their split partials into it."""
     import torch
     rng = np.random.default_rng(42)
     n_heads, n_kv, hd = 32, 8, 128
-    lens = [700, 129, 16, 2048]
-    cache = PagedKvCache(ctx, 1, n_kv, hd, sum((l + 15) // 16 for l in lens) + 2, "f16")
+    cache = PagedKvCache(ctx, 1, n_kv, hd, sum((l + 15) // 16 for l in lens) + 2, kv_dtype)
     seqs = []
     for l in lens:
         s = cache.new_sequence(l)
@@ -37,9 +40,12 @@ def test_static_scratch_attention_matches_regular_entry_twice(ctx):
         q_dev = torch.from_numpy(q).cuda()
         out_dev = torch.full_like(q_dev, float("nan"))
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         check(L.juno_attn_decode_static(ctx.handle, cache.handle, 0, len(seqs), arr, n_heads,
                                         C.c_void_p(q_dev.data_ptr()), C.c_void_p(out_dev.data_ptr())),
               "juno_attn_decode_static")
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)  # the call took no device memory (cudaMemGetInfo)
         got = out_dev.cpu().numpy()
         assert np.isfinite(got).all()
         assert rel_err(got, want) < TOL, (call, rel_err(got, want))
