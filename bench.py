@@ -89,18 +89,28 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.sm)}
 
 
-def cpu_decode_rate(arch, tensors, budget_s: float, threads: int | None = None):
-    """Times the CPU oracle on a bounded sample: decode steps at an empty context through the first L' layers plus
-    the output projection, scaled to the full model by quantised weight bytes.  Returns (tok/s, cores, sample)."""
+def host_cores() -> int:
+    """Cores this process may run on.  (torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the CPU arm sets
+    its thread count from this instead.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_decode_rate(arch, tensors, budget_s: float, ctx_len: int = 0):
+    """Times the CPU oracle on a bounded sample: batch-1 decode steps at context `ctx_len` (the KV cache of the sample
+    layers is pre-filled with pseudo-random rows) through the first L' layers plus the output projection, on all host
+    cores, scaled to the full model: the layer part by the number of layers, the output projection once.
+    Returns (tok/s, cores, sample)."""
     from oracle import oracle as o
     o.build()
-    if threads:
-        o.set_num_threads(threads)
+    o.set_num_threads(host_cores())
     cores = o.num_threads()
-    # one layer + logits first, to size the sample
+
     def build(n_layers):
         m = o.Model(arch.hidden, n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab, arch.rms_eps,
-                    arch.rope_theta, kv_f16=False, max_seq=64)
+                    arch.rope_theta, kv_f16=False, max_seq=ctx_len + 64)
         for kind, layer, t, rows, cols, blocks in tensors:
             if kind > synth.T_OUTPUT and layer >= n_layers:
                 continue
@@ -111,65 +121,74 @@ def cpu_decode_rate(arch, tensors, budget_s: float, threads: int | None = None):
         a = synth.Arch(arch.hidden, n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab)
         return weight_bytes(a)
 
+    def timed(m, steps, first_pos):
+        s = m.new_seq()
+        if first_pos:
+            s.fill(first_pos, seed=2)
+        t0 = time.perf_counter()
+        for i in range(steps):
+            m.forward(s, 1 + i, first_pos + i)
+        return (time.perf_counter() - t0) / steps
+
+    # the output projection alone (a model of zero layers is not allowed: one layer, then subtract it below)
     probe = build(1)
-    s = probe.new_seq()
-    t0 = time.perf_counter()
-    probe.forward(s, 1, 0)
-    t1 = time.perf_counter() - t0
+    t_one = timed(probe, 2, ctx_len)
     probe.close()
-    per_byte = t1 / sample_bytes(1)
-    # choose layers so that ~4 steps fit the budget
-    want = budget_s / 4 / per_byte
-    n_layers = arch.n_layers
-    while n_layers > 1 and sample_bytes(n_layers) > want:
-        n_layers -= 1
+    # choose layers so that a handful of steps fit the budget
+    n_layers = max(2, min(arch.n_layers, int(budget_s / 4 / max(t_one, 1e-6))))
     m = build(n_layers)
-    s = m.new_seq()
-    steps = 0
-    t0 = time.perf_counter()
-    while steps < 4 or (time.perf_counter() - t0 < budget_s * 0.6 and steps < 32):
-        m.forward(s, 1 + steps, steps)
-        steps += 1
-    dt = (time.perf_counter() - t0) / steps
+    steps = max(2, min(16, int(budget_s * 0.6 / max(t_one * n_layers, 1e-6))))
+    t_n = timed(m, steps, ctx_len)
     m.close()
-    scale = weight_bytes(arch) / sample_bytes(n_layers)
-    sample = (f"{steps} batch-1 decode steps at positions 0..{steps - 1} through layers 0..{n_layers - 1} + output "
-              f"projection ({sample_bytes(n_layers) / 1e9:.2f} GB of blocks/step), time scaled x{scale:.2f} by weight bytes")
-    return 1.0 / (dt * scale), cores, sample
+    per_layer = max(0.0, (t_n - t_one) / (n_layers - 1))
+    t_out = max(0.0, t_one - per_layer)
+    dt = per_layer * arch.n_layers + t_out
+    sample = (f"{steps} batch-1 decode steps at context {ctx_len} (pre-filled KV) through layers 0..{n_layers - 1} + output "
+              f"projection on {cores} threads; full model = {arch.n_layers} x the per-layer time ({per_layer * 1e3:.1f} ms) + the "
+              f"output projection ({t_out * 1e3:.1f} ms)")
+    return 1.0 / dt, cores, sample
 
 
 def run_reference(args, arch, seed, rank):
+    """The CPU restatement of Juno's quantised path (oracle/) as the whole run: rank 0 alone, on all host cores.  A step
+    is one batch-1 decode step at the benchmark's context over a sample of the layers (KV pre-filled), scaled to the
+    full model; a batch of B sequences costs B such steps (InferencePipeline.forwardBatch loops, :62-69)."""
     if rank != 0:
         return
     tensors = list(synth.random_model(arch, seed))
     from oracle import oracle as o
     o.build()
+    o.set_num_threads(host_cores())
     cores = o.num_threads()
-    # a step = one batch-1 decode step of the CPU path on a layer sample sized for the run length
     total_steps = args.steps + args.warmup
-    budget = 150.0
-    probe_rate, _, _ = cpu_decode_rate(arch, tensors, 6.0)
+    start = 0 if args.no_prefill else args.ctx - 1
+    probe_rate, _, _ = cpu_decode_rate(arch, tensors, 6.0, start)
     full_step = 1.0 / probe_rate
-    frac = min(1.0, budget / (total_steps * full_step))
-    n_layers = max(1, int(arch.n_layers * frac))
+    budget = 150.0
+    n_layers = max(1, min(arch.n_layers, int(arch.n_layers * budget / (total_steps * full_step))))
     m = o.Model(arch.hidden, n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab, arch.rms_eps,
-                arch.rope_theta, kv_f16=False, max_seq=total_steps + 1)
+                arch.rope_theta, kv_f16=False, max_seq=start + total_steps + 1)
     for kind, layer, t, rows, cols, blocks in tensors:
         if kind > synth.T_OUTPUT and layer >= n_layers:
             continue
         m.set_tensor(kind, layer, blocks, t, 1 if kind in (1, 3, 4) else rows, cols)
     a_s = synth.Arch(arch.hidden, n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab)
-    scale = weight_bytes(arch) / weight_bytes(a_s)
+    # bytes one step reads: quantised blocks + FP32 K and V of the attended positions
+    def step_bytes(a):
+        return weight_bytes(a) + start * kv_bytes_per_pos(a, elem=4)
+    scale = step_bytes(arch) / step_bytes(a_s)
     s = m.new_seq()
+    if start:
+        s.fill(start, seed=2)
     for i in range(args.warmup):
-        m.forward(s, 1 + i, i)
+        m.forward(s, 1 + i, start + i)
     t0 = time.perf_counter()
     for i in range(args.steps):
-        m.forward(s, 7 + i, args.warmup + i)
+        m.forward(s, 7 + i, start + args.warmup + i)
     dt = (time.perf_counter() - t0) / args.steps * scale
-    val = 1.0 / dt  # the CPU path serves a batch as `batch` serial forwards (InferencePipeline.java:62-69)
-    sample = (f"batch-1 decode steps from an empty context through layers 0..{n_layers - 1} + output projection, "
-              f"time scaled x{scale:.2f} by weight bytes")
+    val = 1.0 / dt
+    sample = (f"batch-1 decode steps at context {start} (pre-filled FP32 KV) through layers 0..{n_layers - 1} + output "
+              f"projection on {cores} threads, time scaled x{scale:.2f} by the bytes a step reads")
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -199,8 +218,6 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="start decoding at an empty context (quick runs)")
     ap.add_argument("--chunked-prefill", action="store_true",
                     help="fill the prompt through juno_prefill (batched kernels, up to 64 positions per pass) instead of token by token")
-    ap.add_argument("--skip-prefill", action="store_true",
-                    help="start at position ctx-1 over a zero-filled KV cache (same bytes per step; for profiler runs)")
     args = ap.parse_args()
     arch, seed = MODELS[args.model]
     rank = int(os.environ.get("RANK", "0"))
@@ -244,7 +261,7 @@ def main():
     prompts = rng.integers(0, arch.vocab, (B, max(1, args.ctx)))
     # prefill token by token, as GenerationLoop does (positions 0..ctx-2, logits discarded), or in chunks
     prefill = None
-    if not args.skip_prefill and start > 0:
+    if start > 0:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         if args.chunked_prefill:
@@ -281,6 +298,13 @@ def main():
     barrier()
     ms = ev0.elapsed_time(ev1)
     c1 = ctx.counters()
+    import zlib
+    ids_crc = zlib.crc32(np.ascontiguousarray(ids, dtype=np.int32).tobytes())
+    if world > 1:  # every rank must have decoded the same tokens
+        crcs = [None] * world
+        dist.all_gather_object(crcs, ids_crc)
+        if len(set(crcs)) != 1:
+            raise SystemExit(f"tensor-parallel ranks decoded different token ids: {crcs}")
     clocks = sampler.result()
     last, pos = ids[-1].tolist(), pos + K
     if world > 1:
@@ -315,39 +339,48 @@ def main():
     ctx.profile(False)
     peak, peak_kind = measured_peaks()
     g = prof["gemv_q4k"]
-    kname = "gemv_kernel<Q4_K> (fused dequant-GEMV)" if B < 9 else "gemm_kernel<Q4_K> (one-pass batched dequant-GEMM)"
-    if prof.get("decode_step", {}).get("launches"):  # JUNO_STEP_KERNEL=1: the whole step is one kernel
-        g, kname = prof["decode_step"], "decode_step_kernel (persistent step kernel; weights only)"
-    roofline = {"bound": "hbm", "kernel": kname, "achieved": None, "peak": peak,
-                "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind}
-    if g["launches"]:
-        ach = g["algo_bytes"] / (g["ms"] / 1e3) / 1e9
-        # DRAM traffic per launch: ncu on the same kernel (profiles/gemv_q4k_q6k_128256x4096_b1.md) measured
-        # dram read+write = 1.04 x the algorithmic bytes (byte-wide scale header of the tile layout, no re-reads);
-        # scaled to this mix of launches by the bytes they process
-        if kname.startswith("gemv_kernel"):
-            roofline["traffic"] = 1.04 * g["algo_bytes"] / g["launches"]
-            roofline["traffic_source"] = "ncu capture of the 128256x4096 launch, scaled by algorithmic bytes"
-        roofline.update({"achieved": ach, "frac": ach / peak, "launches_timed": g["launches"],
-                         "avg_launch_us": g["ms"] * 1e3 / g["launches"],
-                         "algo_bytes_per_launch": g["algo_bytes"] / g["launches"]})
+    kname = ("qgemv_kernel<Q4_K> (integer tensor-core fused dequant-GEMV)" if B < 9 else
+             "gemm_kernel<Q4_K> / gemm_tc_kernel<Q4_K> (one-pass batched dequant-GEMM)")
+    # Profiling mode runs the step eagerly with events round every launch: its times include launch gaps the CUDA graph
+    # does not have.  What is reported for the dominant kernel is its SHARE of the event-timed step applied to the
+    # graph's step time, so that the kernel times of a step add up to ms_per_step.
+    tot_ms = sum(v["ms"] for v in prof.values() if v["launches"] and v is not prof.get("gemm_tcgen05"))
     step_bytes = weight_bytes(arch) / world + B * (pos - K // 2) * kv_bytes_per_pos(arch) / world
-    step_roof = {"algo_bytes_per_step_per_gpu": step_bytes, "achieved_gbs_per_gpu": step_bytes / (ms_per_step / 1e3) / 1e9,
-                 "frac_of_peak": step_bytes / (ms_per_step / 1e3) / 1e9 / peak}
+    step_frac = step_bytes / (ms_per_step / 1e3) / 1e9 / peak
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                "peak_kind": peak_kind,
+                "step": {"algo_bytes_per_step_per_gpu": step_bytes, "achieved": step_bytes / (ms_per_step / 1e3) / 1e9,
+                         "frac": step_frac, "note": "weights + KV bytes of one step / ms_per_step: the headline fraction"}}
+    if g["launches"] and tot_ms > 0:
+        share = g["ms"] / tot_ms
+        bytes_per_step = g["algo_bytes"] / prof_steps
+        launches_per_step = g["launches"] / prof_steps
+        in_graph_ms = share * ms_per_step
+        ach = bytes_per_step / (in_graph_ms / 1e3) / 1e9
+        roofline.update({"achieved": ach, "frac": ach / peak, "share_of_step": share, "algo_bytes_per_step": bytes_per_step,
+                         "launches_per_step": launches_per_step, "avg_launch_us": in_graph_ms * 1e3 / launches_per_step,
+                         "algo_bytes_per_launch": bytes_per_step / launches_per_step,
+                         "how": "achieved = algo_bytes_per_step / (share_of_step * ms_per_step)"})
+        if B < 9:
+            # ncu on this kernel: dram read + write = 1.03 x the algorithmic bytes on the 28672x4096 and 128256x4096
+            # launches (no re-reads; the excess is the byte-wide scale header of the tile layout)
+            roofline["traffic"] = 1.03 * bytes_per_step / launches_per_step
+            roofline["traffic_source"] = "ncu captures of the 28672x4096 and 128256x4096 launches, scaled by algorithmic bytes"
+    step_roof = roofline["step"]
     kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
                    "gbs": (v["algo_bytes"] / (v["ms"] / 1e3) / 1e9 if v["ms"] > 0 and v["algo_bytes"] > 0 else None)}
                for k, v in prof.items() if v["launches"]}
 
     line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": workload_config(args, arch), "clocks": clocks, "e2e": e2e,
+            "dtype": "i8xf32" if B < 9 else "f16", "data": "synthetic", "config": workload_config(args, arch), "clocks": clocks, "e2e": e2e,
             "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]), "roofline": roofline,
-            "step_roofline": step_roof, "kernels_profiled": kernels}
+            "step_roofline": step_roof, "kernels_profiled": kernels, "greedy_ids_crc32": ids_crc}
     if prefill:
         line["prefill"] = prefill
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            v, cores, sample = cpu_decode_rate(arch, tensors, 15.0)
+            v, cores, sample = cpu_decode_rate(arch, tensors, 15.0, start)
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     h.release_gpu_resources()

@@ -197,6 +197,11 @@ int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void
                           int32_t ggml_type, int64_t rows, int64_t cols);
 int juno_model_finalize(juno_model *m);
 int juno_model_free(juno_model *m); /* releaseGpuResources (LlamaTransformerHandler.java:424-448) */
+/* How a finalized model exchanges the partial products of its row-parallel projections: 0 = one GPU (nothing to
+ * exchange), 1 = NCCL all-reduce, 2 = stores into peer-mapped inboxes by the producing kernels (up to eight
+ * sequences per step; larger steps still use NCCL).  Replaces the coordinator-side sum of
+ * TensorParallelPipelineClient.allReduceSum (:244-272) either way. */
+int juno_model_tp_mode(juno_model *m, int32_t *mode);
 int juno_model_seq_create(juno_model *m, juno_seq **out);
 
 /* One decode step for n sequences: token_ids[i] is fed at positions[i] (only the last token

@@ -74,6 +74,7 @@ SIGNATURES = {
     "juno_model_set_tensor": (C.c_int, [P, I32, I32, P, I32, I64, I64]),
     "juno_model_finalize": (C.c_int, [P]),
     "juno_model_free": (C.c_int, [P]),
+    "juno_model_tp_mode": (C.c_int, [P, C.POINTER(I32)]),
     "juno_model_seq_create": (C.c_int, [P, PP]),
     "juno_forward": (C.c_int, [P, I32, PP, P, P, P, P]),
     "juno_decode_greedy": (C.c_int, [P, I32, PP, P, P, I32, P]),

@@ -169,6 +169,71 @@ __global__ void advance_kernel(int n, const int32_t *picked, int32_t *tokens, in
     if (i == 0) *step_counter = step + 1;
 }
 
+// Vocabulary-parallel greedy pick without gathering the logits: every rank pushes the first maximum of its slice
+// (value, global index) into every rank's slot, then publishes the step number; the merge waits (bounded) for all
+// ranks and takes the first maximum overall - the same token a first-maximum scan of the gathered logits finds.
+struct PairXchg {
+    float2 *slot[8];      // slot[d]: this rank's row of n pairs inside rank d's buffer
+    unsigned *flag[8];    // flag[d]: this rank's flag inside rank d's buffer
+    int world;
+};
+__global__ void argmax_push_kernel(const float *pval, const int32_t *pidx, int n, int v0, PairXchg x, const unsigned *epoch) {
+    const int seq = threadIdx.x;
+    if (seq < n) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int b = 0; b < kArgmaxBlocks; b++) {
+            const float v = pval[seq * kArgmaxBlocks + b];
+            const int i = pidx[seq * kArgmaxBlocks + b];
+            if (i != 0x7fffffff && (v > best || (v == best && i < bi))) {
+                best = v;
+                bi = i;
+            }
+        }
+        const float2 pr = make_float2(best, __int_as_float(bi == 0x7fffffff ? 0x7fffffff : bi + v0));
+        for (int d = 0; d < x.world; d++) x.slot[d][seq] = pr;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned e = *reinterpret_cast<const volatile unsigned *>(epoch);
+        for (int d = 0; d < x.world; d++) *reinterpret_cast<volatile unsigned *>(x.flag[d]) = e;
+    }
+}
+__global__ void argmax_merge_kernel(const float2 *slots /* [world][stride] */, int stride, const unsigned *flags, int world, int n,
+                                    const unsigned *epoch, int32_t *out, unsigned *err, unsigned *failed) {
+    const unsigned want = *reinterpret_cast<const volatile unsigned *>(epoch);
+    if (threadIdx.x < world && *reinterpret_cast<volatile unsigned *>(failed) == 0u) {
+        const volatile unsigned *f = flags + threadIdx.x;
+        const long long t0 = clock64();
+        while ((int)(*f - want) < 0) {
+            if (clock64() - t0 > 2000000000ll) {  // about a second: the rank may have failed
+                *reinterpret_cast<volatile unsigned *>(failed) = 1u;
+                *reinterpret_cast<volatile unsigned *>(err) = 4u | (threadIdx.x << 8);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    const int seq = threadIdx.x;
+    if (seq >= n) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < world; r++) {
+        const float2 pr = __ldcg(slots + (size_t)r * stride + seq);
+        const int i = __float_as_int(pr.y);
+        if (i != 0x7fffffff && (pr.x > best || (pr.x == best && i < bi))) {
+            best = pr.x;
+            bi = i;
+        }
+    }
+    out[seq] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// Start of a tensor-parallel step: the step number the ranks tag their partial products with.
+__global__ void epoch_kernel(unsigned *epoch) { *epoch += 1u; }
+
 // [world][n][vloc] -> [n][vocab]
 __global__ void ungather_logits_kernel(LogitsView lv, float *out) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -228,6 +293,15 @@ struct juno_model {
     double step_kv_bytes = 0;  // K+V bytes one layer's attention reads in the current step
     std::map<uint64_t, JunoGraph> graphs;
     bool use_graphs = true, mix_formats = true;  // JUNO_NO_GRAPH / JUNO_NO_MIXED
+    // tensor parallelism without collective calls on the 1..8 sequence path: per-rank exchange buffer (flags + inbox
+    // slots per row-parallel product), mapped into every peer (CUDA IPC), see enqueue_layers_q
+    bool tp_push = false;
+    uint8_t *tp_buf = nullptr;           // this rank's buffer
+    uint8_t *tp_peer[8] = {nullptr};     // every rank's buffer as seen from here (tp_peer[rank] == tp_buf)
+    size_t tp_inbox_off = 0, tp_pair_off = 0;
+    int tp_bq = 0;                       // sequences an inbox slot holds
+    unsigned *tp_failed = nullptr;       // device word: a wait for another rank ran out during this step
+    unsigned *tp_epoch = nullptr;        // step number, incremented on the device at the start of every step
     int batched_from = 9;  // smallest batch on the FP16 one-pass kernels (JUNO_GEMM_MIN_BATCH, read when the model is created)
 };
 
@@ -282,6 +356,12 @@ static void model_release(juno_model *m) {
     for (auto &kv : m->graphs)
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     m->graphs.clear();
+    for (int r = 0; r < 8; r++)
+        if (m->tp_peer[r] && m->tp_peer[r] != m->tp_buf) cudaIpcCloseMemHandle(m->tp_peer[r]);
+    if (m->tp_buf) cudaFree(m->tp_buf);
+    if (m->tp_failed) cudaFree(m->tp_failed);
+    if (m->tp_epoch) cudaFree(m->tp_epoch);
+    m->tp_buf = nullptr;
     if (m->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(m->comm);
     m->comm = nullptr;
     for (auto &L : m->layers) {
@@ -339,6 +419,66 @@ static int tp_slice(int hidden, int n_heads, int n_kv_heads, int inter, int voca
     }
     if (world > 1) JUNO_REQUIRE(c0 % 256 == 0 && nc % 256 == 0, "a column slice must be whole 256-column super-blocks");
     *rows = R; *cols = C; *row0 = r0; *nrows = nr; *col0 = c0; *ncols = nc;
+    return JUNO_OK;
+}
+
+// Maps one exchange buffer per rank into every rank (CUDA IPC; the handles travel through an NCCL all-gather).  Any
+// failure leaves the model on the NCCL collectives.
+static int tp_push_setup(juno_model *m) {
+    const char *e = getenv("JUNO_TP_PUSH");
+    if ((e && *e == '0') || m->world > 8) return JUNO_OK;
+    juno_ctx *c = m->ctx;
+    const int W = m->world, H = m->cfg.hidden, n_inst = 2 * m->cfg.n_layers;
+    m->tp_bq = std::min(m->cfg.max_batch, 8);
+    // [greedy-pick flags: 8 words][greedy-pick pairs: 8 ranks x 8 sequences][inbox: n_inst x W slots of bq x H (value, step) pairs]
+    m->tp_pair_off = 8 * 4;
+    m->tp_inbox_off = (m->tp_pair_off + 8 * 8 * sizeof(float2) + 4095) & ~(size_t)4095;
+    const size_t bytes = m->tp_inbox_off + (size_t)n_inst * W * m->tp_bq * H * 8;
+    JUNO_TRY(dev_alloc((void **)&m->tp_buf, bytes));
+    JUNO_CUDA_TRY(cudaMemset(m->tp_buf, 0, bytes));
+    JUNO_TRY(dev_alloc((void **)&m->tp_failed, 4));
+    JUNO_CUDA_TRY(cudaMemset(m->tp_failed, 0, 4));
+    JUNO_TRY(dev_alloc((void **)&m->tp_epoch, 4));
+    JUNO_CUDA_TRY(cudaMemset(m->tp_epoch, 0, 4));
+    cudaIpcMemHandle_t mine, all[8];
+    bool ok = true;
+    if (cudaIpcGetMemHandle(&mine, m->tp_buf) != cudaSuccess) {
+        cudaGetLastError();
+        memset(&mine, 0, sizeof(mine));
+        ok = false;  // no IPC on this system: NCCL path (the ranks still meet in the two collectives below)
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    uint8_t *d_h = nullptr;
+    JUNO_TRY(dev_alloc((void **)&d_h, (size_t)64 * (W + 1)));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(d_h, &mine, 64, cudaMemcpyHostToDevice, c->stream));
+    JUNO_NCCL_TRY(g_nccl.AllGather(d_h, d_h + 64, 16, kNcclFloat, m->comm, c->stream));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(all, d_h + 64, (size_t)64 * W, cudaMemcpyDeviceToHost, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    cudaFree(d_h);
+    for (int r = 0; ok && r < W; r++) {
+        if (r == m->rank) {
+            m->tp_peer[r] = m->tp_buf;
+            continue;
+        }
+        void *ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            ok = false;
+            break;
+        }
+        m->tp_peer[r] = static_cast<uint8_t *>(ptr);
+    }
+    // every rank must take the same path: agree on the outcome
+    float *d_ok = nullptr;
+    JUNO_TRY(dev_alloc((void **)&d_ok, 4));
+    const float mine_ok = ok ? 0.f : 1.f;
+    JUNO_CUDA_TRY(cudaMemcpyAsync(d_ok, &mine_ok, 4, cudaMemcpyHostToDevice, c->stream));
+    JUNO_NCCL_TRY(g_nccl.AllReduce(d_ok, d_ok, 1, kNcclFloat, kNcclSum, m->comm, c->stream));
+    float bad = 1.f;
+    JUNO_CUDA_TRY(cudaMemcpyAsync(&bad, d_ok, 4, cudaMemcpyDeviceToHost, c->stream));
+    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    cudaFree(d_ok);
+    m->tp_push = (bad == 0.f);
     return JUNO_OK;
 }
 
@@ -556,6 +696,7 @@ extern "C" int juno_model_finalize(juno_model *m) {
     JUNO_TRY(dev_alloc((void **)&m->d_pval, (size_t)B * kArgmaxBlocks * 4));
     JUNO_TRY(dev_alloc((void **)&m->d_step_counter, 4));
     JUNO_CUDA_TRY(cudaMallocHost((void **)&m->h_step, (size_t)4 * B * 4));
+    if (m->world > 1) JUNO_TRY(tp_push_setup(m));
     m->finalized = true;
     return JUNO_OK;
 }
@@ -730,24 +871,60 @@ static int q_group(juno_model *m, juno_qmat *const *mats, float *const *outs, in
 static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const int32_t *d_len, int n_splits, int &cur, cudaStream_t st) {
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
-    const int H = f.hidden, hd = m->hd;
+    const int H = f.hidden, hd = m->hd, W = m->world;
     const int Hl = m->heads_loc * hd, KVl = m->kv_loc * hd, Il = m->inter_loc;
     cur = 0;
-    const float *pend = nullptr;  // row-parallel product not yet added to the residual stream
+    // Tensor parallel, up to tp_bq sequences that fit one launch of both row-parallel products: the partial products
+    // are PUSHED into every rank's inbox by the producing kernel itself (8-byte (value, step number) stores over
+    // NVLink into peer-mapped memory), and the consuming kernel polls the pairs it needs and adds the partials in
+    // rank order.  No collective call, no extra launch, no fence or flag.  Otherwise: NCCL all-reduce between producer and consumer.
+    const bool push = m->tp_push && n <= m->tp_bq && qgemv_batch_chunk(c, Hl, m->layers[0].w[JUNO_T_ATTN_OUT]->type, n) >= n &&
+                      qgemv_batch_chunk(c, Il, m->layers[0].w[JUNO_T_FFN_DOWN]->type, n) >= n;
+    int pend_inst = -1;           // exchange instance of the pending row-parallel product (push mode)
+    const float *pend = nullptr;  // row-parallel product not yet added to the residual stream (NCCL mode / one GPU)
+    auto inbox = [&](int rank_of_buf, int inst, int src) {
+        return reinterpret_cast<float *>(m->tp_peer[rank_of_buf] + m->tp_inbox_off) + ((size_t)inst * W + src) * m->tp_bq * H * 2;
+    };
     auto from_residual = [&](QGemvArgs &a, const float *normw) {
         a.batch = n;
         a.x = m->x[cur];
         a.ldx = H;
         a.normw = normw;
         a.eps = f.rms_eps;
-        if (pend) {
+        if (pend_inst >= 0) {
+            for (int k = 0; k < W; k++) a.add[k] = inbox(m->rank, pend_inst, k);
+            a.n_add = W;
+            a.tagged_adds = true;
+            a.epoch = m->tp_epoch;
+            a.peer_failed = m->tp_failed;
+            a.x_store = m->x[cur ^ 1];
+        } else if (pend) {
             a.add[0] = pend;
             a.n_add = 1;
             a.x_store = m->x[cur ^ 1];
         }
     };
-    auto all_reduce = [&](float *buf) -> int {
-        if (m->world > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(buf, buf, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+    auto row_parallel = [&](juno_qmat *w, const float *x, int K, float *out, int inst) -> int {
+        QGemvArgs a;
+        a.batch = n;
+        a.x = x;
+        a.ldx = K;
+        a.ld_out = H;
+        if (push) {
+            a.n_peers = W;
+            for (int d = 0; d < W; d++) a.peer_out[d] = inbox(d, inst, m->rank);
+            a.epoch = m->tp_epoch;
+        }
+        juno_qmat *ws[1] = {w};
+        float *os[1] = {out};
+        JUNO_TRY(q_group(m, ws, os, 1, a, st));
+        if (push) {
+            pend_inst = inst;
+            pend = nullptr;
+        } else {
+            if (W > 1) JUNO_NCCL_TRY(g_nccl.AllReduce(out, out, (size_t)n * H, kNcclFloat, kNcclSum, m->comm, st));
+            pend = out;
+        }
         return JUNO_OK;
     };
     for (int l = 0; l < f.n_layers; l++) {
@@ -759,8 +936,9 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
             juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
             float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
             JUNO_TRY(q_group(m, qkv_m, qkv_o, 3, a, st));
-            if (pend) cur ^= 1;
+            if (pend || pend_inst >= 0) cur ^= 1;
             pend = nullptr;
+            pend_inst = -1;
         }
         AttnArgs at;
         at.pool = m->pool;
@@ -781,18 +959,8 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
         at.vnew = m->qkv + Hl + KVl;
         at.ldkv = m->qkv_ld;
         JUNO_TRY(launch_attn(c, at, st));
-        {   // proj = Wo att (this rank's heads)
-            QGemvArgs a;
-            a.batch = n;
-            a.x = m->att;
-            a.ldx = Hl;
-            a.ld_out = H;
-            juno_qmat *wo[1] = {L.w[JUNO_T_ATTN_OUT]};
-            float *po[1] = {m->proj};
-            JUNO_TRY(q_group(m, wo, po, 1, a, st));
-            JUNO_TRY(all_reduce(m->proj));
-            pend = m->proj;
-        }
+        // proj = Wo att (this rank's heads)
+        JUNO_TRY(row_parallel(L.w[JUNO_T_ATTN_OUT], m->att, Hl, m->proj, 2 * l));
         {   // hdn = silu(Wgate xn2) * (Wup xn2), xn2 = rmsNorm(x + proj)
             QGemvArgs a;
             from_residual(a, L.ffn_norm);
@@ -803,19 +971,10 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
             JUNO_TRY(q_group(m, gu, go, 1, a, st));
             cur ^= 1;
             pend = nullptr;
+            pend_inst = -1;
         }
-        {   // proj2 = Wdown hdn (this rank's FFN rows)
-            QGemvArgs a;
-            a.batch = n;
-            a.x = m->hdn;
-            a.ldx = Il;
-            a.ld_out = H;
-            juno_qmat *wd[1] = {L.w[JUNO_T_FFN_DOWN]};
-            float *po[1] = {m->proj2};
-            JUNO_TRY(q_group(m, wd, po, 1, a, st));
-            JUNO_TRY(all_reduce(m->proj2));
-            pend = m->proj2;
-        }
+        // proj2 = Wdown hdn (this rank's FFN rows)
+        JUNO_TRY(row_parallel(L.w[JUNO_T_FFN_DOWN], m->hdn, Il, m->proj2, 2 * l + 1));
     }
     // logits = Wout rmsNorm(x + proj2)
     QGemvArgs a;
@@ -824,15 +983,20 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
     juno_qmat *lm[1] = {m->output};
     float *lo[1] = {m->logits_loc};
     JUNO_TRY(q_group(m, lm, lo, 1, a, st));
-    if (pend) cur ^= 1;
+    if (pend || pend_inst >= 0) cur ^= 1;
     return JUNO_OK;
 }
 
-static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, cudaStream_t st) {
+static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance, bool want_logits, cudaStream_t st) {
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
     const int H = f.hidden, hd = m->hd, B = f.max_batch;
     const int32_t *d_tok = m->d_step, *d_pos = m->d_step + B, *d_slot = m->d_step + 2 * B, *d_len = m->d_step + 3 * B;
+    if (m->tp_push) {
+        epoch_kernel<<<1, 1, 0, st>>>(m->tp_epoch);
+        JUNO_CUDA_TRY(cudaGetLastError());
+        c->kernel_launches++;
+    }
     // embedding lookup -> x[0]
     {
         juno_qmat *e = m->tok_embd;
@@ -855,18 +1019,41 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
     LogitsView lv;
     lv.n = n;
     lv.vocab = f.vocab;
-    if (m->vocab_sharded) {
-        JUNO_NCCL_TRY(g_nccl.AllGather(m->logits_loc, m->logits_gather, (size_t)n * m->vocab_loc, kNcclFloat, m->comm, st));
-        lv.base = m->logits_gather;
-        lv.vloc = m->vocab_loc;
-    } else {
+    // Sharded vocabulary: when the caller wants the logits they are gathered (NCCL); when only the greedy pick is
+    // wanted and the ranks exchange through peer memory, (value, index) pairs travel instead and the step holds no
+    // collective call at all.
+    const bool pair_pick = m->vocab_sharded && m->tp_push && !want_logits && n <= 8;
+    if (pair_pick) {
         lv.base = m->logits_loc;
-        lv.vloc = f.vocab;
+        lv.vocab = m->vocab_loc;
+        lv.vloc = m->vocab_loc;
+        argmax_partial_kernel<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(lv, m->d_pval, m->d_pidx);
+        PairXchg x;
+        x.world = m->world;
+        for (int d = 0; d < m->world; d++) {
+            x.slot[d] = reinterpret_cast<float2 *>(m->tp_peer[d] + m->tp_pair_off) + m->rank * 8;
+            x.flag[d] = reinterpret_cast<unsigned *>(m->tp_peer[d]) + m->rank;
+        }
+        argmax_push_kernel<<<1, 32, 0, st>>>(m->d_pval, m->d_pidx, n, m->rank * m->vocab_loc, x, m->tp_epoch);
+        argmax_merge_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const float2 *>(m->tp_buf + m->tp_pair_off), 8,
+                                             reinterpret_cast<const unsigned *>(m->tp_buf), m->world, n, m->tp_epoch,
+                                             m->d_argmax, c->gemv_scratch.qerr, m->tp_failed);
+        JUNO_CUDA_TRY(cudaGetLastError());
+        c->kernel_launches += 3;
+    } else {
+        if (m->vocab_sharded) {
+            JUNO_NCCL_TRY(g_nccl.AllGather(m->logits_loc, m->logits_gather, (size_t)n * m->vocab_loc, kNcclFloat, m->comm, st));
+            lv.base = m->logits_gather;
+            lv.vloc = m->vocab_loc;
+        } else {
+            lv.base = m->logits_loc;
+            lv.vloc = f.vocab;
+        }
+        argmax_partial_kernel<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(lv, m->d_pval, m->d_pidx);
+        argmax_final_kernel<<<(n + 63) / 64, 64, 0, st>>>(m->d_pval, m->d_pidx, n, m->d_argmax);
+        JUNO_CUDA_TRY(cudaGetLastError());
+        c->kernel_launches += 2;
     }
-    argmax_partial_kernel<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(lv, m->d_pval, m->d_pidx);
-    argmax_final_kernel<<<(n + 63) / 64, 64, 0, st>>>(m->d_pval, m->d_pidx, n, m->d_argmax);
-    JUNO_CUDA_TRY(cudaGetLastError());
-    c->kernel_launches += 2;
     if (greedy_advance) {
         advance_kernel<<<1, std::max(32, (n + 31) / 32 * 32), 0, st>>>(n, m->d_argmax, m->d_step, m->d_step + B,
                                                                       m->d_step + 3 * B, m->d_out_ids, m->d_step_counter);
@@ -878,11 +1065,11 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
 
 // Runs one step: the first call for a (n, splits, mode) key runs eagerly (it also sizes every scratch
 // buffer); the second captures the same launches into a CUDA graph, later ones replay it.
-static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
+static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance, bool want_logits) {
     juno_ctx *c = m->ctx;
     cudaStream_t st = c->stream;
-    if (!m->use_graphs || c->profiling) return enqueue_step(m, n, n_splits, greedy_advance, st);
-    const uint64_t key = ((uint64_t)n << 32) | ((uint64_t)n_splits << 1) | (greedy_advance ? 1u : 0u);
+    if (!m->use_graphs || c->profiling) return enqueue_step(m, n, n_splits, greedy_advance, want_logits, st);
+    const uint64_t key = ((uint64_t)n << 32) | ((uint64_t)n_splits << 2) | (want_logits ? 2u : 0u) | (greedy_advance ? 1u : 0u);
     JunoGraph &g = m->graphs[key];
     if (g.exec) {
         JUNO_CUDA_TRY(cudaGraphLaunch(g.exec, st));
@@ -891,11 +1078,11 @@ static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance) {
     }
     if (!g.seen) {
         g.seen = 1;
-        return enqueue_step(m, n, n_splits, greedy_advance, st);
+        return enqueue_step(m, n, n_splits, greedy_advance, want_logits, st);
     }
     const int64_t before = c->kernel_launches.load();
     JUNO_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_step(m, n, n_splits, greedy_advance, st);
+    int rc = enqueue_step(m, n, n_splits, greedy_advance, want_logits, st);
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamEndCapture(st, &graph);
     const int launches = (int)(c->kernel_launches.load() - before);
@@ -937,7 +1124,12 @@ static int step_check(juno_model *m) {
     const unsigned code = c->gemv_scratch.qerr_host ? *reinterpret_cast<volatile unsigned *>(c->gemv_scratch.qerr_host) : 0u;
     if (code) {
         *reinterpret_cast<volatile unsigned *>(c->gemv_scratch.qerr_host) = 0u;
-        set_error("a GEMV warp gave up waiting for a weight tile (warp %u of block %u)", (code >> 8) & 0xffu, code >> 16);
+        if (m->tp_failed) cudaMemset(m->tp_failed, 0, 4);
+        if ((code & 0xffu) >= 3u)
+            set_error("tensor-parallel rank %u did not deliver its %s within a second (this rank gave up waiting)", (code >> 8) & 0xffu,
+                      (code & 0xffu) == 3u ? "partial products" : "greedy pick");
+        else
+            set_error("a GEMV warp gave up waiting for a weight tile (warp %u of block %u)", (code >> 8) & 0xffu, code >> 16);
         return JUNO_ERR_TIMEOUT;
     }
     return JUNO_OK;
@@ -1005,7 +1197,7 @@ int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t 
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
     int n_splits = 1;
     JUNO_TRY(prepare_step(m, n, seqs, token_ids, positions, 0, &n_splits));
-    JUNO_TRY(run_step(m, n, n_splits, false));
+    JUNO_TRY(run_step(m, n, n_splits, false, logits_host != nullptr));
     c->forward_calls++;
     const int V = m->cfg.vocab;
     if (logits_host) {
@@ -1135,7 +1327,7 @@ int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const in
         }
     }
     JUNO_CUDA_TRY(cudaMemsetAsync(m->d_step_counter, 0, 4, c->stream));
-    for (int s = 0; s < steps; s++) JUNO_TRY(run_step(m, n, n_splits, true));
+    for (int s = 0; s < steps; s++) JUNO_TRY(run_step(m, n, n_splits, true, false));
     c->forward_calls += steps;
     JUNO_CUDA_TRY(cudaMemcpyAsync(out_ids, m->d_out_ids, (size_t)steps * n * 4, cudaMemcpyDeviceToHost, c->stream));
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
@@ -1155,6 +1347,13 @@ int juno_model_last_hidden(juno_model *m, int32_t n, float *hidden_host) {
     JUNO_CUDA_TRY(cudaMemcpyAsync(hidden_host, m->x[m->last_x], (size_t)n * m->cfg.hidden * 4, cudaMemcpyDeviceToHost,
                                   c->stream));
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return JUNO_OK;
+}
+
+int juno_model_tp_mode(juno_model *m, int32_t *mode) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(mode, "mode is null");
+    *mode = m->world <= 1 ? 0 : (m->tp_push ? 2 : 1);
     return JUNO_OK;
 }
 

@@ -53,6 +53,12 @@ struct QParams {
     int ring;       // tile slots per warp
     int slot_bytes; // bytes of one slot (largest tile of the launch)
     int wait_ns;             // suspend hint of a wait on a weight tile
+    // tensor-parallel push all-reduce (see QGemvArgs)
+    int n_peers;
+    float *peer_out[kQMaxAdd];
+    int tagged_adds;
+    const unsigned *epoch;
+    unsigned *peer_failed;
     unsigned *err;  // device word: a wait on a weight tile gave up (code | warp << 8 | block << 16)
 };
 
@@ -318,6 +324,9 @@ struct QSrc {
     const float *normw;
     float *x_store;
     int ldx;
+    unsigned tag;      // non-zero: the addends are (value, step number) pairs stored by other GPUs; wait for this number
+    unsigned *failed;  // the word a wait that ran out sets (later waits give up at once), and the error word
+    unsigned *err;
 };
 // The eight values of one lane (columns sb*256 + lane*8 .. +7 of row b) on their way to the operand.
 struct QIn {
@@ -328,6 +337,43 @@ __device__ __forceinline__ void ld8(const float *p, float (&o)[8]) {
     const float4 a = *reinterpret_cast<const float4 *>(p), c = *reinterpret_cast<const float4 *>(p + 4);
     o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = c.x; o[5] = c.y; o[6] = c.z; o[7] = c.w;
 }
+// A wait for another rank's partial products gives up after about a second (the rank may have failed).
+constexpr long long kQPeerWaitLimitClk = 2000000000ll;
+// Eight (value, step number) pairs that another GPU stores with one 8-byte store each: the data is its own flag, so
+// the consumer needs no fence and no separate signal - it re-reads until every pair carries this step's number.  The
+// wait is bounded; a wait that runs out sets the failure word, which ends every later wait at once.
+__device__ __forceinline__ uint4 ld_pairs(const uint4 *p) {
+    uint4 r;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void st_pair(float *slot, size_t idx, float v, unsigned tag) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(slot) + idx), "l"(w) : "memory");
+}
+__device__ __noinline__ void ld8_tagged(const float *slot, size_t idx, unsigned want, unsigned *failed, unsigned *err, unsigned code,
+                                        float (&o)[8]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint2 *>(slot) + idx);
+    uint4 a, b, c, d;
+    long long t0 = 0;
+    for (int spin = 0;; spin++) {
+        a = ld_pairs(p);
+        b = ld_pairs(p + 1);
+        c = ld_pairs(p + 2);
+        d = ld_pairs(p + 3);
+        if (a.y == want && a.w == want && b.y == want && b.w == want && c.y == want && c.w == want && d.y == want && d.w == want) break;
+        if (*reinterpret_cast<volatile unsigned *>(failed) != 0u) break;
+        if (spin == 0) {
+            t0 = clock64();
+        } else if (clock64() - t0 > kQPeerWaitLimitClk) {  // about a second: the rank may have failed
+            *reinterpret_cast<volatile unsigned *>(failed) = 1u;
+            *reinterpret_cast<volatile unsigned *>(err) = code;
+            break;
+        }
+    }
+    o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.z); o[2] = __uint_as_float(b.x); o[3] = __uint_as_float(b.z);
+    o[4] = __uint_as_float(c.x); o[5] = __uint_as_float(c.z); o[6] = __uint_as_float(d.x); o[7] = __uint_as_float(d.z);
+}
 // Issues the loads of one (row, slice) pair; nothing here waits for them (unless there are several addends).
 __device__ __forceinline__ void quantize_fetch(const QSrc &q, int b, int sb, int lane, QIn &in) {
     const size_t roff = (size_t)b * q.ldx + sb * 256 + lane * 8;
@@ -335,13 +381,19 @@ __device__ __forceinline__ void quantize_fetch(const QSrc &q, int b, int sb, int
     if (q.add0) {
         // partial products are summed first, in the order given (TensorParallelPipelineClient.allReduceSum :244-272 adds
         // rank 0..N-1), then added to the residual row (LlamaTransformerHandler.add :1738-1743)
-        ld8(q.add0 + roff, in.s);
+        if (q.tag)
+            ld8_tagged(q.add0, roff, q.tag, q.failed, q.err, 3u, in.s);
+        else
+            ld8(q.add0 + roff, in.s);
         const float *more[7] = {q.add1, q.add2, q.add3, q.add4, q.add5, q.add6, q.add7};
 #pragma unroll
         for (int k = 0; k < 7; k++) {
             if (!more[k]) break;
             float t[8];
-            ld8(more[k] + roff, t);
+            if (q.tag)
+                ld8_tagged(more[k], roff, q.tag, q.failed, q.err, 3u | ((unsigned)(k + 1) << 8), t);
+            else
+                ld8(more[k] + roff, t);
 #pragma unroll
             for (int i = 0; i < 8; i++) in.s[i] = __fadd_rn(in.s[i], t[i]);
         }
@@ -563,11 +615,13 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     __syncwarp();
 
     pdl_wait();  // everything below reads what earlier kernels of the stream wrote
+    bool failed = false;
+    const unsigned step_no = (p.tagged_adds || p.n_peers) ? *reinterpret_cast<const volatile unsigned *>(p.epoch) : 0u;
     // operand: every warp converts (sequence, slice) pairs warp, warp+16, ...
     {
         const QSrc q{p.x, p.n_add > 0 ? p.add[0] : nullptr, p.n_add > 1 ? p.add[1] : nullptr, p.n_add > 2 ? p.add[2] : nullptr, p.n_add > 3 ? p.add[3] : nullptr,
                      p.n_add > 4 ? p.add[4] : nullptr, p.n_add > 5 ? p.add[5] : nullptr, p.n_add > 6 ? p.add[6] : nullptr, p.n_add > 7 ? p.add[7] : nullptr,
-                     p.normw, p.x_store, p.ldx};
+                     p.normw, p.x_store, p.ldx, p.tagged_adds ? step_no : 0u, p.peer_failed, p.err};
         float ss[8];
 #pragma unroll
         for (int b = 0; b < 8; b++) ss[b] = 0.f;
@@ -632,7 +686,6 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     const uint32_t xop_s = smem_u32(xop);
     int slot = 0, it = 0;
     unsigned parity = 0;
-    bool failed = false;
     for (int T = blockIdx.x; T < p.n_tasks; T += gridDim.x, it++) {
         const int R = T * p.G + gi;
         const bool have = (R < p.total_rt) && n_span > 0;
@@ -697,7 +750,12 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
                 const float sc = rs_s[b];
                 v = __fmul_rn(v, sc);
                 if (p.epi == QEPI_SILU_PAIR) v = __fmul_rn(silu_f(v), __fmul_rn(v2, sc));
-                p.out[s][(size_t)b * p.ld_out + orow] = v;
+                if (p.n_peers) {
+                    // one 8-byte (value, step number) store per rank over NVLink: the consumer polls the data itself
+                    for (int d = 0; d < p.n_peers; d++) st_pair(p.peer_out[d], (size_t)b * p.ld_out + orow, v, step_no);
+                } else {
+                    p.out[s][(size_t)b * p.ld_out + orow] = v;
+                }
             }
         }
     }
@@ -842,6 +900,16 @@ int launch_qgemv(juno_ctx *ctx, const QGemvArgs &a, cudaStream_t st) {
     p.slot_bytes = q_slot_bytes(type_mix);
     p.err = ctx->gemv_scratch.qerr;
     p.wait_ns = q_env_int("JUNO_QGEMV_WAIT_NS", 0);
+    p.n_peers = a.n_peers;
+    for (int d = 0; d < a.n_peers; d++) {
+        p.peer_out[d] = a.peer_out[d];
+    }
+    p.tagged_adds = a.tagged_adds ? 1 : 0;
+    p.epoch = a.epoch;
+    p.peer_failed = a.peer_failed;
+    if (a.n_peers) JUNO_REQUIRE(a.nseg == 1 && a.epoch && a.epi == QEPI_STORE, "qgemv: a pushed product is one matrix with a plain store");
+    if (a.tagged_adds) JUNO_REQUIRE(a.peer_failed && a.epoch && a.n_add > 0, "qgemv: a consumer of pushed products needs the step number and the failure word");
+    if (a.n_peers || a.tagged_adds) JUNO_REQUIRE(a.batch <= 8, "qgemv: peer exchange carries at most 8 sequences per launch");
     for (int b0 = 0; b0 < a.batch; b0 += bc_full) {
         p.bc = std::min(bc_full, a.batch - b0);
         for (int s = 0; s < a.nseg; s++) p.out[s] = a.seg[s].out + (size_t)b0 * a.ld_out;

@@ -39,6 +39,20 @@ struct QGemvArgs {
     float *x_store = nullptr;       // optional: the summed input rows are written here (by one CTA)
     const float *normw = nullptr;   // optional RMSNorm (LlamaTransformerHandler.rmsNorm :818-828): operand = normw*v,
     float eps = 0.f;                //   outputs multiplied by 1/sqrt(mean(v^2) + eps)
+
+    // Tensor parallelism without a collective library call (one rank per GPU, peer memory mapped at load time).  The
+    // exchanged unit is an 8-byte (value, step number) pair written with ONE store, so the data is its own flag:
+    // no fence, no counter and no separate signal on either side.
+    // Producer side (row-parallel products): the outputs go into every rank's inbox instead of seg[0].out
+    // (peer_out[d]: this rank's slot in rank d's inbox, [batch][ld_out] pairs), tagged with the step number `*epoch`.
+    int n_peers = 0;
+    float *peer_out[kQMaxAdd] = {nullptr};
+    // Consumer side: with tagged_adds the addends add[0..n_add) are inbox slots ([batch][ldx] pairs) written by the
+    // ranks 0..n_add-1; every load re-reads until the pairs carry `*epoch` (bounded: about a second, then
+    // *peer_failed is set, the error word says which rank, and every later wait gives up at once).
+    bool tagged_adds = false;
+    const unsigned *epoch = nullptr;
+    unsigned *peer_failed = nullptr;
 };
 
 // The integer-MMA kernel is the default for 1..8 sequences; JUNO_QGEMV=0 keeps the bf16-limb kernel (gemv.cu).

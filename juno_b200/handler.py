@@ -171,6 +171,12 @@ class B200TransformerHandler:
         check(self._L.juno_model_last_hidden(self.handle, n, _ptr(out)), "juno_model_last_hidden")
         return out
 
+    def tp_mode(self) -> int:
+        """0 = one GPU, 1 = NCCL all-reduce, 2 = partial products pushed into peer-mapped inboxes."""
+        mode = C.c_int32()
+        check(self._L.juno_model_tp_mode(self.handle, C.byref(mode)), "juno_model_tp_mode")
+        return mode.value
+
     def evict(self, request_id: str) -> None:
         """LlamaTransformerHandler.evict (:498-505): drops the request's KV pages; unknown ids are ignored."""
         s = self._seqs.pop(request_id, None)

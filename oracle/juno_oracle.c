@@ -518,6 +518,21 @@ void jo_seq_free(jo_seq *s) {
     free(s);
 }
 
+/* Benchmark helper (not part of the reference): fills positions [0, n_pos) of every layer's K and V with a
+ * deterministic pseudo-random pattern in [-1, 1), so that a timed decode step attends over a context of that length
+ * without running the n_pos forward passes that would normally produce it. */
+void jo_seq_fill(jo_seq *s, const jo_model *m, int n_pos, unsigned seed) {
+    const size_t kvDim = (size_t)m->cfg.kv_heads * m->cfg.head_dim, per_layer = (size_t)m->cfg.max_seq * kvDim;
+    unsigned state = seed * 2654435761u + 12345u;
+    for (int l = 0; l < m->cfg.layers; l++)
+        for (size_t i = 0; i < (size_t)n_pos * kvDim; i++) {
+            state = state * 1664525u + 1013904223u;
+            s->K[l * per_layer + i] = (float)(int)(state >> 8) * (1.0f / 8388608.0f) - 1.0f;
+            state = state * 1664525u + 1013904223u;
+            s->V[l * per_layer + i] = (float)(int)(state >> 8) * (1.0f / 8388608.0f) - 1.0f;
+        }
+}
+
 static void mv(const jo_tensor *t, const float *x, float *y) {
     jo_matvec(t->type, t->data, x, 0, t->rows, t->cols, y);
 }

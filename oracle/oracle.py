@@ -74,6 +74,7 @@ def lib():
         L.jo_seq_create.restype = C.c_void_p
         L.jo_seq_create.argtypes = [C.c_void_p]
         L.jo_seq_free.argtypes = [C.c_void_p]
+        L.jo_seq_fill.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_uint]
         L.jo_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         L.jo_generate_greedy.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                          C.c_void_p, C.c_void_p]
@@ -233,6 +234,10 @@ class Seq:
     def __init__(self, model: Model):
         self.model = model
         self.h = lib().jo_seq_create(model.h)
+
+    def fill(self, n_pos: int, seed: int = 1):
+        """Benchmark helper: pseudo-random K/V for positions [0, n_pos) of every layer (no forward passes)."""
+        lib().jo_seq_fill(self.h, self.model.h, int(n_pos), int(seed))
 
     def close(self):
         if self.h:
