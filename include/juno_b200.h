@@ -45,6 +45,7 @@ typedef struct juno_qmat juno_qmat;
 typedef struct juno_model juno_model;
 typedef struct juno_seq juno_seq;
 typedef struct juno_kvpool juno_kvpool;
+typedef struct juno_gguf juno_gguf;
 
 /* Thread-local text of the last failure on the calling thread. */
 const char *juno_last_error(void);
@@ -176,6 +177,32 @@ typedef struct juno_model_cfg {
 #define JUNO_T_FFN_UP 10
 #define JUNO_T_FFN_DOWN 11
 
+/* ── GGUF model files (host only, no GPU needed) ───────────────────────────────
+ * Replaces node/GgufReader.java for the tensors and metadata the decode path reads: open (:102-180) parses header
+ * (magic "GGUF", version 2 or 3), metadata (value types 0-12, :1189-1244) and the tensor table, and places the data
+ * section at the next multiple of 32 after it (:169-176).  The file is mapped read-only; tensors are pointers into
+ * the mapping (tensorRaw :329-340 copies them to the heap instead) and stay valid until juno_gguf_close.  A damaged
+ * or foreign file gives JUNO_ERR_INVALID_ARG (the reference throws IOException), a version other than 2 or 3
+ * JUNO_ERR_UNSUPPORTED.  GGUF inside a llamafile ZIP is not supported. */
+int juno_gguf_open(const char *path, juno_gguf **out);
+int juno_gguf_close(juno_gguf *g);
+int juno_gguf_info(juno_gguf *g, int32_t *version, int64_t *n_tensors, int64_t *n_meta, int64_t *data_offset);
+/* metaLong / metaFloat (:199-216): any numeric value converts, a missing key or another type gives dflt. */
+int juno_gguf_meta_int(juno_gguf *g, const char *key, int64_t dflt, int64_t *out);
+int juno_gguf_meta_float(juno_gguf *g, const char *key, double dflt, double *out);
+/* metaString (:194-197): *len = -1 for a missing key or another type, else the length; buf (may be null) gets at
+ * most buf_len-1 bytes and a terminator. */
+int juno_gguf_meta_string(juno_gguf *g, const char *key, char *buf, int32_t buf_len, int32_t *len);
+int juno_gguf_meta_array_len(juno_gguf *g, const char *key, int64_t *len); /* -1 if the key is not an array */
+int juno_gguf_tensor_name(juno_gguf *g, int64_t index, char *buf, int32_t buf_len); /* file order */
+int juno_gguf_has_tensor(juno_gguf *g, const char *name, int32_t *present);
+/* tensorType / tensorDims / tensorRaw: dims4 is innermost first ([cols, rows] for a matrix, :246-248), unused entries
+ * 1.  Any output pointer may be null.  Asking for data of a type without a byte-size formula gives
+ * JUNO_ERR_UNSUPPORTED (UnsupportedOperationException in the reference); an unknown name JUNO_ERR_INVALID_ARG. */
+int juno_gguf_tensor(juno_gguf *g, const char *name, int32_t *ggml_type, int32_t *n_dims, int64_t *dims4,
+                     const void **data, int64_t *n_bytes);
+int juno_gguf_raw_byte_count(int32_t ggml_type, int64_t n_elems, int64_t *bytes); /* rawByteCount :347-360 */
+
 /* Host-only (no GPU needed): the slice of a FULL tensor of `kind` that rank tp_rank of tp_world keeps - the rule
  * juno_model_set_tensor applies itself (TensorShardContext.java:74-100: headsPerNode = numHeads / world, sliceDim =
  * hidden / world).  out6 = {rows, cols, row0, nrows, col0, ncols} of the full tensor and of the kept sub-matrix:
@@ -196,6 +223,15 @@ int juno_model_create(juno_ctx *ctx, const juno_model_cfg *cfg, juno_model **out
 int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void *blocks,
                           int32_t ggml_type, int64_t rows, int64_t cols);
 int juno_model_finalize(juno_model *m);
+/* LlamaConfig.from (LlamaConfig.java:58-91): fills hidden, n_layers, n_heads, n_kv_heads, inter, vocab, rms_eps and
+ * rope_theta of *cfg from "<general.architecture>.*" (then "llama.*", then the TinyLlama value); vocab is the larger
+ * of <arch>.vocab_size and the length of tokenizer.ggml.tokens.  The other fields are left as they are. */
+int juno_gguf_model_cfg(juno_gguf *g, juno_model_cfg *cfg);
+/* Hands every tensor the reference constructor reads (LlamaTransformerHandler.java:238-275: token_embd, output_norm,
+ * optional output, blk.N.{attn_norm, ffn_norm, attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down}) to
+ * juno_model_set_tensor, straight from the mapped file.  Files with attn_{q,k,v}.bias give JUNO_ERR_UNSUPPORTED.
+ * Call juno_model_finalize afterwards. */
+int juno_model_load_gguf(juno_model *m, juno_gguf *g);
 int juno_model_free(juno_model *m); /* releaseGpuResources (LlamaTransformerHandler.java:424-448) */
 /* How a finalized model exchanges the partial products of its row-parallel projections: 0 = one GPU (nothing to
  * exchange), 1 = NCCL all-reduce, 2 = stores into peer-mapped inboxes by the producing kernels (up to eight

@@ -80,6 +80,19 @@ SIGNATURES = {
     "juno_decode_greedy": (C.c_int, [P, I32, PP, P, P, I32, P]),
     "juno_prefill": (C.c_int, [P, P, P, I32, I32, P, P]),
     "juno_model_last_hidden": (C.c_int, [P, I32, P]),
+    "juno_gguf_open": (C.c_int, [C.c_char_p, PP]),
+    "juno_gguf_close": (C.c_int, [P]),
+    "juno_gguf_info": (C.c_int, [P, C.POINTER(I32), C.POINTER(I64), C.POINTER(I64), C.POINTER(I64)]),
+    "juno_gguf_meta_int": (C.c_int, [P, C.c_char_p, I64, C.POINTER(I64)]),
+    "juno_gguf_meta_float": (C.c_int, [P, C.c_char_p, C.c_double, C.POINTER(C.c_double)]),
+    "juno_gguf_meta_string": (C.c_int, [P, C.c_char_p, C.c_char_p, I32, C.POINTER(I32)]),
+    "juno_gguf_meta_array_len": (C.c_int, [P, C.c_char_p, C.POINTER(I64)]),
+    "juno_gguf_tensor_name": (C.c_int, [P, I64, C.c_char_p, I32]),
+    "juno_gguf_has_tensor": (C.c_int, [P, C.c_char_p, C.POINTER(I32)]),
+    "juno_gguf_tensor": (C.c_int, [P, C.c_char_p, C.POINTER(I32), C.POINTER(I32), C.POINTER(I64), PP, C.POINTER(I64)]),
+    "juno_gguf_raw_byte_count": (C.c_int, [I32, I64, C.POINTER(I64)]),
+    "juno_gguf_model_cfg": (C.c_int, [P, C.POINTER(ModelCfg)]),
+    "juno_model_load_gguf": (C.c_int, [P, P]),
 }
 
 _lib = None

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libjuno_b200.so")
-SOURCES = ["context.cu", "gemv.cu", "qgemv.cu", "gemm.cu", "gemm_tc.cu", "attn.cu", "model.cu"]
+SOURCES = ["context.cu", "gemv.cu", "qgemv.cu", "gemm.cu", "gemm_tc.cu", "attn.cu", "model.cu", "gguf_file.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <string>
 #include <map>
 #include <vector>
 
@@ -1347,6 +1348,44 @@ int juno_model_last_hidden(juno_model *m, int32_t n, float *hidden_host) {
     JUNO_CUDA_TRY(cudaMemcpyAsync(hidden_host, m->x[m->last_x], (size_t)n * m->cfg.hidden * 4, cudaMemcpyDeviceToHost,
                                   c->stream));
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return JUNO_OK;
+}
+
+// Every tensor the reference constructor reads (LlamaTransformerHandler.java:238-275), by its GGUF name, straight from
+// the mapped file.  GGUF dims are [cols (in), rows (out)] (GgufReader.java:246-248).
+int juno_model_load_gguf(juno_model *m, juno_gguf *g) {
+    JUNO_TRY(model_check(m));
+    JUNO_REQUIRE(!m->finalized, "model is already finalized");
+    const juno_model_cfg &f = m->cfg;
+    auto put = [&](const std::string &name, int kind, int layer, bool optional) -> int {
+        int32_t present = 0;
+        JUNO_TRY(juno_gguf_has_tensor(g, name.c_str(), &present));
+        if (!present && optional) return JUNO_OK;
+        int32_t type = 0, nd = 0;
+        int64_t dims[4] = {1, 1, 1, 1}, nbytes = 0;
+        const void *data = nullptr;
+        JUNO_TRY(juno_gguf_tensor(g, name.c_str(), &type, &nd, dims, &data, &nbytes));
+        JUNO_REQUIRE(nd >= 1 && nd <= 2, "tensor %s has %d dimensions, expected 1 or 2", name.c_str(), nd);
+        const int64_t cols = dims[0], rows = nd == 2 ? dims[1] : 1;
+        return juno_model_set_tensor(m, kind, layer, data, type, rows, cols);
+    };
+    {
+        int32_t bias = 0;
+        JUNO_TRY(juno_gguf_has_tensor(g, "blk.0.attn_q.bias", &bias));
+        if (bias) {
+            set_error("the file has attn_q/k/v bias tensors (Qwen2-style, LlamaTransformerHandler.java:258-262), which this library does not apply");
+            return JUNO_ERR_UNSUPPORTED;
+        }
+    }
+    JUNO_TRY(put("token_embd.weight", JUNO_T_TOKEN_EMBD, 0, false));
+    JUNO_TRY(put("output_norm.weight", JUNO_T_OUTPUT_NORM, 0, false));
+    JUNO_TRY(put("output.weight", JUNO_T_OUTPUT, 0, true));  // absent: tied to token_embd (:463-470)
+    static const struct { const char *suffix; int kind; } per_layer[] = {
+        {"attn_norm", JUNO_T_ATTN_NORM}, {"ffn_norm", JUNO_T_FFN_NORM}, {"attn_q", JUNO_T_ATTN_Q},   {"attn_k", JUNO_T_ATTN_K},
+        {"attn_v", JUNO_T_ATTN_V},       {"attn_output", JUNO_T_ATTN_OUT}, {"ffn_gate", JUNO_T_FFN_GATE}, {"ffn_up", JUNO_T_FFN_UP},
+        {"ffn_down", JUNO_T_FFN_DOWN}};
+    for (int l = 0; l < f.n_layers; l++)
+        for (const auto &t : per_layer) JUNO_TRY(put("blk." + std::to_string(l) + "." + t.suffix + ".weight", t.kind, l, false));
     return JUNO_OK;
 }
 

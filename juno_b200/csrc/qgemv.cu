@@ -351,17 +351,13 @@ __device__ __forceinline__ void st_pair(float *slot, size_t idx, float v, unsign
     const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
     asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(slot) + idx), "l"(w) : "memory");
 }
-__device__ __noinline__ void ld8_tagged(const float *slot, size_t idx, unsigned want, unsigned *failed, unsigned *err, unsigned code,
-                                        float (&o)[8]) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint2 *>(slot) + idx);
-    uint4 a, b, c, d;
+__device__ __forceinline__ void ld4_tagged(const uint4 *p, unsigned want, unsigned *failed, unsigned *err, unsigned code, float *o) {
+    uint4 a, b;
     long long t0 = 0;
     for (int spin = 0;; spin++) {
         a = ld_pairs(p);
         b = ld_pairs(p + 1);
-        c = ld_pairs(p + 2);
-        d = ld_pairs(p + 3);
-        if (a.y == want && a.w == want && b.y == want && b.w == want && c.y == want && c.w == want && d.y == want && d.w == want) break;
+        if (a.y == want && a.w == want && b.y == want && b.w == want) break;
         if (*reinterpret_cast<volatile unsigned *>(failed) != 0u) break;
         if (spin == 0) {
             t0 = clock64();
@@ -371,17 +367,26 @@ __device__ __noinline__ void ld8_tagged(const float *slot, size_t idx, unsigned 
             break;
         }
     }
-    o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.z); o[2] = __uint_as_float(b.x); o[3] = __uint_as_float(b.z);
-    o[4] = __uint_as_float(c.x); o[5] = __uint_as_float(c.z); o[6] = __uint_as_float(d.x); o[7] = __uint_as_float(d.z);
+    o[0] = __uint_as_float(a.x);
+    o[1] = __uint_as_float(a.z);
+    o[2] = __uint_as_float(b.x);
+    o[3] = __uint_as_float(b.z);
+}
+__device__ __forceinline__ void ld8_tagged(const float *slot, size_t idx, unsigned want, unsigned *failed, unsigned *err, unsigned code,
+                                           float (&o)[8]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint2 *>(slot) + idx);
+    ld4_tagged(p, want, failed, err, code, o);
+    ld4_tagged(p + 2, want, failed, err, code, o + 4);
 }
 // Issues the loads of one (row, slice) pair; nothing here waits for them (unless there are several addends).
+template <bool TAGGED>
 __device__ __forceinline__ void quantize_fetch(const QSrc &q, int b, int sb, int lane, QIn &in) {
     const size_t roff = (size_t)b * q.ldx + sb * 256 + lane * 8;
     ld8(q.x + roff, in.v);
     if (q.add0) {
         // partial products are summed first, in the order given (TensorParallelPipelineClient.allReduceSum :244-272 adds
         // rank 0..N-1), then added to the residual row (LlamaTransformerHandler.add :1738-1743)
-        if (q.tag)
+        if (TAGGED)
             ld8_tagged(q.add0, roff, q.tag, q.failed, q.err, 3u, in.s);
         else
             ld8(q.add0 + roff, in.s);
@@ -390,7 +395,7 @@ __device__ __forceinline__ void quantize_fetch(const QSrc &q, int b, int sb, int
         for (int k = 0; k < 7; k++) {
             if (!more[k]) break;
             float t[8];
-            if (q.tag)
+            if (TAGGED)
                 ld8_tagged(more[k], roff, q.tag, q.failed, q.err, 3u | ((unsigned)(k + 1) << 8), t);
             else
                 ld8(more[k] + roff, t);
@@ -560,7 +565,9 @@ struct QCursor {
     int T, i;
 };
 
-template <int TYPE, int NT, int OCC>
+// TAGGED: the addends are (value, step number) pairs from other GPUs (a kernel of its own, so that the polling loads
+// cost the single-GPU kernels no registers).
+template <int TYPE, int NT, int OCC, bool TAGGED>
 __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) {
     using B = XBlk<TYPE>;
     constexpr int NSEQ = 2 * NT;
@@ -630,7 +637,7 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
             const int b = pr / NB, sb = pr - b * NB;
             QIn t;
             float w8[8];
-            quantize_fetch(q, b, sb, lane, t);
+            quantize_fetch<TAGGED>(q, b, sb, lane, t);
             if (q.normw) ld8(q.normw + sb * 256 + lane * 8, w8);
             float part = 0.f;
             quantize_slice<TYPE>(q, b, sb, lane, t, w8, xop + (size_t)pr * B::bytes, part);
@@ -817,7 +824,7 @@ static void qgemv_geometry(const juno_ctx *ctx, int NB, int total_rt, int occ, i
     *grid_out = std::max(1, std::min(slots, *ntasks_out));
 }
 
-template <int TYPE, int NT, int OCC>
+template <int TYPE, int NT, int OCC, bool TAGGED>
 static int qlaunch_inst(juno_ctx *ctx, const QParams &p, int grid, size_t smem, cudaStream_t st) {
     static std::mutex mu;
     static bool configured[64] = {false};
@@ -825,21 +832,24 @@ static int qlaunch_inst(juno_ctx *ctx, const QParams &p, int grid, size_t smem, 
         std::lock_guard<std::mutex> g(mu);
         const int dev = ctx->device & 63;
         if (!configured[dev]) {
-            JUNO_CUDA_TRY(cudaFuncSetAttribute(qgemv_kernel<TYPE, NT, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin));
+            JUNO_CUDA_TRY(cudaFuncSetAttribute(qgemv_kernel<TYPE, NT, OCC, TAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin));
             configured[dev] = true;
         }
     }
-    JUNO_CUDA_TRY(launch_pdl(qgemv_kernel<TYPE, NT, OCC>, dim3(grid), dim3(kQThreads), smem, st, p));
+    JUNO_CUDA_TRY(launch_pdl(qgemv_kernel<TYPE, NT, OCC, TAGGED>, dim3(grid), dim3(kQThreads), smem, st, p));
     ctx->kernel_launches++;
     return JUNO_OK;
 }
 template <int TYPE>
 static int qlaunch_type(juno_ctx *ctx, const QParams &p, int occ, int grid, size_t smem, cudaStream_t st) {
+    const bool tg = p.tagged_adds != 0;
     switch ((p.bc + 1) / 2) {
-    case 1: return occ == 2 ? qlaunch_inst<TYPE, 1, 2>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 1, 1>(ctx, p, grid, smem, st);
-    case 2: return qlaunch_inst<TYPE, 2, 1>(ctx, p, grid, smem, st);
-    case 3: return qlaunch_inst<TYPE, 3, 1>(ctx, p, grid, smem, st);
-    case 4: return qlaunch_inst<TYPE, 4, 1>(ctx, p, grid, smem, st);
+    case 1:
+        if (occ == 2) return tg ? qlaunch_inst<TYPE, 1, 2, true>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 1, 2, false>(ctx, p, grid, smem, st);
+        return tg ? qlaunch_inst<TYPE, 1, 1, true>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 1, 1, false>(ctx, p, grid, smem, st);
+    case 2: return tg ? qlaunch_inst<TYPE, 2, 1, true>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 2, 1, false>(ctx, p, grid, smem, st);
+    case 3: return tg ? qlaunch_inst<TYPE, 3, 1, true>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 3, 1, false>(ctx, p, grid, smem, st);
+    case 4: return tg ? qlaunch_inst<TYPE, 4, 1, true>(ctx, p, grid, smem, st) : qlaunch_inst<TYPE, 4, 1, false>(ctx, p, grid, smem, st);
     default: break;
     }
     set_error("qgemv: unsupported batch chunk %d", p.bc);

@@ -108,11 +108,25 @@ class B200TransformerHandler:
               "juno_model_set_tensor")
 
     def load(self, tensors) -> "B200TransformerHandler":
-        """tensors: iterable of (kind, layer, ggml_type, rows, cols, blocks) — synth.random_model or gguf.model_tensors."""
+        """tensors: iterable of (kind, layer, ggml_type, rows, cols, blocks), e.g. synth.random_model."""
         for kind, layer, t, rows, cols, blocks in tensors:
             self.set_tensor(kind, layer, blocks, t, rows, cols)
         check(self._L.juno_model_finalize(self.handle), "juno_model_finalize")
         return self
+
+    def load_gguf(self, gguf) -> "B200TransformerHandler":
+        """Every tensor the reference constructor reads (LlamaTransformerHandler.java:238-275), straight from the mapped
+        file (gguf: gguf_file.GgufFile)."""
+        check(self._L.juno_model_load_gguf(self.handle, gguf.handle), "juno_model_load_gguf")
+        check(self._L.juno_model_finalize(self.handle), "juno_model_finalize")
+        return self
+
+    @classmethod
+    def from_gguf(cls, path, ctx: GpuContext | None = None, **kw) -> "B200TransformerHandler":
+        """The reference's load path in one call: GgufReader.open, LlamaConfig.from, the handler constructor."""
+        from .gguf_file import GgufFile
+        with GgufFile(path) as g:
+            return cls(g.arch(), ctx, **kw).load_gguf(g)
 
     # ── ForwardPassHandler ─────────────────────────────────────────────────────
     def is_ready(self) -> bool:

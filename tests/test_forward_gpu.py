@@ -310,3 +310,52 @@ def test_greedy_identity_batch_16_and_64_exact_path(ctx, oracle, n_seq, monkeypa
     assert n_near_ties <= n_seq // 16, n_near_ties  # and such near-ties are rare
     h.release_gpu_resources()
     om.close()
+
+
+@pytest.mark.parametrize("tied", [False, True], ids=["q6k-output", "tied-output"])
+def test_model_loaded_from_a_gguf_file(ctx, oracle, tmp_path, tied):
+    """The reference's load path end to end: a GGUF file on disk -> juno_gguf_open -> LlamaConfig.from ->
+    juno_model_load_gguf.  The oracle reads the same file through the restated Java parser.  As in real Q4_K_M
+    files, output.weight is Q6_K; without output.weight the projection is tied to token_embd."""
+    from juno_b200 import gguf_file
+    from juno_b200.handler import B200TransformerHandler
+    from oracle import gguf_reader as oref
+
+    def type_map(kind):
+        return synth.Q6_K if kind == synth.T_OUTPUT else synth.q4_k_m_type(kind)
+
+    arch = SMALL128
+    path = tmp_path / "model.gguf"
+    gguf_file.write_model(path, arch, synth.random_model(arch, 31, type_map, norm="random"), tied_output=tied)
+    h = B200TransformerHandler.from_gguf(path, ctx, max_batch=2, max_seqs=2, max_ctx=64, kv_dtype="f32")
+    assert (h.arch.hidden, h.arch.n_layers, h.arch.n_kv_heads, h.arch.vocab) == (arch.hidden, arch.n_layers, arch.n_kv_heads, arch.vocab)
+    r = oref.GgufReader(path)
+    c = oref.llama_config(r)
+    om = oracle.Model(c["hidden"], c["n_layers"], c["n_heads"], c["n_kv_heads"], c["inter"], c["vocab"], c["rms_eps"], c["rope_theta"],
+                      kv_f16=False, max_seq=64)
+    for kind, layer, t, rows, cols, raw in oref.model_tensors(r, c["n_layers"]):
+        om.set_tensor(kind, layer, raw, t, rows, cols)
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, arch.vocab, 12).tolist()
+    seq = om.new_seq()
+    for p, t in enumerate(prompt):
+        ref = om.forward(seq, t, p)
+        got = h.forward(ForwardRequest("f", prompt[: p + 1], p)).logits
+        assert rel_err(got, ref) < TOL
+    ref_ids, _ = om.generate_greedy(om.new_seq(), prompt, 24)
+    assert generate_greedy(B200InferencePipeline(h), "g", prompt, 24) == ref_ids.tolist()
+    h.release_gpu_resources()
+
+
+def test_gguf_with_qkv_bias_is_refused(ctx, tmp_path):
+    """Qwen2-style attn_{q,k,v}.bias tensors (LlamaTransformerHandler.java:258-262) are not applied by this library:
+    loading such a file fails loudly instead of computing without them."""
+    from juno_b200 import _lib, gguf_file
+    from juno_b200.handler import B200TransformerHandler
+    arch = TINY
+    entries = list(gguf_file.model_tensor_entries(synth.random_model(arch, 32)))
+    entries.append(("blk.0.attn_q.bias", 0, [arch.hidden], np.zeros(arch.hidden, np.float32)))
+    path = tmp_path / "bias.gguf"
+    gguf_file.write_gguf(path, gguf_file.llama_metadata(arch), entries)
+    with pytest.raises(_lib.JunoError, match="bias"):
+        B200TransformerHandler.from_gguf(path, ctx, max_ctx=32)
