@@ -246,8 +246,10 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+// K/V pages are read once per step: evict-first, so that they do not push the activations, the norm weights and the
+// kernels' instructions out of the L2.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint64_t pol) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol) : "memory");
 }
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
@@ -282,14 +284,16 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_mma_kernel(const AttnP
     __half *my_kv = sm_kv + (size_t)warp * 4 * TILE;
     const uint32_t my_kv_s = (uint32_t)__cvta_generic_to_shared(my_kv);
     const int pg0 = t0 >> 4, pg1 = (t1 + 15) >> 4;
+    uint64_t l2_pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(l2_pol));
     auto issue = [&](int pg, int stage) {  // this warp's copy of page pg into its stage
         const size_t off = layer_off + (size_t)table[pg] * page_stride;
         const uint32_t kd = my_kv_s + (uint32_t)(stage * 2 * TILE) * 2u, vd = kd + TILE * 2u;
 #pragma unroll
         for (int i = 0; i < HD / 16; i++) {  // 16 rows x HD/8 chunks of 16 bytes = 32 lanes x HD/16
             const int ch = i * 32 + lane, row = ch / (HD / 8), col8 = ch - row * (HD / 8);
-            cp_async_16(kd + (uint32_t)(row * LDT + col8 * 8) * 2u, kbase + off + (size_t)row * HD + col8 * 8);
-            cp_async_16(vd + (uint32_t)(row * LDT + col8 * 8) * 2u, vbase + off + (size_t)row * HD + col8 * 8);
+            cp_async_16(kd + (uint32_t)(row * LDT + col8 * 8) * 2u, kbase + off + (size_t)row * HD + col8 * 8, l2_pol);
+            cp_async_16(vd + (uint32_t)(row * LDT + col8 * 8) * 2u, vbase + off + (size_t)row * HD + col8 * 8, l2_pol);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };

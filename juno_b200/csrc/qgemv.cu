@@ -538,9 +538,16 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, unsigned parity, unsigne
             : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, unsigned bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
+// Weight tiles are read once per step: they are requested with the evict-first policy, so that the gigabytes streamed
+// through the L2 do not push out what every kernel start needs again (activations, norm weights, instructions).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, unsigned bytes, uint32_t bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar), "l"(pol)
                  : "memory");
 }
 // A wait on a weight tile gives up after this many SM cycles (about a fifth of a second); after the first give-up
@@ -593,6 +600,7 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     QCursor pc{(int)blockIdx.x, 0};
     const uint8_t *pc_src = nullptr;  // source of the next copy inside the current span
     unsigned pc_bytes = 0;
+    const uint64_t l2_pol = l2_evict_first_policy();
     auto produce = [&](int slot) {  // lane 0 only
         if (n_span == 0 || pc.T >= p.n_tasks) return;
         if (pc.i == 0) {
@@ -606,7 +614,7 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
             pc_bytes = (unsigned)tile_bytes(ty);
         }
         mbar_expect_tx(my_bars + slot * 8, pc_bytes);
-        bulk_g2s(my_ring + slot * p.slot_bytes, pc_src, pc_bytes, my_bars + slot * 8);
+        bulk_g2s(my_ring + slot * p.slot_bytes, pc_src, pc_bytes, my_bars + slot * 8, l2_pol);
         pc_src += pc_bytes;
         if (++pc.i == n_span) {
             pc.i = 0;
@@ -621,6 +629,10 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     }
     __syncwarp();
 
+    // The RMSNorm weights are model data: those of the warp's first slice are requested before the wait, so that their
+    // trip to DRAM overlaps the end of the producing kernel.
+    float w8[8];
+    if (p.normw && warp < p.bc * NB) ld8(p.normw + (warp % NB) * 256 + lane * 8, w8);
     pdl_wait();  // everything below reads what earlier kernels of the stream wrote
     bool failed = false;
     const unsigned step_no = (p.tagged_adds || p.n_peers) ? *reinterpret_cast<const volatile unsigned *>(p.epoch) : 0u;
@@ -636,9 +648,8 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
         for (int pr = warp; pr < pairs; pr += kQWarps) {
             const int b = pr / NB, sb = pr - b * NB;
             QIn t;
-            float w8[8];
             quantize_fetch<TAGGED>(q, b, sb, lane, t);
-            if (q.normw) ld8(q.normw + sb * 256 + lane * 8, w8);
+            if (q.normw && pr != warp) ld8(q.normw + sb * 256 + lane * 8, w8);
             float part = 0.f;
             quantize_slice<TYPE>(q, b, sb, lane, t, w8, xop + (size_t)pr * B::bytes, part);
 #pragma unroll
@@ -665,7 +676,9 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
 #pragma unroll
             for (int w8 = 0; w8 < kQWarps; w8++) s += ssw[w8 * 8 + tid];
             // rmsNorm (:818-828): 1f / (float) Math.sqrt(ss / n + eps)
-            sc = __fdiv_rn(1.f, (float)sqrt((double)__fadd_rn(__fdiv_rn(s, (float)p.K), p.eps)));
+            // (float) Math.sqrt((double) v) is the correctly rounded single-precision root of v: 53 bits are more than
+            // twice 24 + 2, so the second rounding cannot change the result
+            sc = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s, (float)p.K), p.eps)));
         }
         rs_s[tid] = sc;  // read by the warps that finish tasks: ordered by the task barriers
     }
