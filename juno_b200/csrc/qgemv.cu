@@ -939,7 +939,10 @@ int launch_qgemv(juno_ctx *ctx, const QGemvArgs &a, cudaStream_t st) {
         p.x = a.x + (size_t)b0 * a.ldx;
         for (int k = 0; k < a.n_add; k++) p.add[k] = a.add[k] + (size_t)b0 * a.ldx;
         p.x_store = a.x_store ? a.x_store + (size_t)b0 * a.ldx : nullptr;
-        p.ring = std::max(kQMinRing, std::min(qgemv_ring_slots(ctx, a.K, type_mix, p.bc, occ), q_env_int("JUNO_QGEMV_RING", kQMaxRing)));
+        // Two slots per warp, although more would fit: with 16-32 warps per SM the copies in flight already cover the
+        // bandwidth-delay product, and every further slot only lengthens the queue in front of the loads of x (the
+        // decode step measured 2.5-5 % slower with four to eight slots).
+        p.ring = std::max(kQMinRing, std::min(qgemv_ring_slots(ctx, a.K, type_mix, p.bc, occ), q_env_int("JUNO_QGEMV_RING", 2)));
         const size_t smem = qgemv_fixed_smem(a.K, type_mix, p.bc) + (size_t)kQWarps * p.ring * p.slot_bytes;
         int rc;
         if (type_mix == 0)
