@@ -5,7 +5,9 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cstring>
+#include <thread>
 #include <string>
 #include <map>
 #include <vector>
@@ -30,6 +32,8 @@ struct NcclApi {
     int (*GetUniqueId)(NcclId *) = nullptr;
     int (*CommInitRank)(NcclComm *, int, NcclId, int) = nullptr;
     int (*CommDestroy)(NcclComm) = nullptr;
+    int (*CommAbort)(NcclComm) = nullptr;                 // optional
+    int (*CommGetAsyncError)(NcclComm, int *) = nullptr;  // optional
     int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
@@ -54,6 +58,8 @@ static int nccl_load() {
         (int (*)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t))dlsym(h, "ncclAllReduce");
     g_nccl.AllGather = (int (*)(const void *, void *, size_t, int, NcclComm, cudaStream_t))dlsym(h, "ncclAllGather");
     g_nccl.GetErrorString = (const char *(*)(int))dlsym(h, "ncclGetErrorString");
+    g_nccl.CommAbort = (int (*)(NcclComm))dlsym(h, "ncclCommAbort");
+    g_nccl.CommGetAsyncError = (int (*)(NcclComm, int *))dlsym(h, "ncclCommGetAsyncError");
     if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.CommDestroy || !g_nccl.AllReduce || !g_nccl.AllGather) {
         set_error("libnccl.so.2 lacks a required symbol");
         return JUNO_ERR_NCCL;
@@ -302,6 +308,7 @@ struct juno_model {
     size_t tp_inbox_off = 0, tp_pair_off = 0;
     int tp_bq = 0;                       // sequences an inbox slot holds
     unsigned *tp_failed = nullptr;       // device word: a wait for another rank ran out during this step
+    bool comm_failed = false;            // a collective timed out or NCCL reported an asynchronous error: no further steps
     unsigned *tp_epoch = nullptr;        // step number, incremented on the device at the start of every step
     int batched_from = 9;  // smallest batch on the FP16 one-pass kernels (JUNO_GEMM_MIN_BATCH, read when the model is created)
 };
@@ -363,7 +370,13 @@ static void model_release(juno_model *m) {
     if (m->tp_failed) cudaFree(m->tp_failed);
     if (m->tp_epoch) cudaFree(m->tp_epoch);
     m->tp_buf = nullptr;
-    if (m->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(m->comm);
+    if (m->comm) {
+        // after a failure the peers may be gone: abort (returns at once) instead of the orderly teardown
+        if (m->comm_failed && g_nccl.CommAbort)
+            g_nccl.CommAbort(m->comm);
+        else if (g_nccl.CommDestroy)
+            g_nccl.CommDestroy(m->comm);
+    }
     m->comm = nullptr;
     for (auto &L : m->layers) {
         for (int k = 0; k < 12; k++) free_qmat(L.w[k]);
@@ -1069,6 +1082,10 @@ static int enqueue_step(juno_model *m, int n, int n_splits, bool greedy_advance,
 static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance, bool want_logits) {
     juno_ctx *c = m->ctx;
     cudaStream_t st = c->stream;
+    if (m->comm_failed) {
+        set_error("the tensor-parallel communicator was aborted after a failed step: free the model and build a new group");
+        return JUNO_ERR_NCCL;
+    }
     if (!m->use_graphs || c->profiling) return enqueue_step(m, n, n_splits, greedy_advance, want_logits, st);
     const uint64_t key = ((uint64_t)n << 32) | ((uint64_t)n_splits << 2) | (want_logits ? 2u : 0u) | (greedy_advance ? 1u : 0u);
     JunoGraph &g = m->graphs[key];
@@ -1108,6 +1125,51 @@ static int run_step(juno_model *m, int n, int n_splits, bool greedy_advance, boo
     JUNO_CUDA_TRY(cudaGraphLaunch(g.exec, st));
     c->kernel_launches += launches;
     return JUNO_OK;
+}
+
+// Waits for the step to drain.  A tensor-parallel step can hold NCCL collectives (more than eight sequences, gathered
+// logits, the NCCL exchange mode): if a rank has died they never complete and a plain stream synchronise would block
+// for ever.  So with a communicator the wait polls the stream together with the communicator's asynchronous error
+// state and a deadline (JUNO_NCCL_TIMEOUT_S seconds, default 60); on either it aborts the communicator, which ends
+// the collective kernels in flight, and the model refuses further steps.
+static int step_sync(juno_model *m) {
+    juno_ctx *c = m->ctx;
+    if (m->world <= 1 || !m->comm) {
+        JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+        return JUNO_OK;
+    }
+    static const double limit_s = [] {
+        const char *e = getenv("JUNO_NCCL_TIMEOUT_S");
+        const double v = (e && *e) ? atof(e) : 60.0;
+        return v > 0 ? v : 60.0;
+    }();
+    const auto t0 = std::chrono::steady_clock::now();
+    const char *why = nullptr;
+    int async = 0;
+    for (unsigned spin = 0;; spin++) {
+        const cudaError_t e = cudaStreamQuery(c->stream);
+        if (e == cudaSuccess) return JUNO_OK;
+        if (e != cudaErrorNotReady) JUNO_CUDA_TRY(e);
+        if ((spin & 63) == 63) {
+            if (g_nccl.CommGetAsyncError && g_nccl.CommGetAsyncError(m->comm, &async) == 0 && async != 0 && async != 7 /* in progress */) {
+                why = "NCCL reported an asynchronous error";
+                break;
+            }
+            if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > limit_s) {
+                why = "a collective did not complete before the deadline (a rank may have failed)";
+                break;
+            }
+        }
+        if (spin > 20000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    m->comm_failed = true;
+    if (g_nccl.CommAbort) {
+        g_nccl.CommAbort(m->comm);  // ends the collective kernels in flight
+        m->comm = nullptr;
+        cudaStreamSynchronize(c->stream);
+    }
+    set_error("tensor-parallel step abandoned: %s (async state %d, limit %.0f s); the communicator was aborted", why, async, limit_s);
+    return async != 0 && async != 7 ? JUNO_ERR_NCCL : JUNO_ERR_TIMEOUT;
 }
 
 // After a stream synchronise: did the last step kernel give up on a wait?
@@ -1218,7 +1280,7 @@ int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t 
         JUNO_CUDA_TRY(cudaMemcpyAsync(argmax_out, m->d_argmax, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
         c->d2h_bytes += n * 4;
     }
-    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JUNO_TRY(step_sync(m));
     JUNO_TRY(step_check(m));
     for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + 1);
     m->last_n = n;
@@ -1295,7 +1357,7 @@ int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t
         }
         done += n;
     }
-    JUNO_CUDA_TRY(cudaStreamSynchronize(st));
+    JUNO_TRY(step_sync(m));
     JUNO_TRY(step_check(m));
     seq->len = std::max(seq->len, start_pos + n_tokens);
     return JUNO_OK;
@@ -1331,7 +1393,7 @@ int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const in
     for (int s = 0; s < steps; s++) JUNO_TRY(run_step(m, n, n_splits, true, false));
     c->forward_calls += steps;
     JUNO_CUDA_TRY(cudaMemcpyAsync(out_ids, m->d_out_ids, (size_t)steps * n * 4, cudaMemcpyDeviceToHost, c->stream));
-    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JUNO_TRY(step_sync(m));
     JUNO_TRY(step_check(m));
     c->d2h_bytes += (int64_t)steps * n * 4;
     for (int i = 0; i < n; i++) seqs[i]->len = std::max(seqs[i]->len, positions[i] + steps);

@@ -67,10 +67,12 @@ def test_two_gpu_tensor_parallel_matches_oracle(oracle, push):
     assert np.array_equal(res[0][2], res[1][2])  # both ranks pick the same tokens
 
 
-def _worker_missing_peer(rank, world, nccl_id, q, done):
+def _worker_missing_peer(rank, world, nccl_id, q, done, push=True):
     """Rank 1 stops taking part between steps (nothing of it in flight; the process and its buffers stay until the
     test is over); rank 0 runs one more step alone."""
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["JUNO_TP_PUSH"] = "1" if push else "0"
+    os.environ["JUNO_NCCL_TIMEOUT_S"] = "3"
     from juno_b200 import _lib
     from juno_b200.handler import B200TransformerHandler
     from juno_b200.matvec import GpuContext
@@ -85,7 +87,7 @@ def _worker_missing_peer(rank, world, nccl_id, q, done):
         return
     import time
     time.sleep(1.0)
-    if h.tp_mode() != 2:  # no peer mapping on this system: the step would sit in an NCCL call; nothing to test
+    if push and h.tp_mode() != 2:  # no peer mapping on this system: nothing to test in this mode
         q.put(("result", rank, "skipped: NCCL mode", 0.0))
         return
     t0 = time.time()
@@ -93,7 +95,14 @@ def _worker_missing_peer(rank, world, nccl_id, q, done):
         h.decode_greedy(["a"], [7], [2], 1)
         q.put(("result", rank, "no error", time.time() - t0))
     except _lib.JunoError as e:
-        q.put(("result", rank, f"rc={e.rc}: {e}", time.time() - t0))
+        msg, dt = f"rc={e.rc}: {e}", time.time() - t0
+        if not push:  # the communicator is gone: the model refuses further steps instead of hanging in them
+            try:
+                h.decode_greedy(["a"], [7], [2], 1)
+                msg += " | second step: no error"
+            except _lib.JunoError as e2:
+                msg += f" | second step: rc={e2.rc}"
+        q.put(("result", rank, msg, dt))
 
 
 def test_missing_rank_times_out_instead_of_hanging():
@@ -122,4 +131,32 @@ def test_missing_rank_times_out_instead_of_hanging():
     if res[2].startswith("skipped"):
         pytest.skip(res[2])
     assert f"rc={_lib.ERR_TIMEOUT}" in res[2] and "did not deliver" in res[2], res
+    assert res[3] < 30.0, res
+
+
+def test_missing_rank_in_nccl_mode_is_ended_by_the_watchdog():
+    """The same failure with the NCCL exchange: the all-reduce of the lonely rank can never complete; the step's wait
+    polls the stream with a deadline (JUNO_NCCL_TIMEOUT_S=3 here), aborts the communicator and returns
+    JUNO_ERR_TIMEOUT; later steps are refused with JUNO_ERR_NCCL.  Nothing faults: the abort ends NCCL's own kernel."""
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from juno_b200 import _lib
+    from juno_b200.handler import B200TransformerHandler
+    nccl_id = B200TransformerHandler.nccl_unique_id()
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    done = mpc.Event()
+    procs = [mpc.Process(target=_worker_missing_peer, args=(r, 2, nccl_id, q, done, False)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msgs = [q.get(timeout=300) for _ in range(3)]
+    done.set()
+    for p in procs:
+        p.join(60)
+        if p.is_alive():
+            p.kill()  # this exact child: a teardown that waits for the vanished peer must not hold the suite
+    res = [m for m in msgs if m[0] == "result"][0]
+    assert f"rc={_lib.ERR_TIMEOUT}" in res[2] and "communicator was aborted" in res[2], res
+    assert f"second step: rc={_lib.ERR_NCCL}" in res[2], res
     assert res[3] < 30.0, res
