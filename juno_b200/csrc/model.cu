@@ -5,7 +5,9 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <atomic>
 #include <chrono>
+#include <memory>
 #include <cstring>
 #include <thread>
 #include <string>
@@ -1163,10 +1165,26 @@ static int step_sync(juno_model *m) {
         if (spin > 20000) std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
     m->comm_failed = true;
+    // The captured step graphs hold references on the communicator's plans, and the abort waits for them: mark the
+    // graphs for destruction first (it happens when their run ends).  The abort itself sets the flag that ends the
+    // collective kernels in flight; it runs on a helper thread, so that this call returns even if the teardown
+    // inside the library waits for something that never comes.
+    for (auto &kv : m->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    m->graphs.clear();
     if (g_nccl.CommAbort) {
-        g_nccl.CommAbort(m->comm);  // ends the collective kernels in flight
+        NcclComm comm = m->comm;
         m->comm = nullptr;
-        cudaStreamSynchronize(c->stream);
+        auto aborted = std::make_shared<std::atomic<bool>>(false);
+        std::thread([comm, aborted] {
+            g_nccl.CommAbort(comm);
+            aborted->store(true);
+        }).detach();
+        const auto t1 = std::chrono::steady_clock::now();
+        while (std::chrono::duration<double>(std::chrono::steady_clock::now() - t1).count() < 10.0) {
+            if (aborted->load() && cudaStreamQuery(c->stream) != cudaErrorNotReady) break;
+            std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        }
     }
     set_error("tensor-parallel step abandoned: %s (async state %d, limit %.0f s); the communicator was aborted", why, async, limit_s);
     return async != 0 && async != 7 ? JUNO_ERR_NCCL : JUNO_ERR_TIMEOUT;
@@ -1257,10 +1275,13 @@ int juno_forward(juno_model *m, int32_t n, juno_seq *const *seqs, const int32_t 
     std::lock_guard<std::recursive_mutex> lk(c->mu);
     DeviceGuard g(c->device);
     // the pinned step buffer is reused: the previous step must have consumed it
-    JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JUNO_TRY(step_sync(m));
     int n_splits = 1;
     JUNO_TRY(prepare_step(m, n, seqs, token_ids, positions, 0, &n_splits));
     JUNO_TRY(run_step(m, n, n_splits, false, logits_host != nullptr));
+    // With collectives in the step the guarded wait comes first: a device-to-host copy into pageable memory blocks
+    // the caller until the stream reaches it, and would sit behind a collective that never completes.
+    if (m->world > 1) JUNO_TRY(step_sync(m));
     c->forward_calls++;
     const int V = m->cfg.vocab;
     if (logits_host) {
@@ -1305,7 +1326,7 @@ int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t
     for (int done = 0; done < n_tokens;) {
         const int n = std::min(chunk_max, n_tokens - done), pos0 = start_pos + done;
         const bool last = done + n == n_tokens;
-        JUNO_CUDA_TRY(cudaStreamSynchronize(st));  // the pinned step buffer is reused
+        JUNO_TRY(step_sync(m));  // the pinned step buffer is reused
         JUNO_TRY(seq_reserve(seq, pos0 + n, st));
         for (int i = 0; i < n; i++) {
             m->h_step[i] = token_ids[done + i];
@@ -1391,6 +1412,7 @@ int juno_decode_greedy(juno_model *m, int32_t n, juno_seq *const *seqs, const in
     }
     JUNO_CUDA_TRY(cudaMemsetAsync(m->d_step_counter, 0, 4, c->stream));
     for (int s = 0; s < steps; s++) JUNO_TRY(run_step(m, n, n_splits, true, false));
+    if (m->world > 1) JUNO_TRY(step_sync(m));  // before the copy of the ids, see juno_forward
     c->forward_calls += steps;
     JUNO_CUDA_TRY(cudaMemcpyAsync(out_ids, m->d_out_ids, (size_t)steps * n * 4, cudaMemcpyDeviceToHost, c->stream));
     JUNO_TRY(step_sync(m));
