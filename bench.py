@@ -292,9 +292,11 @@ def main():
     sampler.start()
     c0 = ctx.counters()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()  # no effect without a profiler; with `ncu --profile-from-start off` only the timed steps are seen
     ev0.record(stream)
     ids = h.decode_greedy(names, last, [pos] * B, K)
     ev1.record(stream)
+    torch.cuda.profiler.stop()
     barrier()
     ms = ev0.elapsed_time(ev1)
     c1 = ctx.counters()

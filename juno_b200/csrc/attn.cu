@@ -654,15 +654,14 @@ size_t attn_scratch_floats(int n, int n_heads, int hd, int n_splits) {
     return (size_t)n * n_heads * n_splits * (hd + 2);
 }
 
-// Largest split count the cluster-merged kernel takes: a power of two.  Eight (the portable cluster size) by default:
-// clusters of sixteen are placed later by the scheduler and measured 4 % slower on the batch-1 decode step.
+// Largest split count the cluster-merged kernel takes (a power of two, at most 16); 0 = the splits are always merged by
+// attn_combine_kernel.  Off by default: on the batch-1 decode step at context 2048 the cluster merge measured 7 %
+// slower than eighteen independent splits plus the merge kernel (clusters are placed later and wait for their slowest
+// member twice).  JUNO_ATTN_CLUSTER=8 or 16 switches it on; read at every call so that tests can cover both paths.
 static int attn_cluster_max() {
-    static const int v = [] {
-        const char *e = getenv("JUNO_ATTN_CLUSTER");  // 0: always merge with the separate kernel
-        const int m = e ? atoi(e) : 8;
-        return std::max(0, std::min(m, 16));
-    }();
-    return v;
+    const char *e = getenv("JUNO_ATTN_CLUSTER");
+    const int m = e ? atoi(e) : 0;
+    return std::max(0, std::min(m, 16));
 }
 
 int attn_pick_splits(const juno_ctx *ctx, int n, int n_kv_heads, int max_len) {

@@ -60,11 +60,14 @@ def test_attention_long_context_split(ctx, oracle):
     _run(ctx, oracle, 32, 8, 128, [8192], "f16")
 
 
+@pytest.mark.parametrize("cluster", ["0", "8", "16"])
 @pytest.mark.parametrize("lens", [[2049], [300, 2049, 17], [1025, 1040]])
-def test_attention_cluster_merge_with_empty_split(ctx, oracle, lens):
+def test_attention_merge_with_empty_split(ctx, oracle, lens, cluster, monkeypatch):
     """Lengths just above a multiple of the split size: the splits are rounded up to whole pages, so the last
-    split of a sequence holds no position at all.  With FP16 pages the splits of a (sequence, kv head) form one
-    thread-block cluster and are merged on chip: the empty one must still take part."""
+    split of a sequence holds no position at all.  Both merges are covered: the separate merge kernel (the default)
+    and, with JUNO_ATTN_CLUSTER set, the splits of a (sequence, kv head) as one thread-block cluster merged on chip,
+    where the empty split must still take part."""
+    monkeypatch.setenv("JUNO_ATTN_CLUSTER", cluster)
     _run(ctx, oracle, 32, 8, 128, lens, "f16")
 
 
