@@ -11,12 +11,12 @@
 // integer sub-block scales; one conversion per 256-column tile applies d * 2^e in FP32.  The Q4_K min term and the
 // Q6_K offset of 32 are one more integer MMA per tile against per-sub-block sums of q.
 //
-// Data flow.  One CTA of 16 warps per SM.  A CTA task is G = 16/kin row tiles; the kin warps of a row tile split K
-// into contiguous spans and are summed through shared memory in warp order (bitwise repeatable).  Weights go
-// HBM -> shared memory through a ring of tile slots per warp: each slot is filled by ONE cp.async.bulk that the
-// warp issues itself (completion on an mbarrier) and re-issues as soon as it has used the tile, so every warp keeps
-// ring-1 tiles in flight - about 8 MB across the GPU, what HBM needs at its loaded latency.  The ring is filled
-// before the kernel waits for its predecessor (programmatic dependent launch).  The activation operand is built by
+// Data flow.  CTAs of 16 warps, one or two per SM.  A CTA owns a contiguous range of row tiles (the ranges differ by
+// at most one row tile across the grid); its tiles form one flat sequence that the sixteen warps split evenly
+// (QCursor below), and the partial sums of a row tile are added through shared memory in warp order (bitwise
+// repeatable).  Weights go HBM -> shared memory through a ring of tile slots per warp: each slot is filled by ONE
+// cp.async.bulk that the warp issues itself (completion on an mbarrier, L2 evict-first) and re-issues as soon as it
+// has used the tile.  The ring is filled before the kernel waits for its predecessor (programmatic dependent launch).  The activation operand is built by
 // every CTA from the FP32 rows after that wait: the only data that depends on the predecessor.
 #include <cuda_fp16.h>
 
@@ -41,7 +41,6 @@ struct QParams {
     int rt_begin[4];
     int nseg, total_rt;
     int K, NB;
-    int kin, G, n_tasks;
     int ld_out, epi, bc;
     const float *x;
     int ldx;
@@ -568,8 +567,16 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, unsigned parity,
 constexpr int kQBufs = 2;  // buffers of partial sums (one CTA barrier per task)
 
 // Position of a warp in its sequence of weight tiles: CTA task T (stride gridDim.x), tile i of the warp's span.
+// A CTA owns the row tiles [c * RT / grid, (c+1) * RT / grid) and walks them in chunks of at most kQChunk row tiles.
+// Inside a chunk the tiles (row tile, 256-column block) form one flat sequence of T = row tiles x NB tiles, which is
+// also one contiguous stretch of memory; warp w takes the tiles [w*T/16, (w+1)*T/16).  So the sixteen warps carry the
+// same load whatever the shape (no power-of-two split of K, no idle warps), and because a warp's share is at most NB
+// tiles long it touches at most two row tiles, whose partial sums it leaves in two slots of shared memory.
+constexpr int kQChunk = 16;
 struct QCursor {
-    int T, i;
+    int k;        // chunk
+    int f, fend;  // flat tile range still to request inside chunk k
+    int R, sb;    // row tile and block of tile f
 };
 
 // TAGGED: the addends are (value, step number) pairs from other GPUs (a kernel of its own, so that the polling loads
@@ -582,45 +589,60 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NB = p.NB;
-    // [ring: 16 warps x ring x slot_bytes][operand: bc x NB blocks][partials: kQBufs x (G x 16 rows x NSEQ) x kin][ssw][rs][mbarriers]
+    // [ring: 16 warps x ring x slot_bytes][operand: bc x NB blocks][partials: kQBufs x 16 warps x 2 row tiles x 16 rows x NSEQ][ssw][rs][mbarriers]
     const size_t ring_bytes = (size_t)kQWarps * p.ring * p.slot_bytes;
     uint8_t *xop = smem + ring_bytes;
     float *red = reinterpret_cast<float *>(xop + (size_t)p.bc * NB * B::bytes);
-    float *ssw = red + kQBufs * kQWarps * 16 * NSEQ;  // [16 warps][8] sums of squares of the slices a warp converted
+    float *ssw = red + kQBufs * kQWarps * 2 * 16 * NSEQ;  // [16 warps][8] sums of squares of the slices a warp converted
     float *rs_s = ssw + kQWarps * 8;                  // [8] 1/rms per sequence
     const uint32_t my_ring = smem_u32(smem) + (uint32_t)(warp * p.ring * p.slot_bytes);
-    const uint32_t my_bars = smem_u32(rs_s + 16) + (uint32_t)(warp * p.ring * 8);
+    int *wr_s = reinterpret_cast<int *>(rs_s + 16);   // [kQBufs][kQChunk] first | last << 8 warp of a row tile of the chunk
+    const uint32_t my_bars = smem_u32(wr_s + kQBufs * kQChunk) + (uint32_t)(warp * p.ring * 8);
 
-    // the kin warps of a row tile split the NB slices into contiguous spans (the first NB % kin spans one longer)
-    const int gi = warp / p.kin, kj = warp - gi * p.kin;
-    const int span_base = NB / p.kin, span_rem = NB - span_base * p.kin;
-    const int sb_begin = kj * span_base + min(kj, span_rem), n_span = span_base + (kj < span_rem ? 1 : 0);
+    const int rt0 = (int)(((long long)blockIdx.x * p.total_rt) / gridDim.x);
+    const int rtc = (int)(((long long)(blockIdx.x + 1) * p.total_rt) / gridDim.x) - rt0;
+    const int n_chunks = (rtc + kQChunk - 1) / kQChunk;
+    auto chunk_lo = [&](int k) { return rt0 + (k * rtc) / n_chunks; };  // chunks of equal size up to one row tile
 
     // Fill the ring: weights do not depend on the producer of x.  Lane 0 owns the warp's barriers and copies.
-    QCursor pc{(int)blockIdx.x, 0};
-    const uint8_t *pc_src = nullptr;  // source of the next copy inside the current span
+    QCursor pc{0, 0, 0, 0, 0};
+    const uint8_t *pc_src = nullptr;  // source of the next copy
     unsigned pc_bytes = 0;
-    const uint64_t l2_pol = l2_evict_first_policy();
-    auto produce = [&](int slot) {  // lane 0 only
-        if (n_span == 0 || pc.T >= p.n_tasks) return;
-        if (pc.i == 0) {
-            const int R = pc.T * p.G + gi;
-            if (R >= p.total_rt) {
-                pc.T = p.n_tasks;  // row tiles only grow with T: nothing further for this warp
+    bool pc_fresh = true;             // the address has to be worked out (first tile of a chunk or of a row tile)
+    auto cursor_seek = [&](int k) {   // first chunk from k on in which this warp has tiles
+        for (; k < n_chunks; k++) {
+            const int lo = chunk_lo(k), T = (chunk_lo(k + 1) - lo) * NB;
+            const int f0 = (warp * T) >> 4, f1 = ((warp + 1) * T) >> 4;
+            if (f0 < f1) {
+                const int l = f0 / NB;
+                pc = QCursor{k, f0, f1, lo + l, f0 - l * NB};
+                pc_fresh = true;
                 return;
             }
+        }
+        pc.k = n_chunks;
+    };
+    const uint64_t l2_pol = l2_evict_first_policy();
+    auto produce = [&](int slot) {  // lane 0 only
+        if (pc.k >= n_chunks) return;
+        if (pc_fresh) {  // consecutive tiles of a row tile are contiguous; the next row tile may belong to another matrix
             int ty;
-            pc_src = qtile_addr<TYPE>(p, R, sb_begin, ty);
+            pc_src = qtile_addr<TYPE>(p, pc.R, pc.sb, ty);
             pc_bytes = (unsigned)tile_bytes(ty);
+            pc_fresh = false;
         }
         mbar_expect_tx(my_bars + slot * 8, pc_bytes);
         bulk_g2s(my_ring + slot * p.slot_bytes, pc_src, pc_bytes, my_bars + slot * 8, l2_pol);
         pc_src += pc_bytes;
-        if (++pc.i == n_span) {
-            pc.i = 0;
-            pc.T += gridDim.x;
+        if (++pc.f == pc.fend) {
+            cursor_seek(pc.k + 1);
+        } else if (++pc.sb == NB) {
+            pc.sb = 0;
+            pc.R++;
+            pc_fresh = true;
         }
     };
+    if (lane == 0) cursor_seek(0);
     if (lane == 0) {
         for (int sl = 0; sl < p.ring; sl++) mbar_init(my_bars + sl * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -704,18 +726,24 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
 
     float facc[NT][2];
     const uint32_t xop_s = smem_u32(xop);
-    int slot = 0, it = 0;
+    int slot = 0;
     unsigned parity = 0;
-    for (int T = blockIdx.x; T < p.n_tasks; T += gridDim.x, it++) {
-        const int R = T * p.G + gi;
-        const bool have = (R < p.total_rt) && n_span > 0;
+    for (int k = 0; k < n_chunks; k++) {
+        const int lo = chunk_lo(k), crt = chunk_lo(k + 1) - lo, T = crt * NB;
+        const int f0 = (warp * T) >> 4, f1 = ((warp + 1) * T) >> 4, l_first = f0 / NB;
+        float *cred = red + (size_t)(k & (kQBufs - 1)) * (kQWarps * 2 * 16 * NSEQ);
+        float *myred = cred + warp * (2 * 16 * NSEQ);
+        int f = f0;
+#pragma unroll 1
+        for (int j = 0; j < 2; j++) {  // the (at most two) row tiles this warp's tiles belong to
+            const int l = l_first + j, fe = min(f1, (l + 1) * NB);
+            if (f >= fe) continue;
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) facc[nt][0] = facc[nt][1] = 0.f;
-        if (have) {
-            const int type = (TYPE == 0) ? p.seg_type[qseg_of(p, R)] : TYPE;
-            for (int i = 0; i < n_span; i++) {
+            for (int nt = 0; nt < NT; nt++) facc[nt][0] = facc[nt][1] = 0.f;
+            const int type = (TYPE == 0) ? p.seg_type[qseg_of(p, lo + l)] : TYPE;
+            for (int sb = f - l * NB; f < fe; f++, sb++) {
                 mbar_wait_bounded(my_bars + slot * 8, parity, (unsigned)p.wait_ns, p.err, failed);
-                qcompute<TYPE, NT>(type, my_ring + slot * p.slot_bytes, xop_s + (uint32_t)((sb_begin + i) * B::bytes), lane, L, facc);
+                qcompute<TYPE, NT>(type, my_ring + slot * p.slot_bytes, xop_s + (uint32_t)(sb * B::bytes), lane, L, facc);
                 __syncwarp();  // every lane has used the slot's bytes before lane 0 overwrites them
                 if (lane == 0) produce(slot);
                 if (++slot == p.ring) {
@@ -723,59 +751,53 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
                     parity ^= 1u;
                 }
             }
-        }
-        const int buf = it & (kQBufs - 1);
-        // lanes t and t^1 hold the two halves (limbs 0,1 / limb 2) of a (row, sequence) value
-        float *myred = red + (size_t)buf * (kQWarps * 16 * NSEQ);
+            // lanes t and t^1 hold the two halves (limbs 0,1 / limb 2) of a (row, sequence) value
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const float a = facc[nt][0] + __shfl_xor_sync(0xffffffffu, facc[nt][0], 1);
-            const float c = facc[nt][1] + __shfl_xor_sync(0xffffffffu, facc[nt][1], 1);
-            if ((lane & 1) == 0) {
-                const int seq = 2 * nt + (L.t >> 1);
-                myred[(((gi * 16 + L.g) * NSEQ) + seq) * p.kin + kj] = a;
-                myred[(((gi * 16 + L.g + 8) * NSEQ) + seq) * p.kin + kj] = c;
+            for (int nt = 0; nt < NT; nt++) {
+                const float a = facc[nt][0] + __shfl_xor_sync(0xffffffffu, facc[nt][0], 1);
+                const float c = facc[nt][1] + __shfl_xor_sync(0xffffffffu, facc[nt][1], 1);
+                if ((lane & 1) == 0) {
+                    const int seq = 2 * nt + (L.t >> 1);
+                    myred[(j * 16 + L.g) * NSEQ + seq] = a;
+                    myred[(j * 16 + L.g + 8) * NSEQ + seq] = c;
+                }
             }
         }
-        // One CTA barrier per task: it also keeps the sixteen warps in step, which measured faster than letting
-        // them drift (the warps of a CTA walk one contiguous stretch of the matrix).  The finishing duty rotates; a
-        // partial-sum buffer is rewritten two barriers after its finisher has passed the next one.
+        if (tid < crt) {  // the warps whose tiles reach into row tile `tid` of the chunk: wf1(w) > tlo and wf0(w) < thi
+            const int tlo = tid * NB, thi = tlo + NB;
+            const int w_lo = (16 * (tlo + 1) + T - 1) / T - 1, w_hi = min(kQWarps - 1, (16 * thi + T - 1) / T - 1);
+            wr_s[(k & (kQBufs - 1)) * kQChunk + tid] = w_lo | (w_hi << 8);
+        }
+        // One CTA barrier per chunk.  Two buffers of partial sums: a buffer is rewritten two barriers later, when every
+        // thread has finished reading it.
         __syncthreads();
-        if (warp == (it & (kQWarps - 1))) {
-            // K spans of a row, then the output transform.  Two lanes per output: each adds half of the kin partial
-            // sums in warp order, the halves are added low + high (a fixed order: results are bitwise repeatable).
-            const int rows_out = (p.epi == QEPI_SILU_PAIR) ? 8 : 16;
-            const int per_b = p.G * rows_out, total = per_b * p.bc;
-            const int half = lane & 1, kh = p.kin > 1 ? p.kin >> 1 : 1, k0 = (p.kin > 1) ? half * kh : 0;
-            for (int base = 0; base < total; base += 16) {
-                const int idx = base + (lane >> 1);
-                const bool live = idx < total;
-                const int b = live ? idx / per_b : 0, rg = live ? idx - b * per_b : 0, g = rg / rows_out, row = rg - g * rows_out;
-                const float *cr = myred + (((g * 16 + row) * NSEQ) + b) * p.kin + k0;
-                float v = 0.f, v2 = 0.f;
-                if (live && (p.kin > 1 || half == 0)) {
-                    for (int k2 = 0; k2 < kh; k2++) v += cr[k2];
-                    if (p.epi == QEPI_SILU_PAIR)
-                        for (int k2 = 0; k2 < kh; k2++) v2 += cr[8 * NSEQ * p.kin + k2];
-                }
-                const float vo = __shfl_xor_sync(0xffffffffu, v, 1), v2o = __shfl_xor_sync(0xffffffffu, v2, 1);
-                if (!live || half) continue;
-                v += vo;
-                v2 += v2o;
-                const int Rg = T * p.G + g;
-                if (Rg >= p.total_rt) continue;
-                const int s = qseg_of(p, Rg);
-                const int orow = (Rg - p.rt_begin[s]) * rows_out + row;
-                if (orow >= p.rows[s]) continue;
-                const float sc = rs_s[b];
-                v = __fmul_rn(v, sc);
-                if (p.epi == QEPI_SILU_PAIR) v = __fmul_rn(silu_f(v), __fmul_rn(v2, sc));
-                if (p.n_peers) {
-                    // one 8-byte (value, step number) store per rank over NVLink: the consumer polls the data itself
-                    for (int d = 0; d < p.n_peers; d++) st_pair(p.peer_out[d], (size_t)b * p.ld_out + orow, v, step_no);
-                } else {
-                    p.out[s][(size_t)b * p.ld_out + orow] = v;
-                }
+        // K spans of a row in warp order (a fixed order: results are bitwise repeatable), then the output transform
+        const int rows_sh = (p.epi == QEPI_SILU_PAIR) ? 3 : 4, rows_out = 1 << rows_sh;
+        const int per_b = crt << rows_sh, total = per_b * p.bc;
+        for (int idx = tid; idx < total; idx += kQThreads) {
+            const int b = (p.bc == 1) ? 0 : idx / per_b, rg = idx - b * per_b, l = rg >> rows_sh, row = rg & (rows_out - 1);
+            const int tlo = l * NB, wr = wr_s[(k & (kQBufs - 1)) * kQChunk + l];
+            float v = 0.f, v2 = 0.f;
+            for (int w = wr & 255; w <= (wr >> 8); w++) {
+                const int wf0 = (w * T) >> 4, wf1 = ((w + 1) * T) >> 4;
+                if (wf0 >= wf1) continue;  // with fewer than sixteen tiles in the chunk some warps have none
+                // a warp that started in the row tile before has this one in its second slot
+                const float *cr = cred + w * (2 * 16 * NSEQ) + (wf0 < tlo ? 16 * NSEQ : 0) + b;
+                v += cr[row * NSEQ];
+                if (p.epi == QEPI_SILU_PAIR) v2 += cr[(row + 8) * NSEQ];
+            }
+            const int Rg = lo + l;
+            const int s = qseg_of(p, Rg);
+            const int orow = (Rg - p.rt_begin[s]) * rows_out + row;
+            if (orow >= p.rows[s]) continue;
+            const float sc = rs_s[b];
+            v = __fmul_rn(v, sc);
+            if (p.epi == QEPI_SILU_PAIR) v = __fmul_rn(silu_f(v), __fmul_rn(v2, sc));
+            if (p.n_peers) {
+                // one 8-byte (value, step number) store per rank over NVLink: the consumer polls the data itself
+                for (int d = 0; d < p.n_peers; d++) st_pair(p.peer_out[d], (size_t)b * p.ld_out + orow, v, step_no);
+            } else {
+                p.out[s][(size_t)b * p.ld_out + orow] = v;
             }
         }
     }
@@ -797,7 +819,7 @@ static int q_slot_bytes(int type_mix) { return type_mix == 12 ? kQ4KTileBytes : 
 // Shared memory of a launch without its weight ring.
 static size_t qgemv_fixed_smem(int K, int type_mix, int bc) {
     const int nt = (bc + 1) / 2;
-    return (size_t)bc * (K / 256) * xblk_bytes(type_mix) + (size_t)kQBufs * kQWarps * 16 * 2 * nt * 4 + (size_t)kQWarps * 8 * 4 + 64 +
+    return (size_t)bc * (K / 256) * xblk_bytes(type_mix) + (size_t)kQBufs * kQWarps * 2 * 16 * 2 * nt * 4 + (size_t)kQWarps * 8 * 4 + 64 + (size_t)kQBufs * kQChunk * 4 +
            (size_t)kQWarps * kQMaxRing * 8 + 128;
 }
 // Ring slots per warp that fit when `occ` CTAs share an SM (each CTA also pays 1 KB of system shared memory).
@@ -813,28 +835,6 @@ int qgemv_batch_chunk(const juno_ctx *ctx, int K, int type_mix, int batch) {
     int bc = std::min(batch, 8);
     while (bc > 1 && qgemv_ring_slots(ctx, K, type_mix, bc) < kQMinRing) bc--;
     return bc;
-}
-
-// kin (warps per row tile) in {1,2,4,8,16}: the fewest tiles for the busiest warp, with a charge of half a tile per
-// CTA task for its barrier and epilogue.
-static void qgemv_geometry(const juno_ctx *ctx, int NB, int total_rt, int occ, int *kin_out, int *ntasks_out, int *grid_out) {
-    const int slots = ctx->sm_count * occ;
-    int best_kin = kQWarps;
-    double best = 1e30;
-    for (int kin = 1; kin <= kQWarps; kin *= 2) {
-        const int G = kQWarps / kin, tasks = (total_rt + G - 1) / G, waves = (tasks + slots - 1) / slots, nbw = (NB + kin - 1) / kin;
-        const double cost = (double)waves * nbw + 0.5 * waves;
-        if (cost < best - 1e-9) {
-            best = cost;
-            best_kin = kin;
-        }
-    }
-    int kin = q_env_int("JUNO_QGEMV_KIN", best_kin);
-    if (kin < 1 || kin > kQWarps || (kin & (kin - 1))) kin = best_kin;
-    const int G = kQWarps / kin;
-    *kin_out = kin;
-    *ntasks_out = (total_rt + G - 1) / G;
-    *grid_out = std::max(1, std::min(slots, *ntasks_out));
 }
 
 template <int TYPE, int NT, int OCC, bool TAGGED>
@@ -911,9 +911,8 @@ int launch_qgemv(juno_ctx *ctx, const QGemvArgs &a, cudaStream_t st) {
     // two CTAs per SM (64 registers per thread, half the ring each) when the launch is a single n-tile and still gets a ring
     int occ = q_env_int("JUNO_QGEMV_OCC", 2);
     if (occ != 2 || bc_full > 2 || qgemv_ring_slots(ctx, a.K, type_mix, bc_full, 2) < kQMinRing) occ = 1;
-    int grid = 1;
-    qgemv_geometry(ctx, p.NB, total_rt, occ, &p.kin, &p.n_tasks, &grid);
-    p.G = kQWarps / p.kin;
+    // one CTA per slot of the GPU, each with its share of the row tiles (never more CTAs than row tiles)
+    const int grid = std::max(1, std::min(ctx->sm_count * occ, total_rt));
     p.ld_out = a.ld_out;
     p.epi = a.epi;
     p.ldx = a.ldx;
