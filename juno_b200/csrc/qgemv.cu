@@ -809,11 +809,6 @@ static int q_env_int(const char *name, int dflt) {
     return (v && *v) ? atoi(v) : dflt;
 }
 
-bool qgemv_enabled() {
-    static const bool on = q_env_int("JUNO_QGEMV", 1) != 0;
-    return on;
-}
-
 constexpr int kQMinRing = 2, kQMaxRing = 6;
 static int q_slot_bytes(int type_mix) { return type_mix == 12 ? kQ4KTileBytes : type_mix == 8 ? kQ80TileBytes : kQ6KTileBytes; }
 // Shared memory of a launch without its weight ring.

@@ -55,8 +55,6 @@ struct QGemvArgs {
     unsigned *peer_failed = nullptr;
 };
 
-// The integer-MMA kernel is the default for 1..8 sequences; JUNO_QGEMV=0 keeps the bf16-limb kernel (gemv.cu).
-bool qgemv_enabled();
 // Most sequences one launch can take for this K and block format mix (shared memory), at most 8.
 int qgemv_batch_chunk(const juno_ctx *ctx, int K, int type_mix, int batch);
 // Enqueues the product (several launches when the batch exceeds one chunk).  All pointers are device pointers.
