@@ -1,7 +1,7 @@
 // Batched dequant-GEMM for decode batches above eight sequences (and for prompt chunks): Y[b][r] = sum_c w(r,c) x[b][c]
 // in ONE pass over the quantised weights.
 //
-// Where the GEMV kernel (gemv.cu) spends three bf16 limb columns per sequence to keep the products exact, this kernel
+// Where the GEMV kernel (qgemv.cu) spends three int8 limb columns per sequence to keep the products exact, this kernel
 // treats the batch as a real dense contraction: a warp owns one 16-row tile of the weights for the whole of K, turns
 // each 16x256 quantised tile in registers into FP16 A fragments (w = (d*sc)*q - dmin*m, scale and min in FP16, the
 // integer q exact), and multiplies it with mma.sync.m16n8k16 (f16 in, f32 accumulate) against the activations, one

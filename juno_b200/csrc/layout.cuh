@@ -126,19 +126,4 @@ JHD void q80_elem_loc(int row16, int e, int &byte_off, int &d_off) {
     d_off = 4096 + row16 * 16 + j * 2;
 }
 
-// ── activation operand in shared memory ─────────────────────────────────────────
-// x is split into three bf16 limbs (x = hi + mid + lo exactly) and stored per s16 sub-block and
-// column (column = 3*batch_index + limb) as four bf16 in feed order:
-//   xb[((s16 * ncols + col) * 4 + c) * 4 + feed_pos(t)]      (16-bit elements)
-JHD int xb_index(int k, int ncols, int col) {
-    int s16 = k >> 4, c = (k >> 2) & 3, t = k & 3;
-    return ((s16 * ncols + col) * 4 + c) * 4 + feed_pos(t);
-}
-// Sums of x over 32-column sub-blocks (Q4_K min term), also as three bf16 limbs:
-//   xs[((sb * ncols + col) * 4 + c) * 2 + which]  with 32-sub-block j = 2c + which of super-block sb
-JHD int xs_index(int sub32, int ncols, int col) {
-    int sb = sub32 >> 3, j = sub32 & 7;
-    return ((sb * ncols + col) * 4 + (j >> 1)) * 2 + (j & 1);
-}
-
 }  // namespace juno

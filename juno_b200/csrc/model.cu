@@ -1190,7 +1190,7 @@ static int step_sync(juno_model *m) {
     return async != 0 && async != 7 ? JUNO_ERR_NCCL : JUNO_ERR_TIMEOUT;
 }
 
-// After a stream synchronise: did the last step kernel give up on a wait?
+// After the step has drained: did one of its kernels give up on a wait?
 static int step_check(juno_model *m) {
     if (m->tc_err && m->tc_used) {
         m->tc_used = false;
