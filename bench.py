@@ -364,10 +364,10 @@ def main():
                          "algo_bytes_per_launch": bytes_per_step / launches_per_step,
                          "how": "achieved = algo_bytes_per_step / (share_of_step * ms_per_step)"})
         if B < 9:
-            # ncu on this kernel: dram read + write = 1.03 x the algorithmic bytes on the 28672x4096 and 128256x4096
-            # launches (no re-reads; the excess is the byte-wide scale header of the tile layout)
+            # ncu on this kernel: dram read + write = 1.03 x the algorithmic bytes on the 28672x4096 and 32000x4096
+            # launches of the 4-layer profiling model (no re-reads; the excess is the byte-wide scale header of the tile layout)
             roofline["traffic"] = 1.03 * bytes_per_step / launches_per_step
-            roofline["traffic_source"] = "ncu captures of the 28672x4096 and 128256x4096 launches, scaled by algorithmic bytes"
+            roofline["traffic_source"] = "ncu captures of the 28672x4096 and 32000x4096 launches (same kernel and K), scaled by algorithmic bytes"
     step_roof = roofline["step"]
     kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
                    "gbs": (v["algo_bytes"] / (v["ms"] / 1e3) / 1e9 if v["ms"] > 0 and v["algo_bytes"] > 0 else None)}
