@@ -310,6 +310,8 @@ struct juno_model {
     size_t tp_inbox_off = 0, tp_pair_off = 0;
     int tp_bq = 0;                       // sequences an inbox slot holds
     unsigned *tp_failed = nullptr;       // device word: a wait for another rank ran out during this step
+    float *tp_red = nullptr;             // [2 * n_layers][tp_bq][hidden] (value, step) pairs: the ranks' partials added by the first CTAs
+    bool tp_reduce = false;              // consumers poll tp_red instead of every rank's inbox (four ranks and more)
     bool comm_failed = false;            // a collective timed out or NCCL reported an asynchronous error: no further steps
     unsigned *tp_epoch = nullptr;        // step number, incremented on the device at the start of every step
     int batched_from = 9;  // smallest batch on the FP16 one-pass kernels (JUNO_GEMM_MIN_BATCH, read when the model is created)
@@ -370,6 +372,7 @@ static void model_release(juno_model *m) {
         if (m->tp_peer[r] && m->tp_peer[r] != m->tp_buf) cudaIpcCloseMemHandle(m->tp_peer[r]);
     if (m->tp_buf) cudaFree(m->tp_buf);
     if (m->tp_failed) cudaFree(m->tp_failed);
+    if (m->tp_red) cudaFree(m->tp_red);
     if (m->tp_epoch) cudaFree(m->tp_epoch);
     m->tp_buf = nullptr;
     if (m->comm) {
@@ -454,6 +457,14 @@ static int tp_push_setup(juno_model *m) {
     JUNO_CUDA_TRY(cudaMemset(m->tp_buf, 0, bytes));
     JUNO_TRY(dev_alloc((void **)&m->tp_failed, 4));
     JUNO_CUDA_TRY(cudaMemset(m->tp_failed, 0, 4));
+    JUNO_TRY(dev_alloc((void **)&m->tp_red, (size_t)n_inst * m->tp_bq * H * 8));
+    JUNO_CUDA_TRY(cudaMemset(m->tp_red, 0, (size_t)n_inst * m->tp_bq * H * 8));
+    {
+        // every CTA reading every rank's inbox costs L2 bandwidth in proportion to the ranks (measured 2.2 / 4.9 / 10.9 us
+        // per exchange at 2 / 4 / 8 ranks); from four ranks on the first CTAs add the inboxes once for all
+        const char *r = getenv("JUNO_TP_REDUCE");
+        m->tp_reduce = (r && *r) ? atoi(r) != 0 : W >= 4;
+    }
     JUNO_TRY(dev_alloc((void **)&m->tp_epoch, 4));
     JUNO_CUDA_TRY(cudaMemset(m->tp_epoch, 0, 4));
     cudaIpcMemHandle_t mine, all[8];
@@ -907,7 +918,17 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
         a.ldx = H;
         a.normw = normw;
         a.eps = f.rms_eps;
-        if (pend_inst >= 0) {
+        if (pend_inst >= 0 && m->tp_reduce) {
+            a.red_dst = m->tp_red + (size_t)pend_inst * m->tp_bq * H * 2;
+            for (int k = 0; k < W; k++) a.red_src[k] = inbox(m->rank, pend_inst, k);
+            a.n_red = W;
+            a.add[0] = a.red_dst;
+            a.n_add = 1;
+            a.tagged_adds = true;
+            a.epoch = m->tp_epoch;
+            a.peer_failed = m->tp_failed;
+            a.x_store = m->x[cur ^ 1];
+        } else if (pend_inst >= 0) {
             for (int k = 0; k < W; k++) a.add[k] = inbox(m->rank, pend_inst, k);
             a.n_add = W;
             a.tagged_adds = true;

@@ -56,6 +56,9 @@ struct QParams {
     int n_peers;
     float *peer_out[kQMaxAdd];
     int tagged_adds;
+    int n_red;                       // TAGGED kernels: pre-reduction of the ranks' inbox slots by the first CTAs
+    const float *red_src[kQMaxAdd];
+    float *red_dst;
     const unsigned *epoch;
     unsigned *peer_failed;
     unsigned *err;  // device word: a wait on a weight tile gave up (code | warp << 8 | block << 16)
@@ -658,6 +661,24 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     pdl_wait();  // everything below reads what earlier kernels of the stream wrote
     bool failed = false;
     const unsigned step_no = (p.tagged_adds || p.n_peers) ? *reinterpret_cast<const volatile unsigned *>(p.epoch) : 0u;
+    if (TAGGED && p.n_red > 0 && warp == 0) {
+        // The first CTAs add the ranks' partial products of one (sequence, slice) each, in rank order, and publish the
+        // sums as (value, step number) pairs; all CTAs (these too) then poll one vector instead of n_red.
+        for (int pr = blockIdx.x; pr < p.bc * NB; pr += gridDim.x) {
+            const int b = pr / NB, sb = pr - b * NB;
+            const size_t roff = (size_t)b * p.ldx + sb * 256 + lane * 8;
+            float acc[8];
+            ld8_tagged(p.red_src[0], roff, step_no, p.peer_failed, p.err, 3u, acc);
+            for (int k = 1; k < p.n_red; k++) {
+                float t[8];
+                ld8_tagged(p.red_src[k], roff, step_no, p.peer_failed, p.err, 3u | ((unsigned)k << 8), t);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[i] = __fadd_rn(acc[i], t[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) st_pair(p.red_dst, roff + i, acc[i], step_no);
+        }
+    }
     // operand: every warp converts (sequence, slice) pairs warp, warp+16, ...
     {
         const QSrc q{p.x, p.n_add > 0 ? p.add[0] : nullptr, p.n_add > 1 ? p.add[1] : nullptr, p.n_add > 2 ? p.add[2] : nullptr, p.n_add > 3 ? p.add[3] : nullptr,
@@ -922,6 +943,10 @@ int launch_qgemv(juno_ctx *ctx, const QGemvArgs &a, cudaStream_t st) {
         p.peer_out[d] = a.peer_out[d];
     }
     p.tagged_adds = a.tagged_adds ? 1 : 0;
+    p.n_red = a.tagged_adds ? a.n_red : 0;
+    for (int k = 0; k < p.n_red; k++) p.red_src[k] = a.red_src[k];
+    p.red_dst = a.red_dst;
+    if (p.n_red) JUNO_REQUIRE(a.red_dst && a.n_add == 1 && a.add[0] == a.red_dst, "qgemv: with a pre-reduction the only addend is its result");
     p.epoch = a.epoch;
     p.peer_failed = a.peer_failed;
     if (a.n_peers) JUNO_REQUIRE(a.nseg == 1 && a.epoch && a.epi == QEPI_STORE, "qgemv: a pushed product is one matrix with a plain store");

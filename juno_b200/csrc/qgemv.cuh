@@ -51,6 +51,13 @@ struct QGemvArgs {
     // ranks 0..n_add-1; every load re-reads until the pairs carry `*epoch` (bounded: about a second, then
     // *peer_failed is set, the error word says which rank, and every later wait gives up at once).
     bool tagged_adds = false;
+    // With many ranks every CTA reading every inbox costs more than the smaller matrices save (the L2 reads grow with
+    // CTAs x ranks).  With n_red > 0 the first CTAs of the grid first add the inbox slots red_src[0..n_red) of one
+    // 256-column slice each, in rank order, and publish the sums as pairs in `red_dst` (local memory, same layout as an
+    // inbox slot); add[0] must then be red_dst, which every CTA polls as its single addend.
+    int n_red = 0;
+    const float *red_src[kQMaxAdd] = {nullptr};
+    float *red_dst = nullptr;
     const unsigned *epoch = nullptr;
     unsigned *peer_failed = nullptr;
 };
