@@ -27,6 +27,7 @@
 #include "gemv.cuh"
 #include "layout.cuh"
 #include "qgemv.cuh"
+#include "qsplit.cuh"
 
 namespace juno {
 
@@ -575,7 +576,6 @@ constexpr int kQBufs = 2;  // buffers of partial sums (one CTA barrier per task)
 // also one contiguous stretch of memory; warp w takes the tiles [w*T/16, (w+1)*T/16).  So the sixteen warps carry the
 // same load whatever the shape (no power-of-two split of K, no idle warps), and because a warp's share is at most NB
 // tiles long it touches at most two row tiles, whose partial sums it leaves in two slots of shared memory.
-constexpr int kQChunk = 16;
 struct QCursor {
     int k;        // chunk
     int f, fend;  // flat tile range still to request inside chunk k
@@ -602,10 +602,10 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     int *wr_s = reinterpret_cast<int *>(rs_s + 16);   // [kQBufs][kQChunk] first | last << 8 warp of a row tile of the chunk
     const uint32_t my_bars = smem_u32(wr_s + kQBufs * kQChunk) + (uint32_t)(warp * p.ring * 8);
 
-    const int rt0 = (int)(((long long)blockIdx.x * p.total_rt) / gridDim.x);
-    const int rtc = (int)(((long long)(blockIdx.x + 1) * p.total_rt) / gridDim.x) - rt0;
-    const int n_chunks = (rtc + kQChunk - 1) / kQChunk;
-    auto chunk_lo = [&](int k) { return rt0 + (k * rtc) / n_chunks; };  // chunks of equal size up to one row tile
+    int rt0, rtc;
+    qsplit_cta((int)blockIdx.x, (int)gridDim.x, p.total_rt, rt0, rtc);
+    const int n_chunks = qsplit_chunks(rtc);
+    auto chunk_lo = [&](int k) { return qsplit_chunk_lo(rt0, rtc, n_chunks, k); };
 
     // Fill the ring: weights do not depend on the producer of x.  Lane 0 owns the warp's barriers and copies.
     QCursor pc{0, 0, 0, 0, 0};
@@ -615,7 +615,8 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     auto cursor_seek = [&](int k) {   // first chunk from k on in which this warp has tiles
         for (; k < n_chunks; k++) {
             const int lo = chunk_lo(k), T = (chunk_lo(k + 1) - lo) * NB;
-            const int f0 = (warp * T) >> 4, f1 = ((warp + 1) * T) >> 4;
+            int f0, f1;
+            qsplit_warp(warp, T, f0, f1);
             if (f0 < f1) {
                 const int l = f0 / NB;
                 pc = QCursor{k, f0, f1, lo + l, f0 - l * NB};
@@ -751,7 +752,9 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
     unsigned parity = 0;
     for (int k = 0; k < n_chunks; k++) {
         const int lo = chunk_lo(k), crt = chunk_lo(k + 1) - lo, T = crt * NB;
-        const int f0 = (warp * T) >> 4, f1 = ((warp + 1) * T) >> 4, l_first = f0 / NB;
+        int f0, f1;
+        qsplit_warp(warp, T, f0, f1);
+        const int l_first = f0 / NB;
         float *cred = red + (size_t)(k & (kQBufs - 1)) * (kQWarps * 2 * 16 * NSEQ);
         float *myred = cred + warp * (2 * 16 * NSEQ);
         int f = f0;
@@ -784,9 +787,9 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
                 }
             }
         }
-        if (tid < crt) {  // the warps whose tiles reach into row tile `tid` of the chunk: wf1(w) > tlo and wf0(w) < thi
-            const int tlo = tid * NB, thi = tlo + NB;
-            const int w_lo = (16 * (tlo + 1) + T - 1) / T - 1, w_hi = min(kQWarps - 1, (16 * thi + T - 1) / T - 1);
+        if (tid < crt) {  // the warps whose tiles reach into row tile `tid` of the chunk
+            int w_lo, w_hi;
+            qsplit_row_tile_warps(tid, NB, T, w_lo, w_hi);
             wr_s[(k & (kQBufs - 1)) * kQChunk + tid] = w_lo | (w_hi << 8);
         }
         // One CTA barrier per chunk.  Two buffers of partial sums: a buffer is rewritten two barriers later, when every
@@ -800,7 +803,8 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
             const int tlo = l * NB, wr = wr_s[(k & (kQBufs - 1)) * kQChunk + l];
             float v = 0.f, v2 = 0.f;
             for (int w = wr & 255; w <= (wr >> 8); w++) {
-                const int wf0 = (w * T) >> 4, wf1 = ((w + 1) * T) >> 4;
+                int wf0, wf1;
+                qsplit_warp(w, T, wf0, wf1);
                 if (wf0 >= wf1) continue;  // with fewer than sixteen tiles in the chunk some warps have none
                 // a warp that started in the row tile before has this one in its second slot
                 const float *cr = cred + w * (2 * 16 * NSEQ) + (wf0 < tlo ? 16 * NSEQ : 0) + b;

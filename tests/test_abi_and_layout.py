@@ -83,3 +83,28 @@ def test_tensor_shard_context_geometry():
         TensorShardContext(32, 4096, 8, 8)
     with pytest.raises(ValueError):
         TensorShardContext(31, 4096, 0, 1)
+
+
+def test_gemv_work_split_covers_every_tile_once(layout_host):
+    """The split of a fused dequant-GEMV launch over CTAs, chunks and warps (csrc/qsplit.cuh, the same functions the
+    kernel calls, built for the host): every (row tile, block) exactly once, the request order of a warp equals its use
+    order, the finisher reads exactly the partial-sum slots that were written, and the busiest warp carries at most one
+    row tile's worth of rounding more than the mean."""
+    import ctypes as C
+    import random
+    L = layout_host
+    L.qsplit_check.restype = C.c_int
+    L.qsplit_check.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]
+    # (row tiles, blocks of K, CTAs): the decode-step products of the 8B and 70B architectures on 148 SMs x 1 or 2 CTAs,
+    # their tensor-parallel shards, and degenerate shapes
+    cases = [(384, 16, 148), (256, 16, 256), (1792, 16, 296), (256, 56, 148), (8016, 16, 296), (640, 32, 148), (3584, 32, 296),
+             (512, 112, 148), (896, 16, 296), (128, 8, 128), (1002, 16, 296), (64, 1, 64), (8016, 1, 296), (300, 16, 296),
+             (1, 16, 1), (3, 2, 3), (17, 3, 4), (33, 5, 2), (5000, 7, 296)]
+    rng = random.Random(1)
+    cases += [(rt := rng.randint(1, 3000), rng.randint(1, 60), min(rng.choice([1, 2, 7, 148, 296]), rt)) for _ in range(200)]
+    for rt, nb, grid in cases:
+        busiest = C.c_int()
+        assert L.qsplit_check(rt, nb, grid, C.byref(busiest)) == 0, (rt, nb, grid)
+        per_cta = -(-rt // grid)  # row tiles of the busiest CTA
+        chunks = -(-per_cta // 16)
+        assert busiest.value <= -(-per_cta * nb // 16) + chunks, (rt, nb, grid, busiest.value)
