@@ -29,8 +29,10 @@ extern "C" {
 #define JUNO_ERR_OOM (-2)      /* cudaMalloc failed (the reference string-matches "cudaMalloc",
                                   LlamaTransformerHandler.java:350-352); there is no CPU fallback */
 #define JUNO_ERR_CUDA (-3)
-#define JUNO_ERR_NCCL (-4)
-#define JUNO_ERR_TIMEOUT (-5)
+#define JUNO_ERR_NCCL (-4)     /* NCCL call failed, or the communicator was aborted after a step that timed out */
+#define JUNO_ERR_TIMEOUT (-5)  /* a bounded wait ran out: a weight tile never arrived, or a tensor-parallel rank did not
+                                  deliver (about a second for the peer exchange, JUNO_NCCL_TIMEOUT_S for NCCL steps);
+                                  the context stays usable */
 #define JUNO_ERR_CLOSED (-6)   /* handle already freed (IllegalStateException in MatVec.java:46-54) */
 #define JUNO_ERR_UNSUPPORTED (-7)
 

@@ -568,9 +568,8 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, unsigned parity,
     }
 }
 
-constexpr int kQBufs = 2;  // buffers of partial sums (one CTA barrier per task)
+constexpr int kQBufs = 2;  // buffers of partial sums (one CTA barrier per chunk)
 
-// Position of a warp in its sequence of weight tiles: CTA task T (stride gridDim.x), tile i of the warp's span.
 // A CTA owns the row tiles [c * RT / grid, (c+1) * RT / grid) and walks them in chunks of at most kQChunk row tiles.
 // Inside a chunk the tiles (row tile, 256-column block) form one flat sequence of T = row tiles x NB tiles, which is
 // also one contiguous stretch of memory; warp w takes the tiles [w*T/16, (w+1)*T/16).  So the sixteen warps carry the
@@ -724,7 +723,7 @@ __global__ void __launch_bounds__(kQThreads, OCC) qgemv_kernel(const QParams p) 
             // twice 24 + 2, so the second rounding cannot change the result
             sc = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s, (float)p.K), p.eps)));
         }
-        rs_s[tid] = sc;  // read by the warps that finish tasks: ordered by the task barriers
+        rs_s[tid] = sc;  // read when the outputs of a chunk are finished: ordered by the chunk barrier
     }
 
     LaneX<NT> L;
