@@ -359,3 +359,36 @@ def test_gguf_with_qkv_bias_is_refused(ctx, tmp_path):
     gguf_file.write_gguf(path, gguf_file.llama_metadata(arch), entries)
     with pytest.raises(_lib.JunoError, match="bias"):
         B200TransformerHandler.from_gguf(path, ctx, max_ctx=32)
+
+
+def test_session_reuse_restarts_prefill_at_the_matched_prefix(ctx, oracle):
+    """Multi-turn session as GenerationLoop runs it (GenerationLoop.java:283-294, 385-405): the KV state of a session
+    stays under its key; the next turn's prompt begins with the previous prompt, so its prefill starts at the matched
+    offset and overwrites the positions the previous turn generated into.  Logits of the second turn must equal a run
+    from scratch on the whole second prompt, for the token-by-token prefill and for the chunked one."""
+    arch = SMALL128
+    rng = np.random.default_rng(9)
+    p1 = rng.integers(0, arch.vocab, 20).tolist()
+    p2 = p1 + rng.integers(0, arch.vocab, 12).tolist()
+    om, h = build_pair(oracle, arch, seed=33, kv_dtype="f32", max_ctx=96, max_batch=8, max_seqs=3, ctx=ctx)
+    pipe = B200InferencePipeline(h)
+    # from scratch on the second prompt (oracle), positions 0..31
+    seq = om.new_seq()
+    for p, t in enumerate(p2):
+        ref = om.forward(seq, t, p)
+    for rid, chunked in (("session-a", False), ("session-b", True)):
+        generate_greedy(pipe, rid, p1, 8)  # turn 1: prompt, then 8 generated positions 20..27 in the cache
+        if chunked:
+            h.prefill(rid, p2[len(p1):-1], len(p1))  # turn 2 restarts at the matched prefix (20) and rewrites 20..30
+        else:
+            for p in range(len(p1), len(p2) - 1):
+                h.forward_batch([rid], [[p2[p]]], [p], want_logits=False, want_argmax=True)
+        got = h.forward(ForwardRequest(rid, p2, len(p2) - 1)).logits
+        tol = 5e-3 if chunked else TOL  # the chunked prefill runs FP16 operands (see the chunked-prefill test)
+        assert rel_err(got, ref) < tol, (rid, rel_err(got, ref))
+        assert int(np.argmax(got)) == oracle.greedy(ref)
+    # eviction frees the session's pages for others (KVCacheManager eviction): a third session fits after one is evicted
+    h.evict("session-a")
+    got = h.forward(ForwardRequest("session-c", p2[:1], 0)).logits
+    assert rel_err(got, om.forward(om.new_seq(), p2[0], 0)) < TOL
+    h.release_gpu_resources()
