@@ -178,6 +178,9 @@ typedef struct juno_model_cfg {
 #define JUNO_T_FFN_GATE 9
 #define JUNO_T_FFN_UP 10
 #define JUNO_T_FFN_DOWN 11
+#define JUNO_T_ATTN_Q_BIAS 12 /* optional attn_{q,k,v}.bias (F32 vectors; LlamaTransformerHandler.java:258-262, added to */
+#define JUNO_T_ATTN_K_BIAS 13 /* q, k, v before the rotation, :758-762); all three for every layer, or none */
+#define JUNO_T_ATTN_V_BIAS 14
 
 /* ── GGUF model files (host only, no GPU needed) ───────────────────────────────
  * Replaces node/GgufReader.java for the tensors and metadata the decode path reads: open (:102-180) parses header
@@ -231,7 +234,7 @@ int juno_model_finalize(juno_model *m);
 int juno_gguf_model_cfg(juno_gguf *g, juno_model_cfg *cfg);
 /* Hands every tensor the reference constructor reads (LlamaTransformerHandler.java:238-275: token_embd, output_norm,
  * optional output, blk.N.{attn_norm, ffn_norm, attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down}) to
- * juno_model_set_tensor, straight from the mapped file.  Files with attn_{q,k,v}.bias give JUNO_ERR_UNSUPPORTED.
+ * juno_model_set_tensor, straight from the mapped file; attn_{q,k,v}.bias of every layer too when blk.0.attn_q.bias exists.
  * Call juno_model_finalize afterwards. */
 int juno_model_load_gguf(juno_model *m, juno_gguf *g);
 int juno_model_free(juno_model *m); /* releaseGpuResources (LlamaTransformerHandler.java:424-448) */

@@ -240,6 +240,13 @@ __global__ void argmax_merge_kernel(const float2 *slots /* [world][stride] */, i
     out[seq] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
+// q, k, v += bias (LlamaTransformerHandler.addInPlace :1641-1646, applied before the rotation :758-762): one row of
+// biases laid out like a row of the q|k|v buffer.  Launched only for models that carry attn_{q,k,v}.bias.
+__global__ void qkv_bias_kernel(float *qkv, const float *bias, int n, int width, int ld) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (i < width && b < n) qkv[(size_t)b * ld + i] = __fadd_rn(qkv[(size_t)b * ld + i], bias[i]);
+}
+
 // Start of a tensor-parallel step: the step number the ranks tag their partial products with.
 __global__ void epoch_kernel(unsigned *epoch) { *epoch += 1u; }
 
@@ -259,6 +266,8 @@ struct JunoLayer {
     std::vector<uint8_t> gate_host, up_host;  // row slices waiting for their partner
     int gate_type = -1, up_type = -1;
     float *attn_norm = nullptr, *ffn_norm = nullptr;
+    float *bqkv = nullptr;  // optional attn_{q,k,v}.bias of this rank, laid out like a row of the q|k|v buffer
+    int bias_seen = 0;      // bit per bias kind received
 };
 
 struct JunoGraph {
@@ -387,6 +396,7 @@ static void model_release(juno_model *m) {
         for (int k = 0; k < 12; k++) free_qmat(L.w[k]);
         if (L.attn_norm) cudaFree(L.attn_norm);
         if (L.ffn_norm) cudaFree(L.ffn_norm);
+        if (L.bqkv) cudaFree(L.bqkv);
     }
     m->layers.clear();
     if (m->output_is_embd) m->output = nullptr;
@@ -606,7 +616,7 @@ int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void
     JUNO_TRY(model_check(m));
     JUNO_REQUIRE(blocks, "blocks is null");
     JUNO_REQUIRE(!m->finalized, "model is already finalized");
-    JUNO_REQUIRE(kind >= 0 && kind <= JUNO_T_FFN_DOWN, "unknown tensor kind %d", kind);
+    JUNO_REQUIRE(kind >= 0 && kind <= JUNO_T_ATTN_V_BIAS, "unknown tensor kind %d", kind);
     juno_ctx *c = m->ctx;
     const juno_model_cfg &f = m->cfg;
     std::lock_guard<std::recursive_mutex> lk(c->mu);
@@ -616,6 +626,24 @@ int juno_model_set_tensor(juno_model *m, int32_t kind, int32_t layer, const void
     if (kind > JUNO_T_OUTPUT) JUNO_REQUIRE(layer >= 0 && layer < f.n_layers, "layer %d out of range", layer);
     if (kind == JUNO_T_ATTN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].attn_norm);
     if (kind == JUNO_T_FFN_NORM) return upload_f32_vector(c, blocks, type, rows, cols, H, &m->layers[layer].ffn_norm);
+    if (kind >= JUNO_T_ATTN_Q_BIAS) {
+        // attn_{q,k,v}.bias: F32 vectors of hidden / kvDim elements; this rank keeps the slice of its heads
+        JunoLayer &L = m->layers[layer];
+        const int full = kind == JUNO_T_ATTN_Q_BIAS ? H : f.n_kv_heads * hd;
+        const int loc = kind == JUNO_T_ATTN_Q_BIAS ? m->heads_loc * hd : m->kv_loc * hd;
+        const int dst = kind == JUNO_T_ATTN_Q_BIAS ? 0 : kind == JUNO_T_ATTN_K_BIAS ? m->heads_loc * hd : (m->heads_loc + m->kv_loc) * hd;
+        JUNO_REQUIRE(type == JUNO_TYPE_F32, "bias vectors must be F32 (got GGML type %d)", type);
+        JUNO_REQUIRE(rows * cols == full, "bias kind %d has %lld elements, expected %d", kind, (long long)(rows * cols), full);
+        if (!L.bqkv) {
+            JUNO_TRY(dev_alloc((void **)&L.bqkv, (size_t)m->qkv_ld * 4));
+            JUNO_CUDA_TRY(cudaMemset(L.bqkv, 0, (size_t)m->qkv_ld * 4));
+        }
+        JUNO_CUDA_TRY(cudaMemcpyAsync(L.bqkv + dst, static_cast<const float *>(blocks) + (size_t)r * loc, (size_t)loc * 4, cudaMemcpyHostToDevice, c->stream));
+        JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
+        c->h2d_bytes += loc * 4;
+        L.bias_seen |= 1 << (kind - JUNO_T_ATTN_Q_BIAS);
+        return JUNO_OK;
+    }
 
     int64_t want_rows = 0, want_cols = 0, row0 = 0, nrows = 0, col0 = 0, ncols = 0;
     JUNO_TRY(tp_slice(f.hidden, f.n_heads, f.n_kv_heads, f.inter, f.vocab, kind, m->rank, m->world, &want_rows, &want_cols, &row0, &nrows,
@@ -684,6 +712,8 @@ extern "C" int juno_model_finalize(juno_model *m) {
     for (int l = 0; l < f.n_layers; l++) {
         JunoLayer &L = m->layers[l];
         JUNO_REQUIRE(L.attn_norm && L.ffn_norm, "layer %d: norm weights missing", l);
+        JUNO_REQUIRE(L.bias_seen == 0 || L.bias_seen == 7, "layer %d: attn_q, attn_k and attn_v biases come together or not at all", l);
+        JUNO_REQUIRE(L.bias_seen == m->layers[0].bias_seen, "layer %d: either every layer has attention biases or none (:258-262)", l);
         for (int k = JUNO_T_ATTN_Q; k <= JUNO_T_FFN_DOWN; k++)
             if (k != JUNO_T_FFN_UP) JUNO_REQUIRE(L.w[k], "layer %d: tensor kind %d missing", l, k);
     }
@@ -809,6 +839,12 @@ static int enqueue_layers_batched(juno_model *m, int n, const int32_t *d_slot, c
         juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
         float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
         JUNO_TRY(product(qkv_m, qkv_o, 3, EPI_STORE, m->qkv_ld, m->img_h, sc_h));
+        if (L.bqkv) {
+            const int width = Hl + 2 * KVl;
+            qkv_bias_kernel<<<dim3((width + 255) / 256, n), 256, 0, st>>>(m->qkv, L.bqkv, n, width, m->qkv_ld);
+            JUNO_CUDA_TRY(cudaGetLastError());
+            c->kernel_launches++;
+        }
         AttnArgs at;
         at.pool = m->pool;
         at.layer = l;
@@ -973,6 +1009,12 @@ static int enqueue_layers_q(juno_model *m, int n, const int32_t *d_slot, const i
             juno_qmat *qkv_m[3] = {L.w[JUNO_T_ATTN_Q], L.w[JUNO_T_ATTN_K], L.w[JUNO_T_ATTN_V]};
             float *qkv_o[3] = {m->qkv, m->qkv + Hl, m->qkv + Hl + KVl};
             JUNO_TRY(q_group(m, qkv_m, qkv_o, 3, a, st));
+            if (L.bqkv) {
+                const int width = Hl + 2 * KVl;
+                qkv_bias_kernel<<<dim3((width + 255) / 256, n), 256, 0, st>>>(m->qkv, L.bqkv, n, width, m->qkv_ld);
+                JUNO_CUDA_TRY(cudaGetLastError());
+                c->kernel_launches++;
+            }
             if (pend || pend_inst >= 0) cur ^= 1;
             pend = nullptr;
             pend_inst = -1;
@@ -1474,14 +1516,8 @@ int juno_model_load_gguf(juno_model *m, juno_gguf *g) {
         const int64_t cols = dims[0], rows = nd == 2 ? dims[1] : 1;
         return juno_model_set_tensor(m, kind, layer, data, type, rows, cols);
     };
-    {
-        int32_t bias = 0;
-        JUNO_TRY(juno_gguf_has_tensor(g, "blk.0.attn_q.bias", &bias));
-        if (bias) {
-            set_error("the file has attn_q/k/v bias tensors (Qwen2-style, LlamaTransformerHandler.java:258-262), which this library does not apply");
-            return JUNO_ERR_UNSUPPORTED;
-        }
-    }
+    int32_t has_bias = 0;  // the reference decides by the first layer's attn_q.bias (:258-262)
+    JUNO_TRY(juno_gguf_has_tensor(g, "blk.0.attn_q.bias", &has_bias));
     JUNO_TRY(put("token_embd.weight", JUNO_T_TOKEN_EMBD, 0, false));
     JUNO_TRY(put("output_norm.weight", JUNO_T_OUTPUT_NORM, 0, false));
     JUNO_TRY(put("output.weight", JUNO_T_OUTPUT, 0, true));  // absent: tied to token_embd (:463-470)
@@ -1489,8 +1525,14 @@ int juno_model_load_gguf(juno_model *m, juno_gguf *g) {
         {"attn_norm", JUNO_T_ATTN_NORM}, {"ffn_norm", JUNO_T_FFN_NORM}, {"attn_q", JUNO_T_ATTN_Q},   {"attn_k", JUNO_T_ATTN_K},
         {"attn_v", JUNO_T_ATTN_V},       {"attn_output", JUNO_T_ATTN_OUT}, {"ffn_gate", JUNO_T_FFN_GATE}, {"ffn_up", JUNO_T_FFN_UP},
         {"ffn_down", JUNO_T_FFN_DOWN}};
-    for (int l = 0; l < f.n_layers; l++)
+    for (int l = 0; l < f.n_layers; l++) {
         for (const auto &t : per_layer) JUNO_TRY(put("blk." + std::to_string(l) + "." + t.suffix + ".weight", t.kind, l, false));
+        if (has_bias) {
+            JUNO_TRY(put("blk." + std::to_string(l) + ".attn_q.bias", JUNO_T_ATTN_Q_BIAS, l, false));
+            JUNO_TRY(put("blk." + std::to_string(l) + ".attn_k.bias", JUNO_T_ATTN_K_BIAS, l, false));
+            JUNO_TRY(put("blk." + std::to_string(l) + ".attn_v.bias", JUNO_T_ATTN_V_BIAS, l, false));
+        }
+    }
     return JUNO_OK;
 }
 

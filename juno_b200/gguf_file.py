@@ -89,7 +89,7 @@ def model_tensor_entries(model_tensors, tied_output: bool = False):
         if tied_output and kind == synth.T_OUTPUT:
             continue  # output.weight absent: the reference ties it to token_embd (LlamaTransformerHandler.java:463-470)
         name = synth.GGUF_NAMES[kind].format(layer)
-        dims = [cols] if kind in (synth.T_OUTPUT_NORM, synth.T_ATTN_NORM, synth.T_FFN_NORM) else [cols, rows]
+        dims = [cols] if kind in (synth.T_OUTPUT_NORM, synth.T_ATTN_NORM, synth.T_FFN_NORM) or kind >= synth.T_ATTN_Q_BIAS else [cols, rows]
         yield name, t, dims, blocks
 
 

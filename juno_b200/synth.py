@@ -93,12 +93,14 @@ LLAMA3_70B = Arch(8192, 80, 64, 8, 28672, 128256, 1e-5, 500000.0)
 # tensor kind ids shared with the C ABI
 (T_TOKEN_EMBD, T_OUTPUT_NORM, T_OUTPUT, T_ATTN_NORM, T_FFN_NORM, T_ATTN_Q, T_ATTN_K, T_ATTN_V, T_ATTN_OUT,
  T_FFN_GATE, T_FFN_UP, T_FFN_DOWN) = range(12)
+T_ATTN_Q_BIAS, T_ATTN_K_BIAS, T_ATTN_V_BIAS = 12, 13, 14  # optional (Qwen2-style files)
 
 GGUF_NAMES = {T_TOKEN_EMBD: "token_embd.weight", T_OUTPUT_NORM: "output_norm.weight", T_OUTPUT: "output.weight",
               T_ATTN_NORM: "blk.{}.attn_norm.weight", T_FFN_NORM: "blk.{}.ffn_norm.weight",
               T_ATTN_Q: "blk.{}.attn_q.weight", T_ATTN_K: "blk.{}.attn_k.weight", T_ATTN_V: "blk.{}.attn_v.weight",
               T_ATTN_OUT: "blk.{}.attn_output.weight", T_FFN_GATE: "blk.{}.ffn_gate.weight",
-              T_FFN_UP: "blk.{}.ffn_up.weight", T_FFN_DOWN: "blk.{}.ffn_down.weight"}
+              T_FFN_UP: "blk.{}.ffn_up.weight", T_FFN_DOWN: "blk.{}.ffn_down.weight",
+              T_ATTN_Q_BIAS: "blk.{}.attn_q.bias", T_ATTN_K_BIAS: "blk.{}.attn_k.bias", T_ATTN_V_BIAS: "blk.{}.attn_v.bias"}
 
 
 def q4_k_m_type(kind: int) -> int:
@@ -110,14 +112,17 @@ def tensor_shape(arch: Arch, kind: int):
     H, I, V, kv = arch.hidden, arch.inter, arch.vocab, arch.kv_dim
     return {T_TOKEN_EMBD: (V, H), T_OUTPUT: (V, H), T_ATTN_Q: (H, H), T_ATTN_K: (kv, H), T_ATTN_V: (kv, H),
             T_ATTN_OUT: (H, H), T_FFN_GATE: (I, H), T_FFN_UP: (I, H), T_FFN_DOWN: (H, I),
-            T_OUTPUT_NORM: (1, H), T_ATTN_NORM: (1, H), T_FFN_NORM: (1, H)}[kind]
+            T_OUTPUT_NORM: (1, H), T_ATTN_NORM: (1, H), T_FFN_NORM: (1, H),
+            T_ATTN_Q_BIAS: (1, H), T_ATTN_K_BIAS: (1, kv), T_ATTN_V_BIAS: (1, kv)}[kind]
 
 
-def random_model(arch: Arch, seed: int, type_map=q4_k_m_type, norm: str = "ones"):
+def random_model(arch: Arch, seed: int, type_map=q4_k_m_type, norm: str = "ones", qkv_bias: bool = False):
     """Yields (kind, layer, ggml_type, rows, cols, uint8 blocks) in a fixed order:
     token_embd, output_norm, output, then per layer attn_norm, ffn_norm, q, k, v, o, gate, up, down.
     norm="ones": RMSNorm weights of 1.0 (the benchmark configurations); norm="random": 1 + 0.3*N(0,1), drawn per
-    vector from a generator of their own, so that the matrices of a seed are the same either way."""
+    vector from a generator of their own, so that the matrices of a seed are the same either way.
+    qkv_bias: after each layer's matrices also attn_{q,k,v}.bias (F32, N(0,1) from the same side generator), as
+    Qwen2-style files carry them."""
     rng = np.random.default_rng(seed)
     rng_norm = np.random.default_rng([seed, 0x6E6F726D])
 
@@ -139,3 +144,7 @@ def random_model(arch: Arch, seed: int, type_map=q4_k_m_type, norm: str = "ones"
         yield T_FFN_NORM, l, F32, 1, arch.hidden, norm_vec()
         for kind in (T_ATTN_Q, T_ATTN_K, T_ATTN_V, T_ATTN_OUT, T_FFN_GATE, T_FFN_UP, T_FFN_DOWN):
             yield mat(kind, l)
+        if qkv_bias:
+            for kind in (T_ATTN_Q_BIAS, T_ATTN_K_BIAS, T_ATTN_V_BIAS):
+                n = tensor_shape(arch, kind)[1]
+                yield kind, l, F32, 1, n, rng_norm.standard_normal(n).astype(np.float32).view(np.uint8)

@@ -159,3 +159,6 @@ def model_tensors(r: GgufReader, n_layers: int):
     for l in range(n_layers):
         for suffix, kind in _PER_LAYER:
             yield one(f"blk.{l}.{suffix}.weight", kind, l)
+        if r.has_tensor("blk.0.attn_q.bias"):  # the constructor decides by the first layer's attn_q.bias (:258-262)
+            for suffix, kind in (("attn_q", 12), ("attn_k", 13), ("attn_v", 14)):
+                yield one(f"blk.{l}.{suffix}.bias", kind, l)

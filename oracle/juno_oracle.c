@@ -451,7 +451,7 @@ int jo_greedy(const float *logits, int n, float *probs) {
 /* ── model ─────────────────────────────────────────────────────────────────── */
 enum { JO_T_TOKEN_EMBD = 0, JO_T_OUTPUT_NORM, JO_T_OUTPUT, JO_T_ATTN_NORM, JO_T_FFN_NORM,
        JO_T_ATTN_Q, JO_T_ATTN_K, JO_T_ATTN_V, JO_T_ATTN_OUT, JO_T_FFN_GATE, JO_T_FFN_UP,
-       JO_T_FFN_DOWN, JO_T_COUNT };
+       JO_T_FFN_DOWN, JO_T_ATTN_Q_BIAS, JO_T_ATTN_K_BIAS, JO_T_ATTN_V_BIAS, JO_T_COUNT };
 
 typedef struct {
     const uint8_t *data; /* borrowed */
@@ -564,6 +564,15 @@ int jo_forward(const jo_model *m, jo_seq *s, int token, int pos, float *logits, 
         mv(&L[JO_T_ATTN_Q], xn, q);
         mv(&L[JO_T_ATTN_K], xn, k);
         mv(&L[JO_T_ATTN_V], xn, v);
+        if (L[JO_T_ATTN_Q_BIAS].data) { /* optional attn_{q,k,v}.bias, added before the rotation (:758-762) */
+            const float *bq = (const float *)L[JO_T_ATTN_Q_BIAS].data, *bk = (const float *)L[JO_T_ATTN_K_BIAS].data,
+                        *bv = (const float *)L[JO_T_ATTN_V_BIAS].data;
+            for (int i = 0; i < H; i++) q[i] = q[i] + bq[i];
+            for (int i = 0; i < kvDim; i++) {
+                k[i] = k[i] + bk[i];
+                v[i] = v[i] + bv[i];
+            }
+        }
         jo_rope(q, pos, c->heads, c->head_dim, c->theta);
         jo_rope(k, pos, c->kv_heads, c->head_dim, c->theta);
         for (int i = 0; i < kvDim; i++) {

@@ -347,18 +347,55 @@ def test_model_loaded_from_a_gguf_file(ctx, oracle, tmp_path, tied):
     h.release_gpu_resources()
 
 
-def test_gguf_with_qkv_bias_is_refused(ctx, tmp_path):
-    """Qwen2-style attn_{q,k,v}.bias tensors (LlamaTransformerHandler.java:258-262) are not applied by this library:
-    loading such a file fails loudly instead of computing without them."""
-    from juno_b200 import _lib, gguf_file
+@pytest.mark.parametrize("via_gguf", [False, True], ids=["set_tensor", "gguf-file"])
+def test_qkv_bias_models(ctx, oracle, tmp_path, via_gguf):
+    """Qwen2-style attn_{q,k,v}.bias tensors (LlamaTransformerHandler.java:258-262): added to q, k, v before the rotation
+    (:758-762).  Exact path token by token, the chunked prefill (batched kernels) and the greedy ids, against the oracle
+    with the same biases; handed over tensor by tensor and read from a GGUF file."""
+    from juno_b200 import gguf_file
+    from juno_b200.handler import B200TransformerHandler
+    from oracle import gguf_reader as oref
+    arch = SMALL128
+    if via_gguf:
+        path = tmp_path / "bias.gguf"
+        gguf_file.write_model(path, arch, synth.random_model(arch, 34, norm="random", qkv_bias=True))
+        h = B200TransformerHandler.from_gguf(path, ctx, max_batch=8, max_seqs=2, max_ctx=64, kv_dtype="f32")
+        r = oref.GgufReader(path)
+        om = oracle.Model(arch.hidden, arch.n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab, arch.rms_eps,
+                          arch.rope_theta, kv_f16=False, max_seq=64)
+        kinds = set()
+        for kind, layer, t, rows, cols, raw in oref.model_tensors(r, arch.n_layers):
+            om.set_tensor(kind, layer, raw, t, rows, cols)
+            kinds.add(kind)
+        assert {12, 13, 14} <= kinds
+    else:
+        om, h = build_pair(oracle, arch, seed=34, kv_dtype="f32", max_ctx=64, max_batch=8, max_seqs=2, ctx=ctx, qkv_bias=True)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, arch.vocab, 14).tolist()
+    seq = om.new_seq()
+    for p, t in enumerate(prompt):
+        ref = om.forward(seq, t, p)
+        got = h.forward(ForwardRequest("tok", prompt[: p + 1], p)).logits
+        assert rel_err(got, ref) < TOL, (p, rel_err(got, ref))
+    got = h.prefill("chunk", prompt, 0, want_logits=True)
+    assert rel_err(got, ref) < 5e-3 and int(np.argmax(got)) == oracle.greedy(ref)
+    ref_ids, _ = om.generate_greedy(om.new_seq(), prompt, 16)
+    h.evict("tok")
+    assert generate_greedy(B200InferencePipeline(h), "g", prompt, 16) == ref_ids.tolist()
+    h.release_gpu_resources()
+
+
+def test_incomplete_qkv_bias_is_refused(ctx):
+    """A model with a bias for q but not for k and v cannot be finalized."""
     from juno_b200.handler import B200TransformerHandler
     arch = TINY
-    entries = list(gguf_file.model_tensor_entries(synth.random_model(arch, 32)))
-    entries.append(("blk.0.attn_q.bias", 0, [arch.hidden], np.zeros(arch.hidden, np.float32)))
-    path = tmp_path / "bias.gguf"
-    gguf_file.write_gguf(path, gguf_file.llama_metadata(arch), entries)
-    with pytest.raises(_lib.JunoError, match="bias"):
-        B200TransformerHandler.from_gguf(path, ctx, max_ctx=32)
+    h = B200TransformerHandler(arch, ctx, max_ctx=32)
+    for kind, layer, t, rows, cols, blocks in synth.random_model(arch, 35):
+        h.set_tensor(kind, layer, blocks, t, rows, cols)
+    h.set_tensor(synth.T_ATTN_Q_BIAS, 0, np.zeros(arch.hidden, np.float32), synth.F32, 1, arch.hidden)
+    with pytest.raises(ValueError, match="biases come together"):
+        h.load([])
+    h.release_gpu_resources()
 
 
 def test_session_reuse_restarts_prefill_at_the_matched_prefix(ctx, oracle):

@@ -138,3 +138,35 @@ def test_oracle_forward_runs_and_kv_modes_differ_only_slightly(oracle):
     assert np.abs(a - b).max() / np.abs(a).max() < 5e-2
     with pytest.raises(AssertionError):
         o32.forward(s32, 1, 16)  # beyond max_seq
+
+
+def test_oracle_qkv_bias_is_added_before_the_rotation(oracle):
+    """attn_{q,k,v}.bias (LlamaTransformerHandler.java:258-262, 758-762): zero biases leave every logit bit-identical; a
+    bias on v alone shifts the attention output of position 0 (softmax over one position = 1) by exactly Wo * bias, which
+    shows in the hidden state; a model without bias tensors is unchanged."""
+    from juno_b200 import synth
+    arch = synth.Arch(hidden=256, n_layers=1, n_heads=4, n_kv_heads=2, inter=512, vocab=512)
+    tensors = list(synth.random_model(arch, 3, norm="random"))
+
+    def model(bias):
+        m = oracle.Model(arch.hidden, arch.n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab, arch.rms_eps,
+                         arch.rope_theta, kv_f16=False, max_seq=8)
+        for kind, layer, t, rows, cols, blocks in tensors:
+            m.set_tensor(kind, layer, blocks, t, 1 if kind in (1, 3, 4) else rows, cols)
+        if bias is not None:
+            bq, bk, bv = bias
+            m.set_tensor(12, 0, bq.view(np.uint8), 0, 1, arch.hidden)
+            m.set_tensor(13, 0, bk.view(np.uint8), 0, 1, arch.kv_dim)
+            m.set_tensor(14, 0, bv.view(np.uint8), 0, 1, arch.kv_dim)
+        return m
+
+    z = lambda n: np.zeros(n, np.float32)
+    base = model(None).forward(model(None).new_seq(), 7, 0)
+    m0 = model((z(arch.hidden), z(arch.kv_dim), z(arch.kv_dim)))
+    assert np.array_equal(m0.forward(m0.new_seq(), 7, 0).view(np.uint32), base.view(np.uint32))
+    rng = np.random.default_rng(0)
+    mb = model((z(arch.hidden), z(arch.kv_dim), rng.standard_normal(arch.kv_dim).astype(np.float32)))
+    assert not np.array_equal(mb.forward(mb.new_seq(), 7, 0), base)
+    # q and k biases do not matter at position 0 of a fresh sequence: one position, softmax weight exactly 1
+    mqk = model((rng.standard_normal(arch.hidden).astype(np.float32), rng.standard_normal(arch.kv_dim).astype(np.float32), z(arch.kv_dim)))
+    assert np.array_equal(mqk.forward(mqk.new_seq(), 7, 0).view(np.uint32), base.view(np.uint32))
