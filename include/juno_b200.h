@@ -115,6 +115,12 @@ int juno_kvpool_free(juno_kvpool *p);
 int juno_kvseq_create(juno_kvpool *p, int32_t max_tokens, juno_seq **out);
 int juno_seq_free(juno_seq *s);
 int juno_seq_length(juno_seq *s, int32_t *n_tokens);
+/* Prefix sharing between requests (a kvcache/PrefixCache hit, PrefixCache.java, whose key belongs to another live
+ * request): a new sequence that already holds the first n_tokens cached positions of src (n_tokens <= its length).
+ * No data moves: the pages of the prefix are shared and counted per holder; before either sequence writes into a
+ * shared page (its next position, or a rewrite of older ones) it gets a private copy of that page.  juno_seq_free of
+ * one holder leaves the shared pages to the others. */
+int juno_seq_fork(juno_seq *src, int32_t n_tokens, juno_seq **out);
 /* Append n_tokens positions of K and V ([n_tokens][n_kv_heads*head_dim] FP32, host)
  * for one layer at positions [pos, pos+n_tokens); values are rounded to the pool dtype. */
 int juno_seq_append_kv(juno_seq *s, int32_t layer, int32_t pos, int32_t n_tokens, const float *k_host,

@@ -65,6 +65,7 @@ SIGNATURES = {
     "juno_kvseq_create": (C.c_int, [P, I32, PP]),
     "juno_seq_free": (C.c_int, [P]),
     "juno_seq_length": (C.c_int, [P, C.POINTER(I32)]),
+    "juno_seq_fork": (C.c_int, [P, I32, PP]),
     "juno_seq_append_kv": (C.c_int, [P, I32, I32, I32, P, P]),
     "juno_attn_decode": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),
     "juno_attn_decode_static": (C.c_int, [P, P, I32, I32, PP, I32, P, P]),

@@ -931,6 +931,7 @@ int kvpool_create(juno_ctx *ctx, int n_layers, int n_kv_heads, int head_dim, int
     memset(p->h_table, 0, tbytes);
     p->free_pages.reserve(n_pages);
     for (int i = n_pages - 1; i >= 0; i--) p->free_pages.push_back(i);
+    p->page_refs.assign((size_t)n_pages, 0);
     for (int i = max_slots - 1; i >= 0; i--) p->free_slots.push_back(i);
     *out = p;
     return JUNO_OK;
@@ -973,25 +974,58 @@ int seq_create(juno_kvpool *p, int max_tokens, juno_seq **out) {
     return JUNO_OK;
 }
 
-int seq_reserve(juno_seq *s, int upto, cudaStream_t st) {
+// Copies one page (all layers, K and V) to another on the device, ordered on `st`.
+static int page_copy(juno_kvpool *p, int dst, int src, cudaStream_t st) {
+    const size_t page_bytes = (size_t)p->n_kv_heads * kPageTokens * p->head_dim * p->elem_bytes;
+    for (int layer = 0; layer < p->n_layers; layer++) {
+        const size_t d = ((size_t)layer * p->n_pages + dst) * page_bytes, s = ((size_t)layer * p->n_pages + src) * page_bytes;
+        JUNO_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(p->k) + d, static_cast<const uint8_t *>(p->k) + s, page_bytes, cudaMemcpyDeviceToDevice, st));
+        JUNO_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(p->v) + d, static_cast<const uint8_t *>(p->v) + s, page_bytes, cudaMemcpyDeviceToDevice, st));
+    }
+    return JUNO_OK;
+}
+
+int seq_reserve(juno_seq *s, int from, int upto, cudaStream_t st) {
     juno_kvpool *p = s->pool;
     JUNO_REQUIRE(upto <= s->max_tokens, "position %d is beyond this sequence's limit of %d", upto - 1, s->max_tokens);
     const int need = (upto + kPageTokens - 1) / kPageTokens;
     const int have = (int)s->pages.size();
-    if (need <= have) return JUNO_OK;
-    if ((int)p->free_pages.size() < need - have) {
-        set_error("KV pool exhausted: %d pages free, %d needed", (int)p->free_pages.size(), need - have);
+    // pages of [from, upto) that another sequence holds too (a shared prefix): this sequence writes into its own copy
+    const int first = std::max(0, from) / kPageTokens, last = std::min(need, have) - 1;
+    int shared = 0;
+    for (int i = first; i <= last; i++) shared += p->page_refs[(size_t)s->pages[(size_t)i]] > 1 ? 1 : 0;
+    const int fresh = std::max(0, need - have) + shared;
+    if (fresh == 0) return JUNO_OK;
+    if ((int)p->free_pages.size() < fresh) {
+        set_error("KV pool exhausted: %d pages free, %d needed", (int)p->free_pages.size(), fresh);
         return JUNO_ERR_OOM;
     }
     int32_t *row = p->h_table + (size_t)s->slot * p->max_pages_per_seq;
+    int lo = need, hi = -1;  // table entries that change
+    for (int i = first; i <= last; i++) {
+        const int old = s->pages[(size_t)i];
+        if (p->page_refs[(size_t)old] <= 1) continue;
+        const int pg = p->free_pages.back();
+        p->free_pages.pop_back();
+        JUNO_TRY(page_copy(p, pg, old, st));
+        p->page_refs[(size_t)old]--;
+        p->page_refs[(size_t)pg] = 1;
+        s->pages[(size_t)i] = pg;
+        row[i] = pg;
+        lo = std::min(lo, i);
+        hi = std::max(hi, i);
+    }
     for (int i = have; i < need; i++) {
         int pg = p->free_pages.back();
         p->free_pages.pop_back();
+        p->page_refs[(size_t)pg] = 1;
         s->pages.push_back(pg);
         row[i] = pg;
+        lo = std::min(lo, i);
+        hi = std::max(hi, i);
     }
-    JUNO_CUDA_TRY(cudaMemcpyAsync(p->d_table + (size_t)s->slot * p->max_pages_per_seq + have, row + have,
-                                  (size_t)(need - have) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    JUNO_CUDA_TRY(cudaMemcpyAsync(p->d_table + (size_t)s->slot * p->max_pages_per_seq + lo, row + lo,
+                                  (size_t)(hi - lo + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
     return JUNO_OK;
 }
 
@@ -1054,10 +1088,44 @@ int juno_seq_free(juno_seq *s) {
         DeviceGuard g(p->ctx->device);
         cudaStreamSynchronize(p->ctx->stream);  // no kernel may still read these pages
     }
-    for (int pg : s->pages) p->free_pages.push_back(pg);
+    for (int pg : s->pages)
+        if (--p->page_refs[(size_t)pg] == 0) p->free_pages.push_back(pg);  // a shared page stays with its other holders
     p->free_slots.push_back(s->slot);
     s->pages.clear();
     s->magic = kMagicDead;
+    return JUNO_OK;
+}
+
+int juno_seq_fork(juno_seq *src, int32_t n_tokens, juno_seq **out) {
+    JUNO_TRY(seq_check(src));
+    JUNO_REQUIRE(out, "out is null");
+    JUNO_REQUIRE(n_tokens >= 0 && n_tokens <= src->len, "cannot share %d positions of a sequence that holds %d", n_tokens, src->len);
+    juno_kvpool *p = src->pool;
+    std::lock_guard<std::recursive_mutex> lk(p->ctx->mu);
+    DeviceGuard g(p->ctx->device);
+    juno_seq *s = nullptr;
+    JUNO_TRY(seq_create(p, src->max_tokens, &s));
+    const int n_pg = (n_tokens + kPageTokens - 1) / kPageTokens;
+    int32_t *row = p->h_table + (size_t)s->slot * p->max_pages_per_seq;
+    for (int i = 0; i < n_pg; i++) {
+        const int pg = src->pages[(size_t)i];
+        p->page_refs[(size_t)pg]++;
+        s->pages.push_back(pg);
+        row[i] = pg;
+    }
+    s->len = n_tokens;
+    if (n_pg) {
+        cudaError_t e = cudaMemcpyAsync(p->d_table + (size_t)s->slot * p->max_pages_per_seq, row, (size_t)n_pg * sizeof(int32_t),
+                                        cudaMemcpyHostToDevice, p->ctx->stream);
+        if (e != cudaSuccess) {
+            for (int pg : s->pages) p->page_refs[(size_t)pg]--;
+            p->free_slots.push_back(s->slot);
+            s->magic = kMagicDead;
+            delete s;
+            JUNO_CUDA_TRY(e);
+        }
+    }
+    *out = s;
     return JUNO_OK;
 }
 
@@ -1079,7 +1147,7 @@ int juno_seq_append_kv(juno_seq *s, int32_t layer, int32_t pos, int32_t n_tokens
     if (n_tokens == 0) return JUNO_OK;
     std::lock_guard<std::recursive_mutex> lk(c->mu);
     DeviceGuard g(c->device);
-    JUNO_TRY(seq_reserve(s, pos + n_tokens, c->stream));
+    JUNO_TRY(seq_reserve(s, pos, pos + n_tokens, c->stream));
     const int kvdim = p->n_kv_heads * p->head_dim;
     const size_t bytes = (size_t)n_tokens * kvdim * sizeof(float);
     void *px = c->stage_x, *py = c->stage_y;

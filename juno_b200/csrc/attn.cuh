@@ -13,6 +13,7 @@ struct juno_kvpool {
     int elem_bytes;
     void *k, *v;
     std::vector<int> free_pages;
+    std::vector<int> page_refs;  // sequences holding each page (0 = free): pages of a shared prefix are counted per holder
     // page table for sequences with a slot: [max_slots][max_pages_per_seq] on the device, mirrored in pinned host memory
     int max_slots, max_pages_per_seq;
     int32_t *d_table, *h_table;
@@ -70,6 +71,8 @@ int kvpool_create(juno_ctx *ctx, int n_layers, int n_kv_heads, int head_dim, int
 int kvpool_destroy(juno_kvpool *p);
 int seq_create(juno_kvpool *p, int max_tokens, juno_seq **out);
 // Makes sure pages exist for positions [0, upto) and that the device page table row is current (stream-ordered).
-int seq_reserve(juno_seq *s, int upto, cudaStream_t st);
+// Makes the positions [from, upto) of the sequence writable: allocates missing pages and gives the sequence a private
+// copy of every page of the range that it shares with another sequence (copy-on-write, ordered on `st`).
+int seq_reserve(juno_seq *s, int from, int upto, cudaStream_t st);
 
 }  // namespace juno

@@ -1303,7 +1303,7 @@ static int prepare_step(juno_model *m, int n, juno_seq *const *seqs, const int32
         // a position beyond the sequence's length would make attention read cache rows that were never written
         // (pages come back from the free list as they were left)
         JUNO_REQUIRE(positions[i] <= s->len, "sequence %d: position %d leaves a gap after its %d cached positions", i, positions[i], s->len);
-        JUNO_TRY(seq_reserve(s, positions[i] + 1 + extra_positions, c->stream));
+        JUNO_TRY(seq_reserve(s, positions[i], positions[i] + 1 + extra_positions, c->stream));
         m->h_step[i] = tokens[i];
         m->h_step[B + i] = positions[i];
         m->h_step[2 * B + i] = s->slot;
@@ -1390,7 +1390,7 @@ int juno_prefill(juno_model *m, juno_seq *seq, const int32_t *token_ids, int32_t
         const int n = std::min(chunk_max, n_tokens - done), pos0 = start_pos + done;
         const bool last = done + n == n_tokens;
         JUNO_TRY(step_sync(m));  // the pinned step buffer is reused
-        JUNO_TRY(seq_reserve(seq, pos0 + n, st));
+        JUNO_TRY(seq_reserve(seq, pos0, pos0 + n, st));
         for (int i = 0; i < n; i++) {
             m->h_step[i] = token_ids[done + i];
             m->h_step[B + i] = pos0 + i;

@@ -191,6 +191,17 @@ class B200TransformerHandler:
         check(self._L.juno_model_tp_mode(self.handle, C.byref(mode)), "juno_model_tp_mode")
         return mode.value
 
+    def fork(self, source_id: str, request_id: str, n_tokens: int) -> None:
+        """A new request that starts with the first n_tokens cached positions of another live request (prefix-cache hit
+        across requests): pages are shared, nothing is copied until one of the two writes into a shared page."""
+        if request_id in self._seqs:
+            raise ValueError(f"request {request_id} already holds a KV sequence")
+        if source_id not in self._seqs:
+            raise ValueError(f"request {source_id} holds no KV sequence")
+        s = C.c_void_p()
+        check(self._L.juno_seq_fork(self._seqs[source_id], int(n_tokens), C.byref(s)), "juno_seq_fork")
+        self._seqs[request_id] = s
+
     def evict(self, request_id: str) -> None:
         """LlamaTransformerHandler.evict (:498-505): drops the request's KV pages; unknown ids are ignored."""
         s = self._seqs.pop(request_id, None)

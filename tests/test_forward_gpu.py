@@ -429,3 +429,58 @@ def test_session_reuse_restarts_prefill_at_the_matched_prefix(ctx, oracle):
     got = h.forward(ForwardRequest("session-c", p2[:1], 0)).logits
     assert rel_err(got, om.forward(om.new_seq(), p2[0], 0)) < TOL
     h.release_gpu_resources()
+
+
+@pytest.mark.parametrize("kv_dtype", ["f32", "f16"])
+def test_shared_prefix_fork_and_copy_on_write(ctx, oracle, kv_dtype):
+    """Prefix sharing between live requests (juno_seq_fork): request B adopts the first 24 cached positions of request A
+    (one whole page and half of the next).  Both then go their own ways - B through the chunked prefill and token by
+    token, A by decoding on and by REWRITING positions inside the shared pages - and each must match the oracle run
+    from scratch on its own token sequence: a write into a shared page has to land in a private copy.  Freeing one
+    holder leaves the other intact, and all pages come back in the end."""
+    arch = SMALL128
+    tol = TOL if kv_dtype == "f32" else TOL_F16_KV
+    om, h = build_pair(oracle, arch, seed=36, kv_dtype=kv_dtype, max_ctx=64, max_batch=8, max_seqs=3, ctx=ctx)
+    rng = np.random.default_rng(11)
+    pa = rng.integers(0, arch.vocab, 40).tolist()
+    tail_b = rng.integers(0, arch.vocab, 14).tolist()
+
+    def oracle_logits(tokens):
+        seq = om.new_seq()
+        for p, t in enumerate(tokens):
+            out = om.forward(seq, t, p)
+        return out
+
+    for p in range(len(pa) - 1):
+        h.forward_batch(["A"], [[pa[p]]], [p], want_logits=False, want_argmax=True)
+    h.fork("A", "B", 24)
+    with pytest.raises(ValueError, match="cannot share"):
+        h.fork("A", "C", 41)
+    # B: positions 24..30 through the chunked prefill (first write into the half page -> private copy), then token by token
+    tb = pa[:24] + tail_b
+    h.prefill("B", tb[24:31], 24)
+    for p in range(31, len(tb) - 1):
+        h.forward_batch(["B"], [[tb[p]]], [p], want_logits=False, want_argmax=True)
+    got_b = h.forward(ForwardRequest("B", tb, len(tb) - 1)).logits
+    assert rel_err(got_b, oracle_logits(tb)) < max(tol, 5e-3)
+    # A is untouched by B's writes
+    got_a = h.forward(ForwardRequest("A", pa, len(pa) - 1)).logits
+    assert rel_err(got_a, oracle_logits(pa)) < tol
+    # A rewrites positions 10..39 (inside the page it still shares with B) with other tokens; B must not see them
+    pa2 = pa[:10] + rng.integers(0, arch.vocab, 30).tolist()
+    for p in range(10, len(pa2) - 1):
+        h.forward_batch(["A"], [[pa2[p]]], [p], want_logits=False, want_argmax=True)
+    got_a2 = h.forward(ForwardRequest("A", pa2, len(pa2) - 1)).logits
+    assert rel_err(got_a2, oracle_logits(pa2)) < tol
+    tb2 = tb + [5]
+    got_b2 = h.forward(ForwardRequest("B", tb2, len(tb2) - 1)).logits
+    assert rel_err(got_b2, oracle_logits(tb2)) < max(tol, 5e-3)
+    # one holder leaves; the other still reads the shared first page
+    h.evict("A")
+    tb3 = tb2 + [6]
+    assert rel_err(h.forward(ForwardRequest("B", tb3, len(tb3) - 1)).logits, oracle_logits(tb3)) < max(tol, 5e-3)
+    h.evict("B")
+    # every page is free again: three sequences can be filled to max_ctx
+    for rid in ("x", "y", "z"):
+        h.prefill(rid, rng.integers(0, arch.vocab, 64).tolist(), 0)
+    h.release_gpu_resources()
