@@ -32,7 +32,8 @@ final class B200Bindings {
 
 	/** Tensor kinds of juno_model_set_tensor, in header order. */
 	static final int T_TOKEN_EMBD = 0, T_OUTPUT_NORM = 1, T_OUTPUT = 2, T_ATTN_NORM = 3, T_FFN_NORM = 4, T_ATTN_Q = 5,
-			T_ATTN_K = 6, T_ATTN_V = 7, T_ATTN_OUT = 8, T_FFN_GATE = 9, T_FFN_UP = 10, T_FFN_DOWN = 11;
+			T_ATTN_K = 6, T_ATTN_V = 7, T_ATTN_OUT = 8, T_FFN_GATE = 9, T_FFN_UP = 10, T_FFN_DOWN = 11, T_ATTN_Q_BIAS = 12,
+			T_ATTN_K_BIAS = 13, T_ATTN_V_BIAS = 14;
 
 	/** juno_model_cfg: fifteen 32-bit fields then uint8_t nccl_id[128] = 188 bytes. */
 	static final StructLayout MODEL_CFG = MemoryLayout.structLayout(JAVA_INT.withName("struct_size"),
@@ -79,6 +80,7 @@ final class B200Bindings {
 	static final MethodHandle modelSeqCreate = h("juno_model_seq_create", fn(ADDRESS, ADDRESS));
 	static final MethodHandle seqFree = h("juno_seq_free", fn(ADDRESS));
 	static final MethodHandle seqLength = h("juno_seq_length", fn(ADDRESS, ADDRESS));
+	static final MethodHandle seqFork = h("juno_seq_fork", fn(ADDRESS, JAVA_INT, ADDRESS));
 	static final MethodHandle forward = h("juno_forward", fn(ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
 	static final MethodHandle prefill = h("juno_prefill", fn(ADDRESS, ADDRESS, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
 	static final MethodHandle decodeGreedy = h("juno_decode_greedy", fn(ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS));

@@ -181,6 +181,28 @@ final class B200TransformerHandler implements ForwardPassHandler {
 		}
 	}
 
+	/**
+	 * A prefix-cache hit whose pages belong to another live request (PrefixCache.findLongestPrefix): the new request
+	 * starts with the first matchedTokens cached positions of the source; pages are shared until one of the two writes.
+	 */
+	void adoptPrefix(String sourceRequestId, String requestId, int matchedTokens) {
+		MemorySegment src = sequences.get(sourceRequestId);
+		if (src == null)
+			throw new IllegalArgumentException("request " + sourceRequestId + " holds no KV sequence");
+		synchronized (lock) {
+			try (Arena a = Arena.ofConfined()) {
+				MemorySegment out = a.allocate(ADDRESS);
+				B200Bindings.check((int) B200Bindings.seqFork.invokeExact(src, matchedTokens, out), "juno_seq_fork");
+				if (sequences.putIfAbsent(requestId, out.get(ADDRESS, 0)) != null)
+					throw new IllegalArgumentException("request " + requestId + " already holds a KV sequence");
+			} catch (RuntimeException e) {
+				throw e;
+			} catch (Throwable t) {
+				throw new IllegalStateException(t);
+			}
+		}
+	}
+
 	/** Frees the KV pages of a finished request (KVCacheManager eviction). */
 	void evict(String requestId) {
 		MemorySegment s = sequences.remove(requestId);
