@@ -516,6 +516,13 @@ static int tp_push_setup(juno_model *m) {
     JUNO_CUDA_TRY(cudaStreamSynchronize(c->stream));
     cudaFree(d_ok);
     m->tp_push = (bad == 0.f);
+    if (!m->tp_push) {  // some rank could not map a peer: every rank drops its mappings and the group uses NCCL
+        for (int r = 0; r < W; r++) {
+            if (m->tp_peer[r] && m->tp_peer[r] != m->tp_buf) cudaIpcCloseMemHandle(m->tp_peer[r]);
+            m->tp_peer[r] = nullptr;
+        }
+        cudaGetLastError();
+    }
     return JUNO_OK;
 }
 

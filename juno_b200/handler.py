@@ -126,7 +126,12 @@ class B200TransformerHandler:
         """The reference's load path in one call: GgufReader.open, LlamaConfig.from, the handler constructor."""
         from .gguf_file import GgufFile
         with GgufFile(path) as g:
-            return cls(g.arch(), ctx, **kw).load_gguf(g)
+            h = cls(g.arch(), ctx, **kw)
+            try:
+                return h.load_gguf(g)
+            except Exception:
+                h.release_gpu_resources()  # a file the library refuses must not leave a half-built model behind
+                raise
 
     # ── ForwardPassHandler ─────────────────────────────────────────────────────
     def is_ready(self) -> bool:
