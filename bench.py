@@ -98,7 +98,7 @@ def host_cores() -> int:
         return max(1, os.cpu_count() or 1)
 
 
-def cpu_decode_rate(arch, tensors, budget_s: float, ctx_len: int = 0):
+def cpu_decode_rate(arch, tensors, limit_s: float, ctx_len: int = 0):
     """Times the CPU oracle on a bounded sample: batch-1 decode steps at context `ctx_len` (the KV cache of the sample
     layers is pre-filled with pseudo-random rows) through the first L' layers plus the output projection, on all host
     cores, scaled to the full model: the layer part by the number of layers, the output projection once.
@@ -134,10 +134,10 @@ def cpu_decode_rate(arch, tensors, budget_s: float, ctx_len: int = 0):
     probe = build(1)
     t_one = timed(probe, 2, ctx_len)
     probe.close()
-    # choose layers so that a handful of steps fit the budget
-    n_layers = max(2, min(arch.n_layers, int(budget_s / 4 / max(t_one, 1e-6))))
+    # choose layers so that a handful of steps fit the time limit
+    n_layers = max(2, min(arch.n_layers, int(limit_s / 4 / max(t_one, 1e-6))))
     m = build(n_layers)
-    steps = max(2, min(16, int(budget_s * 0.6 / max(t_one * n_layers, 1e-6))))
+    steps = max(2, min(16, int(limit_s * 0.6 / max(t_one * n_layers, 1e-6))))
     t_n = timed(m, steps, ctx_len)
     m.close()
     per_layer = max(0.0, (t_n - t_one) / (n_layers - 1))
@@ -164,8 +164,8 @@ def run_reference(args, arch, seed, rank):
     start = 0 if args.no_prefill else args.ctx - 1
     probe_rate, _, _ = cpu_decode_rate(arch, tensors, 6.0, start)
     full_step = 1.0 / probe_rate
-    budget = 150.0
-    n_layers = max(1, min(arch.n_layers, int(arch.n_layers * budget / (total_steps * full_step))))
+    limit = 150.0
+    n_layers = max(1, min(arch.n_layers, int(arch.n_layers * limit / (total_steps * full_step))))
     m = o.Model(arch.hidden, n_layers, arch.n_heads, arch.n_kv_heads, arch.inter, arch.vocab, arch.rms_eps,
                 arch.rope_theta, kv_f16=False, max_seq=start + total_steps + 1)
     for kind, layer, t, rows, cols, blocks in tensors:
